@@ -1,0 +1,313 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A16 MoE layer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--impl ours|reference]
+
+One "step" is one pass of the whole layer (router GEMM -> top-k -> dispatch -> grouped
+gate/up + SwiGLU -> down -> shared expert -> combine) over one batch of T synthetic tokens of a
+GLM-scale layer (H=6144, 256 experts top-8, I=2048, one shared expert, int4 group 128).
+Default T=64: the decode-shaped configuration the headline metric is quoted on.  Prints ONE
+JSON line.  With N>1 (launched by torch.distributed.run, one rank per GPU) every rank runs
+its own replica of the layer on its own T tokens: the path shards over independent tokens
+with no data-path collective, so scaling is "weak" and the value is all ranks' tokens over
+the slowest rank's time.
+
+`--impl reference` times the reference's own CPU float32 MoE (GLM52Model::moe_mlp built from
+the reference sources into oracle/_ref, else the C restatement in oracle/) on a bounded
+token sample of the same workload, on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GLM = dict(H=6144, E=256, topk=8, I=2048, Is=2048, group=128)
+W_EXPERT_BYTES = 3 * GLM["H"] * GLM["I"] // 2 + 3 * GLM["H"] * GLM["I"] // GLM["group"] * 2  # 19,464,192
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows = []
+        self.proc = None
+        self.idx = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            f = [c.strip() for c in r.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        sm.sort()
+        return dict(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def algorithmic_bytes(ids_np, T: int) -> dict:
+    """Bytes the layer must move at least once: each distinct expert's weights once, router
+    weight, activations in and out."""
+    import numpy as np
+    distinct = int(np.unique(ids_np).size)
+    wbytes = (distinct + 1) * W_EXPERT_BYTES
+    total = wbytes + GLM["E"] * GLM["H"] * 2 + T * GLM["H"] * 2 + T * GLM["H"] * 4
+    gate_up = (distinct + 1) * (2 * GLM["H"] * GLM["I"] // 2 + 2 * GLM["H"] * GLM["I"] // GLM["group"] * 2)
+    return dict(distinct_experts=distinct, layer_bytes=total, gate_up_bytes=gate_up,
+                down_bytes=wbytes - gate_up)
+
+
+def cpu_port_baseline(Lnp, x_np, sample_tokens: int) -> dict:
+    import oracle
+    xs = x_np[:sample_tokens]
+    nthreads = oracle.max_threads()
+    t0 = time.perf_counter()
+    oracle.moe_layer_w4(xs, Lnp, nthreads=nthreads)
+    dt = time.perf_counter() - t0
+    return dict(value=sample_tokens / dt, unit="tokens/s", cores=nthreads, kind="port",
+                sample=f"first {sample_tokens} tokens of the batch, {dt:.1f} s, C restatement of moe_mlp "
+                       f"(expert-major, int4 rows dequantised on the fly) on {nthreads} threads")
+
+
+def run_ours(args) -> None:
+    import numpy as np
+    import torch
+
+    from glmserve_b200 import ops
+    from glmserve_b200.synth import layer_to_np, make_layer_torch, make_x_torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    T = args.tokens
+
+    Lt = make_layer_torch(GLM, seed=1, device=dev)
+    layer = ops.MoELayer(Lt, keep_raw=False)
+    x = make_x_torch(T, GLM["H"], seed=100 + rank, device=dev)
+    out = torch.empty((T, GLM["H"]), dtype=torch.float32, device=dev)
+    x_host = x.cpu().pin_memory()
+    out_host = torch.empty((T, GLM["H"]), dtype=torch.float32).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # warm-up (also sizes the workspace) and routing for the byte count
+    _, _, ids, _ = layer.forward(x, out=out, path=ops.PATH_DECODE, return_routing=True)
+    for _ in range(max(args.warmup, 3)):
+        layer.forward(x, out=out, path=ops.PATH_DECODE)
+    assert layer.status() == 0, "device-side wait timed out during warm-up"
+    alg = algorithmic_bytes(ids.cpu().numpy(), T)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ops.profile_enable(layer, args.steps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        layer.forward(x, out=out, path=ops.PATH_DECODE)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    stages = ops.profile_read(layer)
+    ops.profile_enable(layer, 0)
+
+    # end to end through the host-buffer call: H2D of the step's tokens, D2H of its output
+    for _ in range(3):
+        layer.forward_host(x_host, out_host, path=ops.PATH_DECODE)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        layer.forward_host(x_host, out_host, path=ops.PATH_DECODE)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if rank == 0 else None
+    assert layer.status() == 0, "device-side wait timed out"
+
+    ms_step = ms_total / args.steps
+    e2e_ms = e2e_s * 1e3 / args.steps
+    if world > 1:
+        t = torch.tensor([ms_step, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        pk = peaks()
+        gu_ms = stages["moe.gate_up"]
+        achieved = alg["gate_up_bytes"] / (gu_ms * 1e-3) / 1e9 if gu_ms > 0 else 0.0
+        layer_gbs = alg["layer_bytes"] / (ms_step * 1e-3) / 1e9
+        line = {
+            "metric": f"w4a16_moe_layer_decode_T{T}_tokens_per_s",
+            "value": world * T / (ms_step * 1e-3),
+            "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "w4a16 (int4 weights, fp16 mma, fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": f"GLM-scale decode MoE layer, T={T} tokens per GPU: hidden 6144, 256 routed "
+                                   "experts top-8, expert intermediate 2048, 1 shared expert, W4A16 group 128, "
+                                   "fp16 scales, bf16 activations",
+                       "multi_gpu": "independent replicas (tokens shard, no collective)" if world > 1 else "single GPU",
+                       "l2": "inputs larger than L2: every step streams the touched experts' "
+                             f"{alg['layer_bytes'] / 1e9:.2f} GB of weights, far beyond the 126 MB L2",
+                       "distinct_experts": alg["distinct_experts"]},
+            "layer_gbs": layer_gbs,
+            "layer_frac_of_measured_hbm": layer_gbs / pk["hbm_gbs"],
+            "layer_frac_of_8tbs": layer_gbs / 8000.0,
+            "stage_ms": {k: v for k, v in stages.items() if k != "forwards"},
+            "roofline": {"bound": "hbm", "kernel": "decode_gemm_kernel<gate_up>",
+                         "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"],
+                         "algorithmic_bytes": alg["gate_up_bytes"], "kernel_ms": gu_ms, "traffic": None},
+            "e2e": {"value": world * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": T * GLM["H"] * 2, "d2h_bytes_per_step": T * GLM["H"] * 4},
+            "gpu_launches": 8 * args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_port_baseline(layer_to_np(Lt), x.float().cpu().numpy(),
+                                                     min(T, args.cpu_tokens))
+        traffic_file = os.path.join(ROOT, "profiles", "decode_gate_up_traffic.json")
+        if os.path.exists(traffic_file):
+            with open(traffic_file) as f:
+                tr = json.load(f)
+            line["roofline"]["traffic"] = tr.get("dram_bytes_per_launch_T64") if T == 64 else None
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args) -> None:
+    """The reference's own CPU float32 MoE on a bounded token sample (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    import numpy as np
+    import torch
+
+    import oracle
+    from glmserve_b200.synth import layer_to_np, make_layer_torch, make_x_torch
+
+    T = args.tokens
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if torch.cuda.is_available() else torch.device("cpu")
+    sample = max(1, min(T, args.ref_tokens))
+    Lt = make_layer_torch(GLM, seed=1, device=dev)
+    x_np = make_x_torch(T, GLM["H"], seed=100, device=dev).float().cpu().numpy()[:sample]
+    Lnp = layer_to_np(Lt)
+    del Lt
+    logits = oracle.linear(Lnp["router_w"], x_np)
+    ids, _, _ = oracle.router(logits, Lnp["e_bias"], GLM["topk"], True, 2.5)
+    use_ref = oracle.ref_available()
+    times = []
+    if use_ref:
+        active = np.zeros(GLM["E"], np.uint8)
+        active[np.unique(ids)] = 1
+        ref_layer = oracle.RefLayer(Lnp, active=active)
+        for i in range(args.warmup + args.steps):
+            _, secs = ref_layer.run(x_np)
+            if i >= args.warmup:
+                times.append(secs)
+        ref_layer.close()
+        cores, kind = 1, "reference"
+        what = (f"GLM52Model::moe_mlp built from the reference sources, first {sample} tokens of the batch, "
+                "1 thread (the reference runs its token loop single-threaded below 256 tokens), weights "
+                "dequantised to fp32 beforehand as the reference does at load")
+    else:
+        cores, kind = oracle.max_threads(), "port"
+        for i in range(args.warmup + args.steps):
+            t0 = time.perf_counter()
+            oracle.moe_layer_w4(x_np, Lnp, nthreads=cores)
+            if i >= args.warmup:
+                times.append(time.perf_counter() - t0)
+        what = f"C restatement of moe_mlp, first {sample} tokens of the batch, {cores} threads"
+    sec = sum(times) / len(times)
+    val = sample / sec
+    print(json.dumps({
+        "impl": "reference", "metric": f"w4a16_moe_layer_decode_T{T}_tokens_per_s", "value": val,
+        "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"GLM-scale decode MoE layer, T={T}: bounded sample of {sample} tokens on the host CPU"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": what},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-tokens", type=int, default=16, help="token sample of the CPU baseline leg")
+    ap.add_argument("--ref-tokens", type=int, default=4, help="token sample of --impl reference")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,423 @@
+// C ABI of the library: argument validation, plan object, workspace carving, launches.
+// Declarations and per-entry documentation: include/glmserve_b200.h.
+#include <new>
+
+#include "common.cuh"
+#include "launchers.cuh"
+
+using namespace gsb;
+
+namespace {
+
+inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+struct gsb_moe_layer {
+    gsb_moe_config cfg;
+    bool tiles_ok;       // shapes fit the tile-stream kernels and prepacked weights are given
+    int sm_count;
+    // stage profiler (counterpart of StageProf, src/model_gpu.cpp:328-388 of the reference)
+    cudaEvent_t* prof_ev = nullptr;   // [prof_sets][GSB_N_STAGES + 1]
+    int prof_sets = 0;
+    int prof_used = 0;
+};
+
+namespace {
+
+// Carves the caller's scratch.  Every buffer starts on a 256-byte boundary.
+struct Workspace {
+    int* status;              // int32[64]
+    float* logits;            // [n, E]
+    int* ids;                 // [n, topk]
+    float* w;                 // [n, topk]
+    int* expert_offsets;      // [E + 1]
+    int* sorted_tok;          // [P]
+    int* sorted_row;          // [P]
+    int* slot_pos;            // [P]
+    int* segs;                // decode segments: int4 per segment, [kMaxSegHeader + nseg_max]
+    __half* xp;               // [n, H] fp16 activations in fragment order
+    __half* hbuf;             // [P + n, Imax] fp16 SwiGLU output in fragment order
+    float* ybuf;              // [P + n, H] per-slot down-projection rows
+    __nv_bfloat16* xnorm;     // [n, H] bf16 (block layer: rmsnorm output)
+    float* mlp;               // [n, H] (block layer: layer output before the residual add)
+    size_t total;
+};
+
+Workspace carve(const gsb_moe_config& c, int n, void* base) {
+    Workspace ws{};
+    const size_t P = (size_t)n * c.topk;
+    const size_t imax = (size_t)(c.moe_inter > c.shared_inter ? c.moe_inter : c.shared_inter);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = off;
+        off = align_up(off + bytes, 256);
+        return base ? reinterpret_cast<char*>(base) + o : nullptr;
+    };
+    ws.status = reinterpret_cast<int*>(take(64 * sizeof(int)));
+    ws.logits = reinterpret_cast<float*>(take((size_t)n * c.n_experts * sizeof(float)));
+    ws.ids = reinterpret_cast<int*>(take(P * sizeof(int)));
+    ws.w = reinterpret_cast<float*>(take(P * sizeof(float)));
+    ws.expert_offsets = reinterpret_cast<int*>(take((size_t)(c.n_experts + 1) * sizeof(int)));
+    ws.sorted_tok = reinterpret_cast<int*>(take(P * sizeof(int)));
+    ws.sorted_row = reinterpret_cast<int*>(take(P * sizeof(int)));
+    ws.slot_pos = reinterpret_cast<int*>(take(P * sizeof(int)));
+    ws.segs = reinterpret_cast<int*>(take(decode_seg_bytes(n, c.topk, c.n_experts)));
+    ws.xp = reinterpret_cast<__half*>(take((size_t)n * c.hidden * sizeof(__half)));
+    ws.hbuf = reinterpret_cast<__half*>(take((P + n) * imax * sizeof(__half)));
+    ws.ybuf = reinterpret_cast<float*>(take((P + n) * (size_t)c.hidden * sizeof(float)));
+    ws.xnorm = reinterpret_cast<__nv_bfloat16*>(take((size_t)n * c.hidden * sizeof(__nv_bfloat16)));
+    ws.mlp = reinterpret_cast<float*>(take((size_t)n * c.hidden * sizeof(float)));
+    ws.total = off;
+    return ws;
+}
+
+bool tile_shapes_ok(const gsb_moe_config& c) {
+    if (c.group != 128) return false;
+    if (c.hidden % 512 || c.moe_inter % 512) return false;
+    if (c.shared_inter && c.shared_inter % 512) return false;
+    if (!c.gate_up_packed || !c.down_packed) return false;
+    if (c.shared_inter && (!c.shared_gate_up_packed || !c.shared_down_packed)) return false;
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* gsb_status_string(int status) {
+    switch (status) {
+        case GSB_OK: return "ok";
+        case GSB_ERR_INVALID_ARG: return "invalid argument";
+        case GSB_ERR_UNSUPPORTED: return "unsupported shape or format";
+        case GSB_ERR_LAUNCH: return "kernel launch failed";
+        case GSB_ERR_TIMEOUT: return "device-side wait timed out";
+        case GSB_ERR_CUDA: return "CUDA runtime call failed";
+        case GSB_ERR_WORKSPACE: return "workspace too small";
+        default: return "unknown status";
+    }
+}
+
+const char* gsb_build_info(void) { return "glmserve_b200 0.1 sm_100a"; }
+
+int gsb_moe_router(const float* logits, const float* e_bias, int n, int E, int topk, int norm_topk,
+                   float routed_scale, int* topk_ids, float* topk_weights, void* stream) {
+    if (n < 0 || E <= 0 || topk <= 0) return GSB_ERR_INVALID_ARG;
+    if (n == 0) return GSB_OK;
+    if (!logits || !topk_ids || !topk_weights) return GSB_ERR_INVALID_ARG;
+    if (E > 1024 || topk > 32 || topk > E) return GSB_ERR_UNSUPPORTED;
+    return launch_router_topk(logits, e_bias, n, E, topk, norm_topk, routed_scale, topk_ids,
+                              topk_weights, as_stream(stream));
+}
+
+int gsb_moe_dispatch(const int* topk_ids, int n, int topk, int E, int* expert_offsets,
+                     int* sorted_token_ids, int* sorted_row, void* stream) {
+    if (n < 0 || E <= 0 || topk <= 0 || !expert_offsets) return GSB_ERR_INVALID_ARG;
+    if (n > 0 && (!topk_ids || !sorted_token_ids || !sorted_row)) return GSB_ERR_INVALID_ARG;
+    if ((int64_t)n * topk > (int64_t)1 << 30) return GSB_ERR_UNSUPPORTED;
+    return launch_dispatch(topk_ids, n, topk, E, expert_offsets, sorted_token_ids, sorted_row,
+                           nullptr, as_stream(stream));
+}
+
+int gsb_moe_expert_ffn_w4a16(const float* x, const int* topk_ids, const float* topk_weights,
+                             const uint8_t* gate_q, const float* gate_sc, const uint8_t* up_q,
+                             const float* up_sc, const uint8_t* down_q, const float* down_sc, int n,
+                             int topk, int hidden, int moe_inter, int E, int group_size, float* out,
+                             void* stream) {
+    if (n < 0 || topk <= 0 || hidden <= 0 || moe_inter <= 0 || E <= 0 || group_size <= 0)
+        return GSB_ERR_INVALID_ARG;
+    if (n == 0) return GSB_OK;
+    if (!x || !topk_ids || !topk_weights || !gate_q || !gate_sc || !up_q || !up_sc || !down_q ||
+        !down_sc || !out)
+        return GSB_ERR_INVALID_ARG;
+    if (!aligned(gate_q, 4) || !aligned(up_q, 4) || !aligned(down_q, 4)) return GSB_ERR_INVALID_ARG;
+    GenericExpertArgs a{};
+    a.x = x; a.ids = topk_ids; a.w = topk_weights;
+    a.gate = gate_q; a.gate_sc = gate_sc; a.up = up_q; a.up_sc = up_sc;
+    a.down = down_q; a.down_sc = down_sc;
+    a.n = n; a.topk = topk; a.H = hidden; a.I = moe_inter; a.Is = 0; a.E = E; a.group = group_size;
+    a.out = out;
+    return launch_generic_expert(a, 0, 0, true, as_stream(stream));
+}
+
+int gsb_moe_expert_ffn(const float* x, const int* topk_ids, const float* topk_weights,
+                       const float* gate_w, const float* up_w, const float* down_w, int n, int topk,
+                       int hidden, int moe_inter, int E, float* out, void* stream) {
+    if (n < 0 || topk <= 0 || hidden <= 0 || moe_inter <= 0 || E <= 0) return GSB_ERR_INVALID_ARG;
+    if (n == 0) return GSB_OK;
+    if (!x || !topk_ids || !topk_weights || !gate_w || !up_w || !down_w || !out)
+        return GSB_ERR_INVALID_ARG;
+    GenericExpertArgs a{};
+    a.x = x; a.ids = topk_ids; a.w = topk_weights;
+    a.gate = gate_w; a.up = up_w; a.down = down_w;
+    a.n = n; a.topk = topk; a.H = hidden; a.I = moe_inter; a.Is = 0; a.E = E; a.group = 1;
+    a.out = out;
+    return launch_generic_expert(a, 0, 0, false, as_stream(stream));
+}
+
+int gsb_gemm_w4a16(const float* x, const uint8_t* qW, const float* scales, const float* bias,
+                   float* y, int64_t n, int64_t in, int64_t out, int64_t group_size, void* stream) {
+    if (n < 0 || in <= 0 || out < 0 || group_size <= 0) return GSB_ERR_INVALID_ARG;
+    if (n == 0 || out == 0) return GSB_OK;
+    if (!x || !qW || !scales || !y || !aligned(qW, 4)) return GSB_ERR_INVALID_ARG;
+    return launch_generic_gemm_w4(x, qW, scales, bias, y, n, in, out, group_size, as_stream(stream));
+}
+
+int gsb_silu_mul(const float* g, const float* u, float* out, int64_t n, void* stream) {
+    if (n < 0 || (n > 0 && (!g || !u || !out))) return GSB_ERR_INVALID_ARG;
+    return launch_silu_mul(g, u, out, n, as_stream(stream));
+}
+int gsb_add_inplace(float* y, const float* x, int64_t n, void* stream) {
+    if (n < 0 || (n > 0 && (!y || !x))) return GSB_ERR_INVALID_ARG;
+    return launch_add_inplace(y, x, n, as_stream(stream));
+}
+int gsb_rmsnorm(const float* x, const float* w, float* out, int64_t n, int64_t d, float eps,
+                void* stream) {
+    if (n < 0 || d <= 0 || (n > 0 && (!x || !w || !out))) return GSB_ERR_INVALID_ARG;
+    return launch_rmsnorm_f32(x, w, out, n, d, eps, as_stream(stream));
+}
+
+int gsb_qtype_has_i8(uint32_t) { return 0; }
+int gsb_quantize_act_q8(const float* x, int64_t n, int64_t in, int8_t* xq, float* xs, void* stream) {
+    if (n < 0 || in <= 0 || (n > 0 && (!x || !xq || !xs))) return GSB_ERR_INVALID_ARG;
+    return launch_quantize_act_q8(x, n, in, xq, xs, as_stream(stream));
+}
+int gsb_gemm_q(uint32_t, const float*, const uint8_t*, const float*, float*, int64_t, int64_t,
+               int64_t, int64_t, void*) { return GSB_ERR_UNSUPPORTED; }
+int gsb_gemm_q_i8(uint32_t, const int8_t*, const float*, const uint8_t*, const float*, float*,
+                  int64_t, int64_t, int64_t, int64_t, void*) { return GSB_ERR_UNSUPPORTED; }
+int gsb_moe_expert_ffn_q(uint32_t, uint32_t, uint32_t, const float*, const int*, const float*,
+                         const uint8_t*, const uint8_t*, const uint8_t*, int, int, int, int, int,
+                         int64_t, int64_t, int64_t, float*, float*, float*, int*, float*, void*) {
+    return GSB_ERR_UNSUPPORTED;
+}
+int gsb_moe_expert_ffn_q_i8(uint32_t, uint32_t, uint32_t, const int8_t*, const float*, const int*,
+                            const float*, const uint8_t*, const uint8_t*, const uint8_t*, int, int,
+                            int, int, int, int64_t, int64_t, int64_t, float*, int8_t*, float*,
+                            float*, float*, int*, float*, void*) {
+    return GSB_ERR_UNSUPPORTED;
+}
+
+// ---- native ---------------------------------------------------------------------------
+
+size_t gsb_prepack_bytes(int experts, int rows, int cols) {
+    if (experts <= 0 || rows <= 0 || cols <= 0 || rows % 32 || cols % 512) return 0;
+    return (size_t)experts * (rows / 32) * (cols / 512) * kChunkBytes;
+}
+
+int gsb_prepack_gate_up(const uint8_t* gate_q, const void* gate_sc, const uint8_t* up_q,
+                        const void* up_sc, int scales_f32, int experts, int inter, int hidden,
+                        int group, void* out, void* stream) {
+    if (!gate_q || !gate_sc || !up_q || !up_sc || !out) return GSB_ERR_INVALID_ARG;
+    if (group != 128 || experts <= 0 || inter % 16 || hidden % 512) return GSB_ERR_UNSUPPORTED;
+    if (!aligned(out, 16) || !aligned(gate_q, 4) || !aligned(up_q, 4)) return GSB_ERR_INVALID_ARG;
+    return launch_prepack(gate_q, gate_sc, up_q, up_sc, scales_f32, experts, inter, hidden, out,
+                          as_stream(stream));
+}
+
+int gsb_prepack_down(const uint8_t* down_q, const void* down_sc, int scales_f32, int experts,
+                     int hidden, int inter, int group, void* out, void* stream) {
+    if (!down_q || !down_sc || !out) return GSB_ERR_INVALID_ARG;
+    if (group != 128 || experts <= 0 || hidden % 32 || inter % 512) return GSB_ERR_UNSUPPORTED;
+    if (!aligned(out, 16) || !aligned(down_q, 4)) return GSB_ERR_INVALID_ARG;
+    return launch_prepack(down_q, down_sc, nullptr, nullptr, scales_f32, experts, hidden, inter, out,
+                          as_stream(stream));
+}
+
+int gsb_moe_layer_create(const gsb_moe_config* cfg, gsb_moe_layer** out) {
+    if (!cfg || !out) return GSB_ERR_INVALID_ARG;
+    const gsb_moe_config& c = *cfg;
+    if (c.hidden <= 0 || c.n_experts <= 0 || c.topk <= 0 || c.moe_inter <= 0 || c.group <= 0 ||
+        c.shared_inter < 0)
+        return GSB_ERR_INVALID_ARG;
+    if (c.topk > c.n_experts || c.n_experts > 1024 || c.topk > 32) return GSB_ERR_UNSUPPORTED;
+    if (c.hidden % c.group || c.moe_inter % c.group || c.hidden % 8 || c.moe_inter % 8 || c.group % 8)
+        return GSB_ERR_UNSUPPORTED;
+    if (c.shared_inter && (c.shared_inter % c.group || c.shared_inter % 8)) return GSB_ERR_UNSUPPORTED;
+    if (!c.router_w) return GSB_ERR_INVALID_ARG;
+    const bool raw = c.gate_q && c.gate_sc && c.up_q && c.up_sc && c.down_q && c.down_sc;
+    const bool tiles = tile_shapes_ok(c);
+    if (!raw && !tiles) return GSB_ERR_INVALID_ARG;
+    if (c.shared_inter && !tiles && !(c.sg_q && c.sg_sc && c.su_q && c.su_sc && c.sd_q && c.sd_sc))
+        return GSB_ERR_INVALID_ARG;
+    gsb_moe_layer* L = new (std::nothrow) gsb_moe_layer();
+    if (!L) return GSB_ERR_CUDA;
+    L->cfg = c;
+    L->tiles_ok = tiles;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess)
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    L->sm_count = sms > 0 ? sms : 148;
+    *out = L;
+    return GSB_OK;
+}
+
+void gsb_moe_layer_destroy(gsb_moe_layer* layer) {
+    if (!layer) return;
+    gsb_moe_layer_profile_enable(layer, 0);
+    delete layer;
+}
+
+size_t gsb_moe_workspace_bytes(const gsb_moe_layer* layer, int n_tokens) {
+    if (!layer || n_tokens < 0) return 0;
+    return carve(layer->cfg, n_tokens, nullptr).total;
+}
+
+int gsb_router_logits(const void* x_bf16, const void* router_w_bf16, int n, int hidden, int E,
+                      float* logits, void* stream) {
+    if (n < 0 || hidden <= 0 || E <= 0) return GSB_ERR_INVALID_ARG;
+    if (n == 0) return GSB_OK;
+    if (!x_bf16 || !router_w_bf16 || !logits || !aligned(x_bf16, 16) || !aligned(router_w_bf16, 16))
+        return GSB_ERR_INVALID_ARG;
+    return launch_router_logits(reinterpret_cast<const __nv_bfloat16*>(x_bf16),
+                                reinterpret_cast<const __nv_bfloat16*>(router_w_bf16), n, hidden, E,
+                                logits, as_stream(stream));
+}
+
+int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float* out,
+                          void* workspace, size_t workspace_bytes, int path, float* logits_out,
+                          int* ids_out, float* weights_out, void* stream) {
+    if (!layer || n < 0) return GSB_ERR_INVALID_ARG;
+    if (n == 0) return GSB_OK;
+    if (!x_bf16 || !out || !workspace || !aligned(workspace, 256) || !aligned(x_bf16, 16))
+        return GSB_ERR_INVALID_ARG;
+    const gsb_moe_config& c = layer->cfg;
+    Workspace ws = carve(c, n, workspace);
+    if (workspace_bytes < ws.total) return GSB_ERR_WORKSPACE;
+    cudaStream_t s = as_stream(stream);
+    cudaEvent_t* ev = nullptr;
+    if (layer->prof_ev && layer->prof_used < layer->prof_sets)
+        ev = layer->prof_ev + (size_t)(layer->prof_used++) * (GSB_N_STAGES + 1);
+    auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], s); };
+    mark(0);
+    if (path == GSB_PATH_AUTO) path = layer->tiles_ok ? GSB_PATH_DECODE : GSB_PATH_DIRECT;
+    if ((path == GSB_PATH_DECODE || path == GSB_PATH_PREFILL) && !layer->tiles_ok)
+        return GSB_ERR_UNSUPPORTED;
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
+
+    int st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden,
+                                  c.n_experts, ws.logits, s);
+    if (st) return st;
+    st = launch_router_topk(ws.logits, c.e_bias, n, c.n_experts, c.topk, c.norm_topk,
+                            c.routed_scale, ws.ids, ws.w, s);
+    if (st) return st;
+    if (logits_out && cudaMemcpyAsync(logits_out, ws.logits, (size_t)n * c.n_experts * sizeof(float),
+                                      cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+        return GSB_ERR_CUDA;
+    if (ids_out && cudaMemcpyAsync(ids_out, ws.ids, (size_t)n * c.topk * sizeof(int),
+                                   cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+        return GSB_ERR_CUDA;
+    if (weights_out && cudaMemcpyAsync(weights_out, ws.w, (size_t)n * c.topk * sizeof(float),
+                                       cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+        return GSB_ERR_CUDA;
+
+    mark(1);
+    if (path == GSB_PATH_DIRECT) {
+        if (!(c.gate_q && c.gate_sc && c.up_q && c.up_sc && c.down_q && c.down_sc))
+            return GSB_ERR_UNSUPPORTED;
+        GenericExpertArgs a{};
+        a.x = x; a.ids = ws.ids; a.w = ws.w;
+        a.gate = c.gate_q; a.gate_sc = c.gate_sc; a.up = c.up_q; a.up_sc = c.up_sc;
+        a.down = c.down_q; a.down_sc = c.down_sc;
+        if (c.shared_inter) {
+            if (!(c.sg_q && c.sg_sc && c.su_q && c.su_sc && c.sd_q && c.sd_sc)) return GSB_ERR_UNSUPPORTED;
+            a.sg = c.sg_q; a.sg_sc = c.sg_sc; a.su = c.su_q; a.su_sc = c.su_sc;
+            a.sd = c.sd_q; a.sd_sc = c.sd_sc;
+        }
+        a.n = n; a.topk = c.topk; a.H = c.hidden; a.I = c.moe_inter; a.Is = c.shared_inter;
+        a.E = c.n_experts; a.group = c.group; a.out = out;
+        mark(2);
+        st = launch_generic_expert(a, 1, 1, true, s);
+        mark(3); mark(4); mark(5);
+        return st;
+    }
+
+    st = launch_dispatch(ws.ids, n, c.topk, c.n_experts, ws.expert_offsets, ws.sorted_tok,
+                         ws.sorted_row, ws.slot_pos, s);
+    if (st) return st;
+    if (path == GSB_PATH_DECODE) {
+        DecodeArgs d{};
+        d.x = x; d.n = n; d.topk = c.topk; d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter;
+        d.E = c.n_experts;
+        d.gate_up_packed = c.gate_up_packed; d.down_packed = c.down_packed;
+        d.shared_gate_up_packed = c.shared_gate_up_packed; d.shared_down_packed = c.shared_down_packed;
+        d.expert_offsets = ws.expert_offsets; d.sorted_tok = ws.sorted_tok; d.slot_pos = ws.slot_pos;
+        d.topk_w = ws.w; d.segs = ws.segs; d.xp = ws.xp; d.hbuf = ws.hbuf; d.ybuf = ws.ybuf;
+        d.status = ws.status; d.out = out; d.sm_count = layer->sm_count;
+        if (ev) { d.ev_prep = ev[2]; d.ev_gate_up = ev[3]; d.ev_down = ev[4]; }
+        st = launch_decode_layer(d, s);
+        mark(5);
+        return st;
+    }
+    return GSB_ERR_UNSUPPORTED;
+}
+
+int gsb_moe_block_layer_forward(gsb_moe_layer* layer, float* hidden, const float* norm_w, float eps,
+                                int n, void* workspace, size_t workspace_bytes, int path,
+                                int* ids_out, void* stream) {
+    if (!layer || n < 0) return GSB_ERR_INVALID_ARG;
+    if (n == 0) return GSB_OK;
+    if (!hidden || !norm_w || !workspace || !aligned(workspace, 256)) return GSB_ERR_INVALID_ARG;
+    const gsb_moe_config& c = layer->cfg;
+    Workspace ws = carve(c, n, workspace);
+    if (workspace_bytes < ws.total) return GSB_ERR_WORKSPACE;
+    cudaStream_t s = as_stream(stream);
+    int st = launch_rmsnorm_bf16(hidden, norm_w, ws.xnorm, n, c.hidden, eps, s);
+    if (st) return st;
+    st = gsb_moe_layer_forward(layer, ws.xnorm, n, ws.mlp, workspace, workspace_bytes, path, nullptr,
+                               ids_out, nullptr, stream);
+    if (st) return st;
+    return launch_add_inplace(hidden, ws.mlp, (int64_t)n * c.hidden, s);
+}
+
+int gsb_moe_layer_profile_enable(gsb_moe_layer* layer, int max_forwards) {
+    if (!layer || max_forwards < 0) return GSB_ERR_INVALID_ARG;
+    if (layer->prof_ev) {
+        for (int i = 0; i < layer->prof_sets * (GSB_N_STAGES + 1); ++i) cudaEventDestroy(layer->prof_ev[i]);
+        delete[] layer->prof_ev;
+        layer->prof_ev = nullptr;
+    }
+    layer->prof_sets = layer->prof_used = 0;
+    if (max_forwards == 0) return GSB_OK;
+    const int total = max_forwards * (GSB_N_STAGES + 1);
+    layer->prof_ev = new (std::nothrow) cudaEvent_t[total];
+    if (!layer->prof_ev) return GSB_ERR_CUDA;
+    for (int i = 0; i < total; ++i)
+        if (cudaEventCreate(&layer->prof_ev[i]) != cudaSuccess) return GSB_ERR_CUDA;
+    layer->prof_sets = max_forwards;
+    return GSB_OK;
+}
+
+int gsb_moe_layer_profile_read(gsb_moe_layer* layer, float* stage_ms, int* n_forwards) {
+    if (!layer || !stage_ms) return GSB_ERR_INVALID_ARG;
+    for (int i = 0; i < GSB_N_STAGES; ++i) stage_ms[i] = 0.f;
+    const int n = layer->prof_used;
+    for (int f = 0; f < n; ++f) {
+        cudaEvent_t* ev = layer->prof_ev + (size_t)f * (GSB_N_STAGES + 1);
+        for (int i = 0; i < GSB_N_STAGES; ++i) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, ev[i], ev[i + 1]) != cudaSuccess) return GSB_ERR_CUDA;
+            stage_ms[i] += ms;
+        }
+    }
+    if (n > 0) for (int i = 0; i < GSB_N_STAGES; ++i) stage_ms[i] /= (float)n;
+    if (n_forwards) *n_forwards = n;
+    layer->prof_used = 0;
+    return GSB_OK;
+}
+
+int gsb_moe_layer_status(gsb_moe_layer* layer, void* workspace) {
+    if (!layer || !workspace) return GSB_ERR_INVALID_ARG;
+    int host[4] = {0, 0, 0, 0};
+    if (cudaMemcpy(host, workspace, sizeof(host), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return GSB_ERR_CUDA;
+    if (host[0] != 0) {
+        cudaMemset(workspace, 0, 64 * sizeof(int));
+        return GSB_ERR_TIMEOUT;
+    }
+    return GSB_OK;
+}
+
+}  // extern "C"

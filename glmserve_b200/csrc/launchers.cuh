@@ -1,0 +1,86 @@
+// Host-callable launch functions shared between translation units.
+#pragma once
+#include "common.cuh"
+
+namespace gsb {
+
+// ---- tile-stream ("prepacked") weight format ------------------------------------------
+// A matrix set is experts x units x chunks.  A unit is 32 weight rows (gate/up: gate rows
+// 16u..16u+15 then up rows 16u..16u+15; down: rows 32u..32u+31); a chunk covers 512 input
+// columns of one unit: eight 1 KiB weight blocks (block b = kstep*2 + half_unit, kstep = 128
+// columns) followed by 256 bytes of fp16 scales [kstep][half_unit][16 rows].  Inside a
+// block, lane L = 4*g + t of a warp owns 16 bytes at [L*16] (row g) and at [512 + L*16]
+// (row g+8): the 32 columns 32t..32t+31 of the kstep as four words; in each word the eight
+// nibbles hold columns (k0,k2,k4,k6,k1,k3,k5,k7) so that masking with 0x000f000f /
+// 0x00f000f0 yields fp16 pairs of adjacent columns.
+constexpr int kChunkCols = 512;
+constexpr int kChunkWeightBytes = 8192;
+constexpr int kChunkBytes = 8448;
+constexpr int kDecodeTokens = 8;  // token rows per work item of the decode kernels
+
+int launch_router_topk(const float* logits, const float* e_bias, int n, int E, int topk,
+                       int norm_topk, float routed_scale, int* ids, float* w, cudaStream_t s);
+int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n, int H, int E,
+                         float* logits, cudaStream_t s);
+int launch_dispatch(const int* topk_ids, int n, int topk, int E, int* expert_offsets,
+                    int* sorted_token_ids, int* sorted_row, int* slot_pos, cudaStream_t s);
+
+struct GenericExpertArgs {
+    const void* x;
+    const int* ids;
+    const float* w;
+    const void* gate;
+    const void* gate_sc;
+    const void* up;
+    const void* up_sc;
+    const void* down;
+    const void* down_sc;
+    const uint8_t* sg; const void* sg_sc; const uint8_t* su; const void* su_sc;
+    const uint8_t* sd; const void* sd_sc;
+    int n, topk, H, I, Is, E, group;
+    float* out;
+};
+int launch_generic_expert(const GenericExpertArgs& a, int xt, int st, bool w4, cudaStream_t s);
+int launch_generic_gemm_w4(const float* x, const uint8_t* qW, const float* scales,
+                           const float* bias, float* y, int64_t n, int64_t in, int64_t out,
+                           int64_t group, cudaStream_t s);
+int launch_silu_mul(const float* g, const float* u, float* out, int64_t n, cudaStream_t s);
+int launch_add_inplace(float* y, const float* x, int64_t n, cudaStream_t s);
+int launch_rmsnorm_f32(const float* x, const float* w, float* out, int64_t n, int64_t d, float eps,
+                       cudaStream_t s);
+int launch_rmsnorm_bf16(const float* x, const float* w, __nv_bfloat16* out, int64_t n, int64_t d,
+                        float eps, cudaStream_t s);
+int launch_quantize_act_q8(const float* x, int64_t n, int64_t in, int8_t* xq, float* xs,
+                           cudaStream_t s);
+int launch_f32_to_bf16(const float* x, __nv_bfloat16* y, int64_t n, cudaStream_t s);
+
+// b == nullptr: one matrix [experts, rows, cols] in units of 32 rows; else two matrices
+// a (gate) and b (up), each [experts, rows, cols], interleaved 16 + 16 rows per unit.
+int launch_prepack(const uint8_t* a_q, const void* a_sc, const uint8_t* b_q, const void* b_sc,
+                   int scales_f32, int experts, int rows, int cols, void* out, cudaStream_t s);
+
+size_t decode_seg_bytes(int n, int topk, int E);
+
+struct DecodeArgs {
+    const __nv_bfloat16* x;
+    int n, topk, H, I, Is, E;
+    const void* gate_up_packed;
+    const void* down_packed;
+    const void* shared_gate_up_packed;
+    const void* shared_down_packed;
+    const int* expert_offsets;
+    const int* sorted_tok;
+    const int* slot_pos;
+    const float* topk_w;
+    int* segs;
+    __half* xp;
+    __half* hbuf;
+    float* ybuf;
+    int* status;
+    float* out;
+    int sm_count;
+    cudaEvent_t ev_prep, ev_gate_up, ev_down;  // optional stage marks (null = none)
+};
+int launch_decode_layer(const DecodeArgs& a, cudaStream_t s);
+
+}  // namespace gsb

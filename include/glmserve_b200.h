@@ -1,0 +1,257 @@
+/*
+ * glmserve_b200 - C ABI of the B200 (sm_100a) W4A16 MoE layer path.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns an int
+ * status (GSB_OK = 0) and never throws or aborts.  All data pointers are DEVICE pointers
+ * unless a parameter says "host".  `stream` is a cudaStream_t passed as void* (NULL = the
+ * legacy default stream, which is what the reference engine uses for every kernel).
+ * Nothing here allocates device memory unless its comment says so: weights, activations
+ * and scratch belong to the caller, as in the reference (src/model_gpu.cpp:578-645).
+ *
+ * Two families:
+ *   1. "operator" entry points - the reference's own launch wrappers from
+ *      cuda/kernels.cuh (namespace glmserve::cuda), same parameter lists and meaning;
+ *      include/glmserve_cuda_shim.cuh re-creates those C++ names on top of them so that
+ *      src/model_gpu.cpp of the reference compiles and links unchanged.
+ *   2. "native" entry points - bf16 activations, fp16 scales, weights prepacked once into
+ *      the tile-stream layout the sm_100a kernels read; one call runs the whole layer.
+ */
+#ifndef GLMSERVE_B200_H
+#define GLMSERVE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GSB_API __attribute__((visibility("default")))
+
+enum {
+    GSB_OK = 0,
+    GSB_ERR_INVALID_ARG = 1, /* null pointer, negative size, misaligned buffer, bad shape */
+    GSB_ERR_UNSUPPORTED = 2, /* shape or format outside what the kernels implement */
+    GSB_ERR_LAUNCH = 3,      /* cudaGetLastError() after the launch was not cudaSuccess */
+    GSB_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up (status word set) */
+    GSB_ERR_CUDA = 5,        /* another CUDA runtime call failed */
+    GSB_ERR_WORKSPACE = 6    /* caller scratch smaller than gsb_moe_workspace_bytes() */
+};
+
+/* Text for a status code (static storage). */
+GSB_API const char* gsb_status_string(int status);
+/* Library version and the architecture it was compiled for ("sm_100a"). */
+GSB_API const char* gsb_build_info(void);
+
+/* ------------------------------------------------------------------------------------
+ * 1. Operator entry points (drop-in for cuda/kernels.cuh of the reference)
+ * ---------------------------------------------------------------------------------- */
+
+/* Replaces moe_router (cuda/kernels.cuh:243-245, cuda/moe_router.cu:17-79).
+ * logits f32 [n,E]; e_bias f32 [E] or NULL; outputs topk_ids i32 [n,topk] in descending
+ * order of (sigmoid(logit)+bias), ties to the smaller expert id, topk_weights f32 [n,topk]
+ * = sigmoid scores, divided by their sum (in selection order) when norm_topk, times
+ * routed_scale.  E <= 1024, topk <= 32, topk <= E.  The sigmoid is evaluated so that the
+ * ids equal the CPU reference's (src/model_glm52.cpp:1113-1129) bit for bit. */
+GSB_API int gsb_moe_router(const float* logits, const float* e_bias, int n, int E, int topk,
+                           int norm_topk, float routed_scale, int* topk_ids,
+                           float* topk_weights, void* stream);
+
+/* Replaces moe_dispatch (cuda/kernels.cuh:249-250, cuda/moe_dispatch.cu:16-45): stable
+ * counting sort of the flat slots i = t*topk + k by expert.  expert_offsets i32 [E+1],
+ * sorted_token_ids / sorted_row i32 [n*topk].  Warp histograms + prefix scan; the order
+ * inside an expert segment is increasing i (no atomics decide any position).
+ * Ids outside [0,E) are a caller error; they are counted in no segment. */
+GSB_API int gsb_moe_dispatch(const int* topk_ids, int n, int topk, int E, int* expert_offsets,
+                             int* sorted_token_ids, int* sorted_row, void* stream);
+
+/* Replaces moe_expert_ffn_w4a16 (cuda/kernels.cuh:259-268, cuda/moe_expert.cu:132-244).
+ * x f32 [n,hidden]; gate_q/up_q u8 [E,moe_inter,hidden/2], gate_sc/up_sc f32
+ * [E,moe_inter,hidden/group]; down_q u8 [E,hidden,moe_inter/2], down_sc f32
+ * [E,hidden,moe_inter/group]; out f32 [n,hidden] is OVERWRITTEN with
+ * sum_k w[t,k] * down(silu(gate x) * up x), slots added in order k = 0..topk-1.
+ * hidden and moe_inter must be even and multiples of group. */
+GSB_API int gsb_moe_expert_ffn_w4a16(const float* x, const int* topk_ids,
+                                     const float* topk_weights, const uint8_t* gate_q,
+                                     const float* gate_sc, const uint8_t* up_q,
+                                     const float* up_sc, const uint8_t* down_q,
+                                     const float* down_sc, int n, int topk, int hidden,
+                                     int moe_inter, int E, int group_size, float* out,
+                                     void* stream);
+
+/* Replaces moe_expert_ffn (cuda/kernels.cuh:254-257, cuda/moe_expert.cu:32-130): the same
+ * with fp32 weights gate_w/up_w [E,moe_inter,hidden], down_w [E,hidden,moe_inter]. */
+GSB_API int gsb_moe_expert_ffn(const float* x, const int* topk_ids, const float* topk_weights,
+                               const float* gate_w, const float* up_w, const float* down_w,
+                               int n, int topk, int hidden, int moe_inter, int E, float* out,
+                               void* stream);
+
+/* Replaces gemm_w4a16 (cuda/kernels.cuh:48-52, cuda/int4_gemm.cu:15-48):
+ * y[n,out] = x[n,in] W[out,in]^T (+ bias), W = (nibble-8)*scales[out, in/group]. */
+GSB_API int gsb_gemm_w4a16(const float* x, const uint8_t* qW, const float* scales,
+                           const float* bias, float* y, int64_t n, int64_t in, int64_t out,
+                           int64_t group_size, void* stream);
+
+/* Replace silu_mul / add_inplace / rmsnorm (cuda/kernels.cuh:18-19, :282-283), the glue the
+ * reference runs around the shared expert and the residual (src/model_gpu.cpp:1430,
+ * :1486-1502).  rmsnorm sums squares in double like the CPU reference. */
+GSB_API int gsb_silu_mul(const float* g, const float* u, float* out, int64_t n, void* stream);
+GSB_API int gsb_add_inplace(float* y, const float* x, int64_t n, void* stream);
+GSB_API int gsb_rmsnorm(const float* x, const float* w, float* out, int64_t n, int64_t d,
+                        float eps, void* stream);
+
+/* The GGML-block-quant ("qgemm") family of cuda/kernels.cuh:59-136.  The entry points and
+ * their scratch contract exist so the reference's caller links; the GGML codecs are a
+ * different weight format and every qtype reports GSB_ERR_UNSUPPORTED, except
+ * gsb_quantize_act_q8 (cuda/qgemm.cu:569-587: per-32 absmax int8 activations), which is
+ * format independent and implemented. */
+GSB_API int gsb_qtype_has_i8(uint32_t qtype);
+GSB_API int gsb_quantize_act_q8(const float* x, int64_t n, int64_t in, int8_t* xq, float* xs,
+                                void* stream);
+GSB_API int gsb_gemm_q(uint32_t qtype, const float* x, const uint8_t* qW, const float* bias,
+                       float* y, int64_t n, int64_t in, int64_t out, int64_t row_bytes,
+                       void* stream);
+GSB_API int gsb_gemm_q_i8(uint32_t qtype, const int8_t* xq, const float* xs, const uint8_t* qW,
+                          const float* bias, float* y, int64_t n, int64_t in, int64_t out,
+                          int64_t row_bytes, void* stream);
+GSB_API int gsb_moe_expert_ffn_q(uint32_t gate_type, uint32_t up_type, uint32_t down_type,
+                                 const float* x, const int* topk_ids, const float* topk_w,
+                                 const uint8_t* gate_q, const uint8_t* up_q,
+                                 const uint8_t* down_q, int n, int topk, int hidden,
+                                 int moe_inter, int E, int64_t gate_row_bytes,
+                                 int64_t up_row_bytes, int64_t down_row_bytes, float* h_act,
+                                 float* dpart, float* out, int* dispatch, float* gu_part,
+                                 void* stream);
+GSB_API int gsb_moe_expert_ffn_q_i8(uint32_t gate_type, uint32_t up_type, uint32_t down_type,
+                                    const int8_t* xq, const float* xs, const int* topk_ids,
+                                    const float* topk_w, const uint8_t* gate_q,
+                                    const uint8_t* up_q, const uint8_t* down_q, int n,
+                                    int topk, int hidden, int moe_inter, int E,
+                                    int64_t gate_row_bytes, int64_t up_row_bytes,
+                                    int64_t down_row_bytes, float* h_act, int8_t* hq,
+                                    float* hs, float* dpart, float* out, int* dispatch,
+                                    float* gu_part, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * 2. Native entry points
+ * ---------------------------------------------------------------------------------- */
+
+/* Size in bytes of one prepacked matrix set: `experts` matrices of [rows, cols] int4 with
+ * one fp16 scale per 128 columns.  rows % 32 == 0 and cols % 512 == 0 are required
+ * (returns 0 otherwise). */
+GSB_API size_t gsb_prepack_bytes(int experts, int rows, int cols);
+
+/* One-time repack of resident int4 weights (the layout src/model_gpu.cpp:948-1000 uploads)
+ * into the tile stream the sm_100a kernels read.  Call where the reference concatenates the
+ * experts at upload time.  scales_f32 != 0: scales are float32 (reference layout), else
+ * fp16.  group must be 128.
+ *   gate/up: matrices [experts, inter, hidden]; unit u holds gate rows 16u..16u+15 then up
+ *            rows 16u..16u+15, so SwiGLU needs no second pass.  Output size
+ *            gsb_prepack_bytes(experts, 2*inter, hidden).
+ *   down:    matrices [experts, hidden, inter]; unit u holds rows 32u..32u+31.  Output size
+ *            gsb_prepack_bytes(experts, hidden, inter). */
+GSB_API int gsb_prepack_gate_up(const uint8_t* gate_q, const void* gate_sc, const uint8_t* up_q,
+                                const void* up_sc, int scales_f32, int experts, int inter,
+                                int hidden, int group, void* out, void* stream);
+GSB_API int gsb_prepack_down(const uint8_t* down_q, const void* down_sc, int scales_f32,
+                             int experts, int hidden, int inter, int group, void* out,
+                             void* stream);
+
+/* Static description of one MoE layer.  All pointers are device pointers owned by the
+ * caller and must outlive the layer object.  Counterpart of the expert fields of DLayer
+ * (src/model_gpu.cpp:499-524). */
+typedef struct gsb_moe_config {
+    int hidden;              /* H */
+    int n_experts;           /* E routed experts resident on this GPU */
+    int topk;                /* k */
+    int moe_inter;           /* I (per-expert intermediate, already /tp under TP) */
+    int shared_inter;        /* Is, 0 = no shared expert */
+    int group;               /* int4 group size along the input dim */
+    int norm_topk;           /* normalise the top-k weights */
+    float routed_scale;      /* routed_scaling_factor */
+    const void* router_w;    /* bf16 [E_global, H] */
+    const float* e_bias;     /* f32 [E_global] or NULL */
+    /* raw resident layout (any shape the quantiser allows); scales fp16 */
+    const uint8_t* gate_q;   /* [E, I, H/2] */
+    const void* gate_sc;     /* fp16 [E, I, H/group] */
+    const uint8_t* up_q;
+    const void* up_sc;
+    const uint8_t* down_q;   /* [E, H, I/2] */
+    const void* down_sc;     /* fp16 [E, H, I/group] */
+    const uint8_t* sg_q;     /* shared expert [Is, H/2] etc., NULL when shared_inter == 0 */
+    const void* sg_sc;
+    const uint8_t* su_q;
+    const void* su_sc;
+    const uint8_t* sd_q;     /* [H, Is/2] */
+    const void* sd_sc;
+    /* prepacked tile streams (gsb_prepack_*), or NULL: then only the direct-layout kernels
+     * can run and shapes the fast kernels need report GSB_ERR_UNSUPPORTED in "fast" mode */
+    const void* gate_up_packed;
+    const void* down_packed;
+    const void* shared_gate_up_packed;
+    const void* shared_down_packed;
+} gsb_moe_config;
+
+typedef struct gsb_moe_layer gsb_moe_layer; /* opaque, host memory only */
+
+/* Creates the host-side plan (validates shapes, picks kernels by shape; allocates host
+ * memory only).  No counterpart in the reference: its per-call wrappers re-derive
+ * everything from arguments; a plan keeps the per-call host work to a few launches. */
+GSB_API int gsb_moe_layer_create(const gsb_moe_config* cfg, gsb_moe_layer** out);
+GSB_API void gsb_moe_layer_destroy(gsb_moe_layer* layer);
+
+/* Scratch the caller must provide for n tokens (256-byte aligned device memory);
+ * counterpart of Scratch::ensure (src/model_gpu.cpp:578-645). */
+GSB_API size_t gsb_moe_workspace_bytes(const gsb_moe_layer* layer, int n_tokens);
+
+/* Path selection for gsb_moe_layer_forward. */
+enum {
+    GSB_PATH_AUTO = 0,    /* by shape: direct-layout kernels for shapes the tile kernels do
+                             not cover, else decode-shaped or prefill-shaped tile kernels */
+    GSB_PATH_DIRECT = 1,  /* direct-layout SIMT kernels (any shape) */
+    GSB_PATH_DECODE = 2,  /* bandwidth-bound split-K tile-stream kernels */
+    GSB_PATH_PREFILL = 3  /* tcgen05 grouped GEMM */
+};
+
+/* The whole layer, replacing the MoE branch of run_layer_step (src/model_gpu.cpp:1446-1495):
+ * router GEMM -> router -> dispatch -> grouped gate/up + SwiGLU -> down -> shared expert ->
+ * deterministic combine (slots in order, shared last).  x bf16 [n,H]; out f32 [n,H]
+ * overwritten.  Optional outputs (NULL to skip): logits_out f32 [n,E], ids_out i32
+ * [n,topk], weights_out f32 [n,topk].  Asynchronous on `stream`; no host sync. */
+GSB_API int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float* out,
+                                  void* workspace, size_t workspace_bytes, int path,
+                                  float* logits_out, int* ids_out, float* weights_out,
+                                  void* stream);
+
+/* Pre-norm + layer + residual, the MLP half of run_layer_step
+ * (src/model_gpu.cpp:1430-1502): hidden f32 [n,H] <- hidden + moe(rmsnorm(hidden) as bf16).
+ * norm_w f32 [H].  Scratch: gsb_moe_workspace_bytes() covers it. */
+GSB_API int gsb_moe_block_layer_forward(gsb_moe_layer* layer, float* hidden,
+                                        const float* norm_w, float eps, int n, void* workspace,
+                                        size_t workspace_bytes, int path, int* ids_out,
+                                        void* stream);
+
+/* Stage entry points of the native path (what the reference's StageProf marks
+ * "moe.router", "moe.experts", "moe.shared" separate; src/model_gpu.cpp:1451-1493). */
+GSB_API int gsb_router_logits(const void* x_bf16, const void* router_w_bf16, int n, int hidden,
+                              int E, float* logits, void* stream);
+
+/* Stage profiler, the counterpart of the reference's StageProf (src/model_gpu.cpp:328-388):
+ * cudaEventRecord at stage marks on the forward's stream.  Stages, in order:
+ * "moe.router" (logits GEMM + top-k), "moe.dispatch" (permutation + activation staging),
+ * "moe.gate_up" (gate/up GEMM + SwiGLU, routed and shared), "moe.down", "moe.combine".
+ * enable() creates CUDA events for up to max_forwards forwards (0 = off; host resources
+ * only); read() - after the caller synchronised - averages the stage times in ms over the
+ * forwards recorded since the last read and starts over. */
+#define GSB_N_STAGES 5
+GSB_API int gsb_moe_layer_profile_enable(gsb_moe_layer* layer, int max_forwards);
+GSB_API int gsb_moe_layer_profile_read(gsb_moe_layer* layer, float* stage_ms, int* n_forwards);
+
+/* Reads (and clears) the device status word of the last forward on this layer after the
+ * caller synchronised the stream: GSB_OK or GSB_ERR_TIMEOUT.  Host call. */
+GSB_API int gsb_moe_layer_status(gsb_moe_layer* layer, void* workspace);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLMSERVE_B200_H */

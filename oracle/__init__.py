@@ -210,6 +210,11 @@ def ref():
     if _ref is None:
         _ref = C.CDLL(os.path.join(_HERE, "_ref", "libglmref.so"))
         _ref.ref_moe_mlp_w4.restype = C.c_double
+        _ref.ref_moe_run.restype = C.c_double
+        _ref.ref_moe_run.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        _ref.ref_moe_create.restype = C.c_void_p
+        _ref.ref_moe_destroy.argtypes = [C.c_void_p]
+        _ref.ref_moe_destroy.restype = None
     return _ref
 
 
@@ -255,3 +260,36 @@ def ref_moe_mlp_w4(x, L, active=None):
     if secs < 0:
         raise RuntimeError("reference moe_mlp failed (an inactive expert was routed to?)")
     return out, float(secs)
+
+
+class RefLayer:
+    """The reference's MoE layer with fp32 weights dequantised once (as after its load);
+    ``run`` calls GLM52Model::moe_mlp and returns (out, seconds inside moe_mlp)."""
+
+    def __init__(self, L, active=None):
+        a = _wargs(L)
+        rw = np.ascontiguousarray(L["router_w"], np.float32)
+        eb = _opt(L.get("e_bias"), np.float32)
+        act = _opt(active, np.uint8)
+        self.H = int(L["H"])
+        self._h = ref().ref_moe_create(self.H, int(L["I"]), int(L["Is"]), int(L["E"]), int(L["topk"]),
+                                       int(L["group"]), _ptr(rw), _ptr(eb), int(bool(L["norm_topk"])),
+                                       C.c_double(L["routed_scale"]), *[_ptr(t) for t in a], _ptr(act))
+        if not self._h:
+            raise RuntimeError("reference layer construction failed")
+
+    def run(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty((x.shape[0], self.H), np.float32)
+        secs = ref().ref_moe_run(self._h, _ptr(x), x.shape[0], _ptr(out))
+        if secs < 0:
+            raise RuntimeError("reference moe_mlp failed (an inactive expert was routed to?)")
+        return out, float(secs)
+
+    def close(self):
+        if self._h:
+            ref().ref_moe_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()

@@ -57,19 +57,26 @@ void ref_linear_forward(const float* w, const float* x, float* y, int64_t n, int
     linear_forward(L, x, y, n);
 }
 
-// Runs the reference's moe_mlp on int4 weights.  `active` (nullable, length E) marks the
-// experts that get dequantised fp32 weights; the others stay empty, so a caller that
-// knows the routing can keep GLM-scale memory bounded (an expert the router picks while
-// empty makes linear_forward throw, which is reported as -1).  Returns seconds spent
-// inside moe_mlp, or a negative value on failure.
+// A reference MoE layer kept alive across calls: GLM52Model + MoEMLP with fp32 weights
+// dequantised once (what the reference holds after load).
+struct RefLayer {
+    GLM52Model model;
+    MoEMLP m;
+    explicit RefLayer(const GLM52Config& cfg) : model(cfg) {}
+};
+
+// `active` (nullable, length E) marks the experts that get dequantised fp32 weights; the
+// others stay empty, so a caller that knows the routing can keep GLM-scale memory bounded
+// (an expert the router picks while empty makes linear_forward throw -> ref_moe_run
+// returns a negative value).  Returns NULL on failure.
 __attribute__((visibility("default")))
-double ref_moe_mlp_w4(const float* x, int n, int H, int I, int Is, int E, int topk, int group,
-                      const float* router_w, const float* e_bias, int norm_topk,
-                      double routed_scale, const uint8_t* gate_q, const float* gate_sc,
-                      const uint8_t* up_q, const float* up_sc, const uint8_t* down_q,
-                      const float* down_sc, const uint8_t* sg_q, const float* sg_sc,
-                      const uint8_t* su_q, const float* su_sc, const uint8_t* sd_q,
-                      const float* sd_sc, const uint8_t* active, float* out) {
+void* ref_moe_create(int H, int I, int Is, int E, int topk, int group, const float* router_w,
+                     const float* e_bias, int norm_topk, double routed_scale,
+                     const uint8_t* gate_q, const float* gate_sc, const uint8_t* up_q,
+                     const float* up_sc, const uint8_t* down_q, const float* down_sc,
+                     const uint8_t* sg_q, const float* sg_sc, const uint8_t* su_q,
+                     const float* su_sc, const uint8_t* sd_q, const float* sd_sc,
+                     const uint8_t* active) {
     try {
         GLM52Config cfg;
         cfg.hidden_size = H;
@@ -78,8 +85,8 @@ double ref_moe_mlp_w4(const float* x, int n, int H, int I, int Is, int E, int to
         cfg.moe_intermediate_size = I;
         cfg.routed_scaling_factor = routed_scale;
         cfg.norm_topk_prob = norm_topk != 0;
-        GLM52Model model(cfg);
-        MoEMLP m;
+        RefLayer* R = new RefLayer(cfg);
+        MoEMLP& m = R->m;
         m.router.out_features = E;
         m.router.in_features = H;
         m.router.w.assign(router_w, router_w + (size_t)E * H);
@@ -99,13 +106,46 @@ double ref_moe_mlp_w4(const float* x, int n, int H, int I, int Is, int E, int to
             m.shared.up_proj = make_linear(su_q, su_sc, Is, H, group);
             m.shared.down_proj = make_linear(sd_q, sd_sc, H, Is, group);
         }
+        return R;
+    } catch (const std::exception&) {
+        return nullptr;
+    }
+}
+
+// GLM52Model::moe_mlp on n token rows; returns the seconds spent inside it (< 0: failure).
+__attribute__((visibility("default")))
+double ref_moe_run(void* handle, const float* x, int n, float* out) {
+    RefLayer* R = static_cast<RefLayer*>(handle);
+    if (!R) return -1.0;
+    try {
         auto t0 = std::chrono::steady_clock::now();
-        model.moe_mlp(m, x, out, n);
+        R->model.moe_mlp(R->m, x, out, n);
         auto t1 = std::chrono::steady_clock::now();
         return std::chrono::duration<double>(t1 - t0).count();
     } catch (const std::exception&) {
         return -1.0;
     }
+}
+
+__attribute__((visibility("default")))
+void ref_moe_destroy(void* handle) { delete static_cast<RefLayer*>(handle); }
+
+// One-shot convenience: create, run, destroy.
+__attribute__((visibility("default")))
+double ref_moe_mlp_w4(const float* x, int n, int H, int I, int Is, int E, int topk, int group,
+                      const float* router_w, const float* e_bias, int norm_topk,
+                      double routed_scale, const uint8_t* gate_q, const float* gate_sc,
+                      const uint8_t* up_q, const float* up_sc, const uint8_t* down_q,
+                      const float* down_sc, const uint8_t* sg_q, const float* sg_sc,
+                      const uint8_t* su_q, const float* su_sc, const uint8_t* sd_q,
+                      const float* sd_sc, const uint8_t* active, float* out) {
+    void* h = ref_moe_create(H, I, Is, E, topk, group, router_w, e_bias, norm_topk, routed_scale,
+                             gate_q, gate_sc, up_q, up_sc, down_q, down_sc, sg_q, sg_sc, su_q, su_sc,
+                             sd_q, sd_sc, active);
+    if (!h) return -1.0;
+    const double secs = ref_moe_run(h, x, n, out);
+    ref_moe_destroy(h);
+    return secs;
 }
 
 }  // extern "C"

@@ -1,0 +1,133 @@
+"""Whole-layer parity of the native entry point against the CPU oracle: router ids and the
+dispatch permutation bit-exact, outputs within max-abs 2e-2 and relative-L2 1e-3."""
+import numpy as np
+import pytest
+
+import oracle
+from glmserve_b200.synth import (CONFIGS, layer_to_np, layer_to_torch, make_layer_np, make_layer_torch,
+                                 make_x_np, make_x_torch)
+from helpers import assert_layer_close, bf16_tensor, load_tiny
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def _check_layer(layer, Lnp, x_np, dev, path, what):
+    """Runs the layer, checks routing against the oracle's selection on the SAME logits
+    (bit-exact), the logits against the oracle's own (tolerance), and the output."""
+    from glmserve_b200 import ops
+    x = bf16_tensor(x_np, dev)
+    out, logits, ids, w = layer.forward(x, path=path, return_routing=True)
+    assert layer.status() == 0
+    logits = logits.cpu().numpy()
+    r = oracle.moe_layer_w4(x_np, Lnp, logits_in=logits)
+    assert r["ties"] == 0
+    assert np.array_equal(ids.cpu().numpy(), r["ids"]), f"{what}: router ids differ"
+    np.testing.assert_allclose(w.cpu().numpy(), r["w"], rtol=0, atol=1e-6)
+    own = oracle.moe_layer_w4(x_np[: min(len(x_np), 16)], Lnp)
+    np.testing.assert_allclose(logits[: len(own["logits"])], own["logits"], rtol=0, atol=2e-5)
+    flips = int((own["ids"] != r["ids"][: len(own["ids"])]).any(axis=1).sum())
+    ma, rl = assert_layer_close(out.cpu().numpy(), r["out"], what)
+    return dict(max_abs=ma, rel_l2=rl, flips=flips, out=out)
+
+
+def test_tiny_config_against_reference_golden(golden_dir, dev):
+    from glmserve_b200 import ops
+    L = load_tiny(golden_dir)
+    layer = ops.MoELayer(layer_to_torch(L, dev))
+    assert not layer.prepacked                      # group 32: direct-layout kernels
+    x = bf16_tensor(L["x"], dev)
+    out, logits, ids, w = layer.forward(x, return_routing=True)
+    # the golden output comes from the reference's own moe_mlp
+    assert np.array_equal(ids.cpu().numpy(), L["ids_numpy"])
+    assert_layer_close(out.cpu().numpy(), L["out_ref"], "tiny vs reference moe_mlp")
+    np.testing.assert_allclose(logits.cpu().numpy(), L["logits_ref"], rtol=0, atol=2e-5)
+
+
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 64, 200])
+def test_mid_config_decode_path(dev, n):
+    from glmserve_b200 import ops
+    L = make_layer_np(CONFIGS["mid"], seed=21)
+    layer = ops.MoELayer(layer_to_torch(L, dev))
+    assert layer.prepacked
+    x = make_x_np(n, L["H"], seed=n)
+    a = _check_layer(layer, L, x, dev, ops.PATH_DECODE, f"mid decode n={n}")
+    b = _check_layer(layer, L, x, dev, ops.PATH_DIRECT, f"mid direct n={n}")
+    # deterministic: a second run gives the same bits
+    out2 = layer.forward(bf16_tensor(x, dev), path=ops.PATH_DECODE)
+    assert torch.equal(out2, a["out"])
+
+
+def test_mid_config_without_shared_expert_and_skew(dev):
+    from glmserve_b200 import ops
+    L = make_layer_np(CONFIGS["mid"], seed=22, shared=False, zipf_amplitude=0.6)
+    layer = ops.MoELayer(layer_to_torch(L, dev))
+    x = make_x_np(96, L["H"], seed=5)
+    _check_layer(layer, L, x, dev, ops.PATH_DECODE, "mid no-shared skewed")
+
+
+def test_unsupported_path_is_reported(golden_dir, dev):
+    from glmserve_b200 import ops
+    from glmserve_b200._lib import GsbError
+    L = load_tiny(golden_dir)
+    layer = ops.MoELayer(layer_to_torch(L, dev))
+    with pytest.raises(GsbError) as e:
+        layer.forward(bf16_tensor(L["x"], dev), path=ops.PATH_DECODE)
+    assert e.value.status == 2
+
+
+@pytest.fixture(scope="module")
+def glm_layer(dev):
+    from glmserve_b200 import ops
+    Lt = make_layer_torch(CONFIGS["glm"], seed=1, device=dev)
+    layer = ops.MoELayer(Lt, keep_raw=False)
+    Lnp = layer_to_np(Lt)
+    del Lt
+    torch.cuda.empty_cache()
+    return layer, Lnp
+
+
+@pytest.mark.parametrize("n", [1, 8, 64])
+def test_glm_scale_decode(dev, glm_layer, n):
+    """GLM-scale layer (H=6144, E=256, top-8, I=2048, g=128) at decode batch sizes."""
+    from glmserve_b200 import ops
+    layer, Lnp = glm_layer
+    x = make_x_torch(n, 6144, seed=100 + n, device=dev)
+    x_np = x.float().cpu().numpy()
+    out, logits, ids, w = layer.forward(x, path=ops.PATH_DECODE, return_routing=True)
+    assert layer.status() == 0
+    r = oracle.moe_layer_w4(x_np, Lnp, logits_in=logits.cpu().numpy())
+    assert np.array_equal(ids.cpu().numpy(), r["ids"])
+    assert_layer_close(out.cpu().numpy(), r["out"], f"glm decode n={n}")
+    out2 = layer.forward(x, path=ops.PATH_DECODE)
+    assert torch.equal(out, out2)
+
+
+def test_block_of_layers_with_prenorm_and_residual(dev):
+    """Two chained layers h <- h + moe(rmsnorm(h)) (the speculative-verify block's shape,
+    scaled down)."""
+    from glmserve_b200 import ops
+    n, H = 32, CONFIGS["mid"]["H"]
+    rng = np.random.default_rng(9)
+    h_np = make_x_np(n, H, seed=77)
+    h = torch.from_numpy(h_np).to(dev)
+    for li in range(2):
+        L = make_layer_np(CONFIGS["mid"], seed=30 + li)
+        nw = (1.0 + 0.02 * rng.standard_normal(H)).astype(np.float32)
+        layer = ops.MoELayer(layer_to_torch(L, dev))
+        ids = torch.empty((n, L["topk"]), dtype=torch.int32, device=dev)
+        # oracle on the SAME input hidden state, routed with the GPU's logits
+        normed = oracle.rmsnorm_rows(h.cpu().numpy(), nw, 1e-5)
+        from glmserve_b200.quant import round_bf16_np
+        xb = round_bf16_np(normed)
+        logits = ops.router_logits(bf16_tensor(xb, dev), layer._keep["router_w"]).cpu().numpy()
+        want = h.cpu().numpy() + oracle.moe_layer_w4(xb, L, logits_in=logits)["out"]
+        layer.block_forward(h, torch.from_numpy(nw).to(dev), 1e-5, ids_out=ids)
+        assert layer.status() == 0
+        assert_layer_close(h.cpu().numpy(), want, f"block layer {li}")
