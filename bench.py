@@ -202,7 +202,7 @@ def run_ours(args) -> None:
             "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "w4a16 (int4 weights, fp16 mma, fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": f"GLM-scale decode MoE layer, T={T} tokens per GPU: hidden 6144, 256 routed "
+            "config": {"workload": f"GLM-scale decode MoE layer, T={T} tokens per GPU: hidden 6144, {GLM['E']} routed "
                                    "experts top-8, expert intermediate 2048, 1 shared expert, W4A16 group 128, "
                                    "fp16 scales, bf16 activations",
                        "multi_gpu": "independent replicas (tokens shard, no collective)" if world > 1 else "single GPU",
@@ -302,7 +302,10 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=16, help="token sample of the CPU baseline leg")
     ap.add_argument("--ref-tokens", type=int, default=4, help="token sample of --impl reference")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--experts", type=int, default=256,
+                    help="routed experts (256 = the benchmark layer; fewer = a small case for profiler captures)")
     args = ap.parse_args()
+    GLM["E"] = args.experts
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -41,6 +41,9 @@ struct Workspace {
     __half* xp;               // [n, H] fp16 activations in fragment order
     __half* hbuf;             // [P + n, Imax] fp16 SwiGLU output in fragment order
     float* ybuf;              // [P + n, H] per-slot down-projection rows
+    __half* xs;               // prefill: [P + n, H] fp16 activations in expert order
+    int* tiles_gu;            // prefill tile lists
+    int* tiles_dn;
     __nv_bfloat16* xnorm;     // [n, H] bf16 (block layer: rmsnorm output)
     float* mlp;               // [n, H] (block layer: layer output before the residual add)
     size_t total;
@@ -68,6 +71,9 @@ Workspace carve(const gsb_moe_config& c, int n, void* base) {
     ws.xp = reinterpret_cast<__half*>(take((size_t)n * c.hidden * sizeof(__half)));
     ws.hbuf = reinterpret_cast<__half*>(take((P + n) * imax * sizeof(__half)));
     ws.ybuf = reinterpret_cast<float*>(take((P + n) * (size_t)c.hidden * sizeof(float)));
+    ws.xs = reinterpret_cast<__half*>(take((P + n) * (size_t)c.hidden * sizeof(__half)));
+    ws.tiles_gu = reinterpret_cast<int*>(take(prefill_tile_bytes(n, c.topk, c.n_experts, c.hidden, (int)imax)));
+    ws.tiles_dn = reinterpret_cast<int*>(take(prefill_tile_bytes(n, c.topk, c.n_experts, c.hidden, (int)imax)));
     ws.xnorm = reinterpret_cast<__nv_bfloat16*>(take((size_t)n * c.hidden * sizeof(__nv_bfloat16)));
     ws.mlp = reinterpret_cast<float*>(take((size_t)n * c.hidden * sizeof(float)));
     ws.total = off;
@@ -348,6 +354,21 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
         d.status = ws.status; d.out = out; d.sm_count = layer->sm_count;
         if (ev) { d.ev_prep = ev[2]; d.ev_gate_up = ev[3]; d.ev_down = ev[4]; }
         st = launch_decode_layer(d, s);
+        mark(5);
+        return st;
+    }
+    if (path == GSB_PATH_PREFILL) {
+        PrefillArgs d{};
+        d.x = x; d.n = n; d.topk = c.topk; d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter;
+        d.E = c.n_experts;
+        d.gate_up_packed = c.gate_up_packed; d.down_packed = c.down_packed;
+        d.shared_gate_up_packed = c.shared_gate_up_packed; d.shared_down_packed = c.shared_down_packed;
+        d.expert_offsets = ws.expert_offsets; d.sorted_tok = ws.sorted_tok; d.slot_pos = ws.slot_pos;
+        d.topk_w = ws.w; d.tiles_gu = ws.tiles_gu; d.tiles_dn = ws.tiles_dn; d.xs = ws.xs;
+        d.hbuf = ws.hbuf; d.ybuf = reinterpret_cast<__half*>(ws.ybuf);
+        d.status = ws.status; d.out = out; d.sm_count = layer->sm_count;
+        if (ev) { d.ev_prep = ev[2]; d.ev_gate_up = ev[3]; d.ev_down = ev[4]; }
+        st = launch_prefill_layer(d, s);
         mark(5);
         return st;
     }

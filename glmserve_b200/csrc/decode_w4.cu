@@ -7,10 +7,12 @@
 //                    contiguous 1-D bulk copy each) into a shared-memory ring, completion
 //                    on mbarriers, running ahead across item boundaries
 //   warps 1..16      consumers: each owns one (128-column kstep, half unit) of every stage
-//                    = split-K across warps; unpacks int4 to exact fp16 integers in
-//                    registers, mma.sync m16n8k16 against the segment's fp16 activations
-//                    (held in shared memory), applies the fp16 group scale to the fp32
-//                    accumulator once per 128 columns
+//                    = split-K across warps.  A nibble n masked in place IS the fp16
+//                    subnormal n * 2^-24 (n * 2^-20 for the odd nibble), so unpacking is one
+//                    AND per fp16 pair; mma.sync m16n8k16 against the segment's fp16
+//                    activations (in shared memory) gives sum x*n exactly in fp32, and once
+//                    per 128 columns the zero point (-8 * sum x, from a per-segment table)
+//                    and the fp16 group scale are applied to the accumulator
 //   warps 17..20     epilogue: sums the 8 K-split partials of each half unit in fixed order,
 //                    fuses SwiGLU (gate/up kernel) and stores fp16 h, or stores the fp32
 //                    down-projection row of the slot (down kernel)
@@ -62,25 +64,42 @@ struct Item {
     int nchunk;
 };
 
-__device__ __forceinline__ Item decode_item(const DecodeKArgs& a, int64_t it, int nshared_seg) {
-    Item r;
-    const int64_t shared_items = (int64_t)nshared_seg * a.units_s;
-    bool sh = it < shared_items;
-    int64_t local = sh ? it : it - shared_items;
-    const int U = sh ? a.units_s : a.units;
-    r.seg = (int)(local / U) + (sh ? 0 : nshared_seg);
-    r.unit = (int)(local % U);
-    const int4 sg = reinterpret_cast<const int4*>(a.segs + kSegHeader)[r.seg];
-    r.expert = sg.x;
-    r.slot_begin = sg.y;
-    r.ntok = sg.z;
-    r.K = sh ? a.Ks : a.K;
-    r.nchunk = r.K / kChunkCols;
-    const uint8_t* base = sh ? a.shared_packed : a.packed;
-    const int64_t e_local = sh ? 0 : r.expert;
-    r.chunks = base + ((e_local * U + r.unit) * (int64_t)r.nchunk) * kChunkBytes;
-    return r;
-}
+// Walks the flat item list [shared segments x units_s | routed segments x units] without a
+// division per item: (segment, unit) advance incrementally, the segment record is re-read
+// only when the segment changes.
+struct ItemIter {
+    int seg, unit, U, nshared_seg;
+    int4 rec;
+    __device__ __forceinline__ void init(const DecodeKArgs& a, long long it, int nshared) {
+        nshared_seg = nshared;
+        const long long shared_items = (long long)nshared * a.units_s;
+        if (it < shared_items) { U = a.units_s; seg = (int)(it / U); unit = (int)(it - (long long)seg * U); }
+        else {
+            const long long l = it - shared_items;
+            U = a.units; const int sg = (int)(l / U); unit = (int)(l - (long long)sg * U); seg = sg + nshared;
+        }
+        rec = reinterpret_cast<const int4*>(a.segs + kSegHeader)[seg];
+    }
+    __device__ __forceinline__ void next(const DecodeKArgs& a) {
+        if (++unit == U) {
+            unit = 0;
+            ++seg;
+            if (seg == nshared_seg) U = a.units;
+            rec = reinterpret_cast<const int4*>(a.segs + kSegHeader)[seg];  // one past the end is padding
+        }
+    }
+    __device__ __forceinline__ Item get(const DecodeKArgs& a) const {
+        Item r;
+        const bool sh = seg < nshared_seg;
+        r.seg = seg; r.unit = unit; r.expert = rec.x; r.slot_begin = rec.y; r.ntok = rec.z;
+        r.K = sh ? a.Ks : a.K;
+        r.nchunk = r.K / kChunkCols;
+        const uint8_t* base = sh ? a.shared_packed : a.packed;
+        const long long e_local = sh ? 0 : rec.x;
+        r.chunks = base + ((e_local * U + unit) * (long long)r.nchunk) * kChunkBytes;
+        return r;
+    }
+};
 
 __device__ __forceinline__ void record_timeout(const DecodeKArgs& a, volatile int* abort_flag,
                                                int where) {
@@ -91,25 +110,16 @@ __device__ __forceinline__ void record_timeout(const DecodeKArgs& a, volatile in
     }
 }
 
-// eight int4 (one word, tile-stream nibble order) -> four fp16x2 of (q - 8), exact
-__device__ __forceinline__ void unpack8(uint32_t w, uint32_t& p01, uint32_t& p23, uint32_t& p45,
-                                        uint32_t& p67) {
-    const __half2 k1032 = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408));
-    const __half2 k16th = __halves2half2(__ushort_as_half(0x2C00), __ushort_as_half(0x2C00));
-    const __half2 km72 = __halves2half2(__ushort_as_half(0xD480), __ushort_as_half(0xD480));
-    uint32_t lo0 = (w & 0x000f000fu) | 0x64006400u;
-    uint32_t hi0 = (w & 0x00f000f0u) | 0x64006400u;
+// Eight int4 of one word (tile-stream nibble order) as fp16 SUBNORMAL bit patterns: a nibble n
+// left in bits 0..3 of a half is n * 2^-24, in bits 4..7 it is n * 2^-20.  lo* hold columns
+// (k0,k1) / (k4,k5), hi* hold (k2,k3) / (k6,k7).
+__device__ __forceinline__ void unpack8(uint32_t w, uint32_t& lo0, uint32_t& hi0, uint32_t& lo1,
+                                        uint32_t& hi1) {
+    lo0 = w & 0x000f000fu;
+    hi0 = w & 0x00f000f0u;
     const uint32_t w8 = w >> 8;
-    uint32_t lo1 = (w8 & 0x000f000fu) | 0x64006400u;
-    uint32_t hi1 = (w8 & 0x00f000f0u) | 0x64006400u;
-    __half2 a = __hsub2(*reinterpret_cast<__half2*>(&lo0), k1032);
-    __half2 b = __hfma2(*reinterpret_cast<__half2*>(&hi0), k16th, km72);
-    __half2 c = __hsub2(*reinterpret_cast<__half2*>(&lo1), k1032);
-    __half2 d = __hfma2(*reinterpret_cast<__half2*>(&hi1), k16th, km72);
-    p01 = *reinterpret_cast<uint32_t*>(&a);
-    p23 = *reinterpret_cast<uint32_t*>(&b);
-    p45 = *reinterpret_cast<uint32_t*>(&c);
-    p67 = *reinterpret_cast<uint32_t*>(&d);
+    lo1 = w8 & 0x000f000fu;
+    hi1 = w8 & 0x00f000f0u;
 }
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -147,7 +157,8 @@ decode_gemm_kernel(const DecodeKArgs a) {
     const int xstride = Kmax * 2 + kXPad;  // bytes per activation row in shared memory
     uint8_t* ring = smem;
     uint8_t* xs = ring + (size_t)nstage * kStageBytes;
-    float* red = reinterpret_cast<float*>(xs + (size_t)kDecodeTokens * xstride);
+    float* sx = reinterpret_cast<float*>(xs + (size_t)kDecodeTokens * xstride);  // [K/128][8] row sums
+    float* red = sx + (size_t)(Kmax >> 7) * kDecodeTokens;
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(red) + 2 * kRedBytes);
     uint64_t* full = bars;                      // [kMaxStages]
     uint64_t* empty = bars + kMaxStages;        // [kMaxStages]
@@ -168,16 +179,19 @@ decode_gemm_kernel(const DecodeKArgs a) {
 
     const int nseg = a.segs[0];
     const int nshared_seg = a.segs[1];
-    const int64_t total = (int64_t)nshared_seg * a.units_s + (int64_t)(nseg - nshared_seg) * a.units;
-    const int64_t it0 = total * blockIdx.x / gridDim.x;
-    const int64_t it1 = total * (blockIdx.x + 1) / gridDim.x;
+    const long long total = (long long)nshared_seg * a.units_s + (long long)(nseg - nshared_seg) * a.units;
+    const long long it0 = total * blockIdx.x / gridDim.x;
+    const long long it1 = total * (blockIdx.x + 1) / gridDim.x;
+    if (it0 >= it1) return;
+    ItemIter iter;
+    iter.init(a, it0, nshared_seg);
 
     if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
             uint32_t q = 0;
-            for (int64_t it = it0; it < it1 && !*abort_flag; ++it) {
-                const Item im = decode_item(a, it, nshared_seg);
+            for (long long it = it0; it < it1 && !*abort_flag; ++it, iter.next(a)) {
+                const Item im = iter.get(a);
                 for (int c0 = 0; c0 < im.nchunk; c0 += kStageChunks, ++q) {
                     const uint32_t slot = q % nstage, ph = (q / nstage) & 1u;
                     if (!mbar_wait(&empty[slot], ph ^ 1u, kWaitLimit)) { record_timeout(a, abort_flag, 1); break; }
@@ -194,11 +208,14 @@ decode_gemm_kernel(const DecodeKArgs a) {
         const int ck = cw >> 3, ks = (cw >> 1) & 3, m = cw & 1;
         const int g = lane >> 2, t = lane & 3;
         const int ctid = tid - 32;  // 0..511
+        const uint32_t w_off = (uint32_t)ck * kChunkBytes + (ks * 2 + m) * 1024 + lane * 16;
+        const uint32_t sc_off = (uint32_t)ck * kChunkBytes + kChunkWeightBytes + ((ks * 2 + m) * 16 + g) * 2;
+        const uint8_t* xlane = xs + (size_t)g * xstride + t * 16;
         uint32_t q = 0, xuse = 0, item_local = 0;
         int cur_seg = -1;
         bool dead = false;
-        for (int64_t it = it0; it < it1 && !dead; ++it, ++item_local) {
-            const Item im = decode_item(a, it, nshared_seg);
+        for (long long it = it0; it < it1 && !dead; ++it, ++item_local, iter.next(a)) {
+            const Item im = iter.get(a);
             if (im.seg != cur_seg) {
                 // every consumer is done with the previous segment's rows before they change
                 mbar_arrive(xbar);
@@ -207,7 +224,7 @@ decode_gemm_kernel(const DecodeKArgs a) {
                 const int vec_per_row = im.K >> 3;  // 16-byte pieces per row
                 for (int idx = ctid; idx < im.ntok * vec_per_row; idx += kConsumerWarps * 32) {
                     const int j = idx / vec_per_row, v = idx - j * vec_per_row;
-                    int64_t row;
+                    long long row;
                     if (GU) row = (im.slot_begin + j < a.P) ? a.sorted_tok[im.slot_begin + j] : (im.slot_begin + j - a.P);
                     else row = im.slot_begin + j;
                     const uint4 val = __ldg(reinterpret_cast<const uint4*>(a.bsrc + row * a.ldb) + v);
@@ -215,6 +232,26 @@ decode_gemm_kernel(const DecodeKArgs a) {
                 }
                 mbar_arrive(xbar);
                 if (!mbar_wait(xbar, xuse & 1u, kWaitLimit)) { record_timeout(a, abort_flag, 3); break; }
+                ++xuse;
+                // per (token, 128-column block) sums of the activations: the zero-point term
+                const int nkb = im.K >> 7;
+                for (int idx = ctid; idx < nkb * kDecodeTokens; idx += kConsumerWarps * 32) {
+                    const int n = idx & (kDecodeTokens - 1), kb = idx >> 3;
+                    float acc = 0.f;
+                    if (n < im.ntok) {
+                        const uint4* src = reinterpret_cast<const uint4*>(xs + (size_t)n * xstride + (size_t)kb * 256);
+#pragma unroll 4
+                        for (int v = 0; v < 16; ++v) {
+                            const uint4 u = src[v];
+                            const __half2* hp = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(hp[e]); acc += f.x; acc += f.y; }
+                        }
+                    }
+                    sx[idx] = acc;
+                }
+                mbar_arrive(xbar);
+                if (!mbar_wait(xbar, xuse & 1u, kWaitLimit)) { record_timeout(a, abort_flag, 7); break; }
                 ++xuse;
                 cur_seg = im.seg;
             }
@@ -227,30 +264,34 @@ decode_gemm_kernel(const DecodeKArgs a) {
                     break;
                 }
                 if (c0 + ck < im.nchunk) {
-                    const uint8_t* chunk = ring + (size_t)slot * kStageBytes + (size_t)ck * kChunkBytes;
-                    const uint8_t* blk = chunk + (ks * 2 + m) * 1024;
-                    const uint4 w0 = lds128(blk + lane * 16);
-                    const uint4 w1 = lds128(blk + 512 + lane * 16);
-                    const __half* sc = reinterpret_cast<const __half*>(chunk + kChunkWeightBytes) + (ks * 2 + m) * 16;
-                    const float s0 = __half2float(sc[g]), s1 = __half2float(sc[g + 8]);
+                    const uint8_t* stage = ring + (size_t)slot * kStageBytes;
+                    const uint4 w0 = lds128(stage + w_off);
+                    const uint4 w1 = lds128(stage + w_off + 512);
+                    const __half* sc = reinterpret_cast<const __half*>(stage + sc_off);
+                    const float s0 = __half2float(sc[0]), s1 = __half2float(sc[8]);
                     const int kb = (c0 + ck) * 4 + ks;  // 128-column block index along K
-                    const uint8_t* xrow = xs + (size_t)g * xstride + (size_t)kb * 256 + t * 16;
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    const float2 sxv = *reinterpret_cast<const float2*>(sx + kb * kDecodeTokens + 2 * t);
+                    const uint8_t* xrow = xlane + (size_t)kb * 256;
+                    float alo[4] = {0.f, 0.f, 0.f, 0.f}, ahi[4] = {0.f, 0.f, 0.f, 0.f};
                     const uint32_t wa[4] = {w0.x, w0.y, w0.z, w0.w};
                     const uint32_t wb[4] = {w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const uint4 xv = lds128(xrow + j * 64);
-                        uint32_t a01, a23, a45, a67, b01, b23, b45, b67;
-                        unpack8(wa[j], a01, a23, a45, a67);
-                        unpack8(wb[j], b01, b23, b45, b67);
-                        mma_16816(acc, a01, b01, a23, b23, xv.x, xv.y);
-                        mma_16816(acc, a45, b45, a67, b67, xv.z, xv.w);
+                        uint32_t al0, ah0, al1, ah1, bl0, bh0, bl1, bh1;
+                        unpack8(wa[j], al0, ah0, al1, ah1);
+                        unpack8(wb[j], bl0, bh0, bl1, bh1);
+                        // columns (k0,k1)+(k4,k5) carry weight n*2^-24, (k2,k3)+(k6,k7) carry n*2^-20
+                        mma_16816(alo, al0, bl0, al1, bl1, xv.x, xv.z);
+                        mma_16816(ahi, ah0, bh0, ah1, bh1, xv.y, xv.w);
                     }
-                    tot[0] = fmaf(s0, acc[0], tot[0]);
-                    tot[1] = fmaf(s0, acc[1], tot[1]);
-                    tot[2] = fmaf(s1, acc[2], tot[2]);
-                    tot[3] = fmaf(s1, acc[3], tot[3]);
+                    // sum x*(n-8) = 2^24*alo + 2^20*ahi - 8*sum(x); then the group scale
+                    const float s0a = s0 * 16777216.f, s0b = s0 * 1048576.f, s0c = s0 * -8.f;
+                    const float s1a = s1 * 16777216.f, s1b = s1 * 1048576.f, s1c = s1 * -8.f;
+                    tot[0] = fmaf(s0a, alo[0], fmaf(s0b, ahi[0], fmaf(s0c, sxv.x, tot[0])));
+                    tot[1] = fmaf(s0a, alo[1], fmaf(s0b, ahi[1], fmaf(s0c, sxv.y, tot[1])));
+                    tot[2] = fmaf(s1a, alo[2], fmaf(s1b, ahi[2], fmaf(s1c, sxv.x, tot[2])));
+                    tot[3] = fmaf(s1a, alo[3], fmaf(s1b, ahi[3], fmaf(s1c, sxv.y, tot[3])));
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[slot]);
@@ -269,8 +310,8 @@ decode_gemm_kernel(const DecodeKArgs a) {
         const int L = ((r & 7) << 2) + (n >> 1);
         const int c = ((r >> 3) << 1) + (n & 1);
         uint32_t item_local = 0;
-        for (int64_t it = it0; it < it1; ++it, ++item_local) {
-            const Item im = decode_item(a, it, nshared_seg);
+        for (long long it = it0; it < it1; ++it, ++item_local, iter.next(a)) {
+            const Item im = iter.get(a);
             const uint32_t rb = item_local & 1u;
             if (*abort_flag || !mbar_wait(&red_full[rb], (item_local >> 1) & 1u, kWaitLimit)) {
                 if (!*abort_flag) record_timeout(a, abort_flag, 6);
@@ -284,7 +325,7 @@ decode_gemm_kernel(const DecodeKArgs a) {
                 s1 += rbuf[(size_t)(2 * j + 1) * 128];
             }
             if (n < im.ntok) {
-                const int64_t slot = im.slot_begin + n;
+                const long long slot = im.slot_begin + n;
                 if (GU) {
                     const float h = __fmul_rn(silu_ref(s0), s1);
                     a.hbuf[slot * a.ldh + frag_pos(im.unit * 16 + r)] = __float2half_rn(h);
@@ -396,7 +437,8 @@ combine_kernel(const float* __restrict__ ybuf, const int* __restrict__ slot_pos,
 }
 
 size_t decode_smem_bytes(int Kmax, int nstage) {
-    return (size_t)nstage * kStageBytes + (size_t)kDecodeTokens * (Kmax * 2 + kXPad) + 2 * kRedBytes +
+    return (size_t)nstage * kStageBytes + (size_t)kDecodeTokens * (Kmax * 2 + kXPad) +
+           (size_t)(Kmax >> 7) * kDecodeTokens * sizeof(float) + 2 * kRedBytes +
            (2 * kMaxStages + 5) * sizeof(uint64_t) + 16;
 }
 
@@ -413,7 +455,7 @@ size_t decode_seg_bytes(int n, int topk, int E) {
     const size_t P = (size_t)n * topk;
     const size_t max_segs = (size_t)E + (P + kDecodeTokens - 1) / kDecodeTokens +
                             ((size_t)n + kDecodeTokens - 1) / kDecodeTokens + 1;
-    return (kSegHeader + 4 * max_segs) * sizeof(int);
+    return (kSegHeader + 4 * (max_segs + 1)) * sizeof(int);
 }
 
 int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {

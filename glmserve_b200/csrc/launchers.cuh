@@ -83,4 +83,29 @@ struct DecodeArgs {
 };
 int launch_decode_layer(const DecodeArgs& a, cudaStream_t s);
 
+size_t prefill_tile_bytes(int n, int topk, int E, int H, int I);
+
+struct PrefillArgs {
+    const __nv_bfloat16* x;
+    int n, topk, H, I, Is, E;
+    const void* gate_up_packed;
+    const void* down_packed;
+    const void* shared_gate_up_packed;
+    const void* shared_down_packed;
+    const int* expert_offsets;
+    const int* sorted_tok;
+    const int* slot_pos;
+    const float* topk_w;
+    int* tiles_gu;
+    int* tiles_dn;
+    __half* xs;     // [P + n, H] fp16 activations in expert order
+    __half* hbuf;   // [P + n, max(I, Is)] fp16
+    __half* ybuf;   // [P + n, H] fp16 per-slot output rows
+    int* status;
+    float* out;
+    int sm_count;
+    cudaEvent_t ev_prep, ev_gate_up, ev_down;
+};
+int launch_prefill_layer(const PrefillArgs& a, cudaStream_t s);
+
 }  // namespace gsb

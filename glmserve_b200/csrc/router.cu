@@ -91,47 +91,51 @@ int launch_router_topk(const float* logits, const float* e_bias, int n, int E, i
 }
 
 // ---- router logits -----------------------------------------------------------------
-// logits[t,e] = sum_i x[t,i] * Wr[e,i], bf16 inputs, fp32 accumulation.  Small-n form:
-// a block handles 8 experts x TT tokens, one warp per expert; lanes stride over the input
-// dim 8 elements (16 bytes) at a time, partial sums are combined with a fixed xor tree, so
-// the result does not depend on n or on the grid (the property the reference wants from
-// its n-invariant gemv, cuda/gemm.cu:37-44).
+// logits[t,e] = sum_i x[t,i] * Wr[e,i], bf16 inputs, fp32 accumulation.  A block stages TT
+// token rows in shared memory once, then each of its 8 warps owns one expert row: lanes
+// stride over the input dim 8 elements (16 bytes) at a time with the weight loads unrolled
+// so several are in flight; partial sums are combined with a fixed xor tree.  The result
+// for a (token, expert) does not depend on n or on the grid (the property the reference
+// wants from its n-invariant gemv, cuda/gemm.cu:37-44).
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& v, float (&f)[8]) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        f[2 * q] = __uint_as_float(u[q] << 16);
+        f[2 * q + 1] = __uint_as_float(u[q] & 0xffff0000u);
+    }
+}
+
 template <int TT>
 __global__ void __launch_bounds__(256)
 router_logits_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr,
                      int n, int H, int E, float* __restrict__ logits) {
+    extern __shared__ uint4 xsm[];  // [TT][H/8]
     const int e = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int t0 = blockIdx.y * TT;
     const int lane = threadIdx.x & 31;
+    const int nvec = H >> 3;
+    for (int idx = threadIdx.x; idx < TT * nvec; idx += blockDim.x) {
+        const int j = idx / nvec, v = idx - j * nvec;
+        xsm[idx] = (t0 + j < n) ? __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + j) * H) + v)
+                                : make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
     if (e >= E) return;
     float acc[TT];
 #pragma unroll
     for (int j = 0; j < TT; ++j) acc[j] = 0.0f;
     const uint4* wrow = reinterpret_cast<const uint4*>(wr + (size_t)e * H);
-    const int nvec = H >> 3;
+#pragma unroll 4
     for (int v = lane; v < nvec; v += 32) {
-        const uint4 wv = __ldg(wrow + v);
-        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
         float wf[8];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float2 f = __bfloat1622float2(wp[q]);
-            wf[2 * q] = f.x;
-            wf[2 * q + 1] = f.y;
-        }
+        bf16x8_to_f32(__ldg(wrow + v), wf);
 #pragma unroll
         for (int j = 0; j < TT; ++j) {
-            const int t = t0 + j;
-            if (t < n) {
-                const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)t * H) + v);
-                const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+            float xf[8];
+            bf16x8_to_f32(xsm[j * nvec + v], xf);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float2 f = __bfloat1622float2(xp[q]);
-                    acc[j] = fmaf(f.x, wf[2 * q], acc[j]);
-                    acc[j] = fmaf(f.y, wf[2 * q + 1], acc[j]);
-                }
-            }
+            for (int q = 0; q < 8; ++q) acc[j] = fmaf(xf[q], wf[q], acc[j]);
         }
     }
 #pragma unroll
@@ -146,8 +150,14 @@ int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n,
     if (n == 0) return GSB_OK;
     if (H % 8 != 0) return GSB_ERR_UNSUPPORTED;
     constexpr int TT = 8;
+    const size_t smem = (size_t)TT * H * 2;
+    if (smem > 200 * 1024) return GSB_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(router_logits_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+        return GSB_ERR_CUDA;
     dim3 grid((unsigned)((E + 7) / 8), (unsigned)((n + TT - 1) / TT));
-    router_logits_kernel<TT><<<grid, 256, 0, s>>>(x, wr, n, H, E, logits);
+    router_logits_kernel<TT><<<grid, 256, smem, s>>>(x, wr, n, H, E, logits);
     return launch_status();
 }
 

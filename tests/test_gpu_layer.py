@@ -64,6 +64,27 @@ def test_mid_config_decode_path(dev, n):
     assert torch.equal(out2, a["out"])
 
 
+@pytest.mark.parametrize("n", [1, 16, 100, 300, 700])
+def test_mid_config_prefill_path(dev, n):
+    """tcgen05 grouped GEMM path on small shapes: single and multiple token tiles, ragged
+    last tiles, experts with no tokens."""
+    from glmserve_b200 import ops
+    L = make_layer_np(CONFIGS["mid"], seed=23)
+    layer = ops.MoELayer(layer_to_torch(L, dev))
+    x = make_x_np(n, L["H"], seed=40 + n)
+    a = _check_layer(layer, L, x, dev, ops.PATH_PREFILL, f"mid prefill n={n}")
+    out2 = layer.forward(bf16_tensor(x, dev), path=ops.PATH_PREFILL)
+    assert torch.equal(out2, a["out"])
+
+
+def test_mid_config_prefill_skewed_no_shared(dev):
+    from glmserve_b200 import ops
+    L = make_layer_np(CONFIGS["mid"], seed=24, shared=False, zipf_amplitude=0.6)
+    layer = ops.MoELayer(layer_to_torch(L, dev))
+    x = make_x_np(1000, L["H"], seed=6)
+    _check_layer(layer, L, x, dev, ops.PATH_PREFILL, "mid prefill skewed")
+
+
 def test_mid_config_without_shared_expert_and_skew(dev):
     from glmserve_b200 import ops
     L = make_layer_np(CONFIGS["mid"], seed=22, shared=False, zipf_amplitude=0.6)
@@ -107,6 +128,20 @@ def test_glm_scale_decode(dev, glm_layer, n):
     assert_layer_close(out.cpu().numpy(), r["out"], f"glm decode n={n}")
     out2 = layer.forward(x, path=ops.PATH_DECODE)
     assert torch.equal(out, out2)
+
+
+def test_glm_scale_prefill(dev, glm_layer):
+    """GLM-scale layer through the tcgen05 path at 512 tokens (about 16 rows per expert)."""
+    from glmserve_b200 import ops
+    layer, Lnp = glm_layer
+    n = 512
+    x = make_x_torch(n, 6144, seed=300, device=dev)
+    x_np = x.float().cpu().numpy()
+    out, logits, ids, w = layer.forward(x, path=ops.PATH_PREFILL, return_routing=True)
+    assert layer.status() == 0
+    r = oracle.moe_layer_w4(x_np, Lnp, logits_in=logits.cpu().numpy())
+    assert np.array_equal(ids.cpu().numpy(), r["ids"])
+    assert_layer_close(out.cpu().numpy(), r["out"], "glm prefill n=512")
 
 
 def test_block_of_layers_with_prenorm_and_residual(dev):
