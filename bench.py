@@ -118,12 +118,42 @@ def cpu_port_baseline(Lnp, x_np, sample_tokens: int) -> dict:
                        f"(expert-major, int4 rows dequantised on the fly) on {nthreads} threads")
 
 
+def layer_flops(T: int) -> dict:
+    routed = 2 * T * GLM["topk"] * 3 * GLM["H"] * GLM["I"]
+    shared = 2 * T * 3 * GLM["H"] * GLM["Is"]
+    router = 2 * T * GLM["H"] * GLM["E"]
+    gate_up = 2 * (T * GLM["topk"] * 2 * GLM["H"] * GLM["I"] + T * 2 * GLM["H"] * GLM["Is"])
+    return dict(layer=routed + shared + router, gate_up=gate_up)
+
+
+def time_layer(layer, x, out, path, steps, warmup, barrier, ops):
+    """Device time of `steps` forwards (CUDA events on the launching stream) and the stage
+    times from the library's stage marks."""
+    import torch
+    for _ in range(max(warmup, 3)):
+        layer.forward(x, out=out, path=path)
+    assert layer.status() == 0, "device-side wait timed out during warm-up"
+    ops.profile_enable(layer, steps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(steps):
+        layer.forward(x, out=out, path=path)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / steps
+    stages = ops.profile_read(layer)
+    ops.profile_enable(layer, 0)
+    assert layer.status() == 0, "device-side wait timed out"
+    return ms, {k: v for k, v in stages.items() if k != "forwards"}
+
+
 def run_ours(args) -> None:
     import numpy as np
     import torch
 
     from glmserve_b200 import ops
-    from glmserve_b200.synth import layer_to_np, make_layer_torch, make_x_torch
+    from glmserve_b200.synth import layer_to_np, make_layer_torch, make_x_torch, zipf_bias
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -134,8 +164,12 @@ def run_ours(args) -> None:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     T = args.tokens
+    prefill = T >= 256 if args.path == "auto" else args.path == "prefill"
+    path = ops.PATH_PREFILL if prefill else ops.PATH_DECODE
 
     Lt = make_layer_torch(GLM, seed=1, device=dev)
+    if prefill:  # configuration 3: Zipf(1.1)-ranked router bias, loads from ~0 to ~8x the mean
+        Lt["e_bias"] = (Lt["e_bias"] + torch.from_numpy(zipf_bias(GLM["E"], np.random.default_rng(1), 0.04)).to(dev)).contiguous()
     layer = ops.MoELayer(Lt, keep_raw=False)
     x = make_x_torch(T, GLM["H"], seed=100 + rank, device=dev)
     out = torch.empty((T, GLM["H"]), dtype=torch.float32, device=dev)
@@ -147,43 +181,66 @@ def run_ours(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # warm-up (also sizes the workspace) and routing for the byte count
-    _, _, ids, _ = layer.forward(x, out=out, path=ops.PATH_DECODE, return_routing=True)
-    for _ in range(max(args.warmup, 3)):
-        layer.forward(x, out=out, path=ops.PATH_DECODE)
-    assert layer.status() == 0, "device-side wait timed out during warm-up"
-    alg = algorithmic_bytes(ids.cpu().numpy(), T)
+    _, _, ids, _ = layer.forward(x, out=out, path=path, return_routing=True)
+    ids_np = ids.cpu().numpy()
+    alg = algorithmic_bytes(ids_np, T)
+    loads = np.bincount(ids_np.ravel(), minlength=GLM["E"])
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    ops.profile_enable(layer, args.steps)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        layer.forward(x, out=out, path=ops.PATH_DECODE)
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
-    stages = ops.profile_read(layer)
-    ops.profile_enable(layer, 0)
+    ms_step, stages = time_layer(layer, x, out, path, args.steps, args.warmup, barrier, ops)
 
     # end to end through the host-buffer call: H2D of the step's tokens, D2H of its output
     for _ in range(3):
-        layer.forward_host(x_host, out_host, path=ops.PATH_DECODE)
+        layer.forward_host(x_host, out_host, path=path)
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        layer.forward_host(x_host, out_host, path=ops.PATH_DECODE)
+        layer.forward_host(x_host, out_host, path=path)
     barrier()
-    e2e_s = time.perf_counter() - t0
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
     clocks = sampler.stop() if rank == 0 else None
-    assert layer.status() == 0, "device-side wait timed out"
 
-    ms_step = ms_total / args.steps
-    e2e_ms = e2e_s * 1e3 / args.steps
+    # the other shapes of the headline metric, on the same resident weights (N=1 only)
+    extra = {}
+    if world == 1 and not args.no_extra and not prefill and T == 64 and GLM["E"] == 256:
+        for t2 in (1, 8):
+            x2 = make_x_torch(t2, GLM["H"], seed=100 + t2, device=dev)
+            o2 = torch.empty((t2, GLM["H"]), dtype=torch.float32, device=dev)
+            flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+            _, _, i2, _ = layer.forward(x2, out=o2, path=ops.PATH_DECODE, return_routing=True)
+            a2 = algorithmic_bytes(i2.cpu().numpy(), t2)
+            ts = []
+            for _ in range(10):  # small working sets: flush L2 (write 256 MiB) before every timed call
+                flush.fill_(1)
+                ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ea.record(); layer.forward(x2, out=o2, path=ops.PATH_DECODE); eb.record()
+                torch.cuda.synchronize()
+                ts.append(ea.elapsed_time(eb))
+            m2 = sorted(ts)[len(ts) // 2]
+            extra[f"decode_T{t2}"] = {"us_per_layer": m2 * 1e3, "layer_gbs": a2["layer_bytes"] / (m2 * 1e-3) / 1e9,
+                                      "distinct_experts": a2["distinct_experts"], "l2": "flushed before each call"}
+            del flush
+        Tp = 8192
+        Ls = dict(Lt)
+        Ls["e_bias"] = (Lt["e_bias"] + torch.from_numpy(zipf_bias(GLM["E"], np.random.default_rng(1), 0.04)).to(dev)).contiguous()
+        layer_p = ops.MoELayer(Ls, share_from=layer)
+        xp = make_x_torch(Tp, GLM["H"], seed=200, device=dev)
+        op_ = torch.empty((Tp, GLM["H"]), dtype=torch.float32, device=dev)
+        _, _, ip, _ = layer_p.forward(xp, out=op_, path=ops.PATH_PREFILL, return_routing=True)
+        lp = np.bincount(ip.cpu().numpy().ravel(), minlength=GLM["E"])
+        msp, stp = time_layer(layer_p, xp, op_, ops.PATH_PREFILL, 5, 3, barrier, ops)
+        fl = layer_flops(Tp)
+        pk = peaks()
+        extra["prefill_T8192"] = {"tokens_per_s": Tp / (msp * 1e-3), "ms_per_layer": msp,
+                                  "tflops": fl["layer"] / (msp * 1e-3) / 1e12,
+                                  "frac_of_measured_bf16_peak": fl["layer"] / (msp * 1e-3) / 1e12 / pk["bf16_tflops"],
+                                  "stage_ms": stp, "load_max_over_mean": float(lp.max() / lp.mean()),
+                                  "load_min_over_mean": float(lp.min() / lp.mean()),
+                                  "routing": "Zipf(1.1)-ranked router bias, amplitude 0.04"}
+
     if world > 1:
         t = torch.tensor([ms_step, e2e_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -192,44 +249,61 @@ def run_ours(args) -> None:
     if rank == 0:
         pk = peaks()
         gu_ms = stages["moe.gate_up"]
-        achieved = alg["gate_up_bytes"] / (gu_ms * 1e-3) / 1e9 if gu_ms > 0 else 0.0
-        layer_gbs = alg["layer_bytes"] / (ms_step * 1e-3) / 1e9
+        shape = "prefill" if prefill else "decode"
+        if prefill:
+            fl = layer_flops(T)
+            achieved = fl["gate_up"] / (gu_ms * 1e-3) / 1e12 if gu_ms > 0 else 0.0
+            roof = {"bound": "tensor", "kernel": "prefill_gemm_kernel<gate_up>", "achieved": achieved,
+                    "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": achieved / pk["bf16_tflops"],
+                    "peak_source": pk["source"], "algorithmic_flops": fl["gate_up"], "kernel_ms": gu_ms,
+                    "traffic": None}
+            whole = {"layer_tflops": fl["layer"] / (ms_step * 1e-3) / 1e12,
+                     "layer_frac_of_measured_bf16_peak": fl["layer"] / (ms_step * 1e-3) / 1e12 / pk["bf16_tflops"],
+                     "load_max_over_mean": float(loads.max() / loads.mean()),
+                     "load_min_over_mean": float(loads.min() / loads.mean())}
+            l2 = "inputs larger than L2: 5 GB of expert weights and 0.9 GB of gathered activations per step"
+        else:
+            achieved = alg["gate_up_bytes"] / (gu_ms * 1e-3) / 1e9 if gu_ms > 0 else 0.0
+            roof = {"bound": "hbm", "kernel": "decode_gemm_kernel<gate_up>", "achieved": achieved,
+                    "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"],
+                    "peak_source": pk["source"], "algorithmic_bytes": alg["gate_up_bytes"], "kernel_ms": gu_ms,
+                    "traffic": None}
+            layer_gbs = alg["layer_bytes"] / (ms_step * 1e-3) / 1e9
+            whole = {"layer_gbs": layer_gbs, "layer_frac_of_measured_hbm": layer_gbs / pk["hbm_gbs"],
+                     "layer_frac_of_8tbs": layer_gbs / 8000.0}
+            l2 = ("inputs larger than L2: every step streams the touched experts' "
+                  f"{alg['layer_bytes'] / 1e9:.2f} GB of weights, far beyond the 126 MB L2")
         line = {
-            "metric": f"w4a16_moe_layer_decode_T{T}_tokens_per_s",
+            "metric": f"w4a16_moe_layer_{shape}_T{T}_tokens_per_s",
             "value": world * T / (ms_step * 1e-3),
             "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "w4a16 (int4 weights, fp16 mma, fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": f"GLM-scale decode MoE layer, T={T} tokens per GPU: hidden 6144, {GLM['E']} routed "
+            "dtype": "w4a16 (int4 weights, fp16 tensor-core math, fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": f"GLM-scale {shape} MoE layer, T={T} tokens per GPU: hidden 6144, {GLM['E']} routed "
                                    "experts top-8, expert intermediate 2048, 1 shared expert, W4A16 group 128, "
-                                   "fp16 scales, bf16 activations",
+                                   "fp16 scales, bf16 activations" + (", Zipf(1.1)-skewed routing" if prefill else ""),
                        "multi_gpu": "independent replicas (tokens shard, no collective)" if world > 1 else "single GPU",
-                       "l2": "inputs larger than L2: every step streams the touched experts' "
-                             f"{alg['layer_bytes'] / 1e9:.2f} GB of weights, far beyond the 126 MB L2",
-                       "distinct_experts": alg["distinct_experts"]},
-            "layer_gbs": layer_gbs,
-            "layer_frac_of_measured_hbm": layer_gbs / pk["hbm_gbs"],
-            "layer_frac_of_8tbs": layer_gbs / 8000.0,
-            "stage_ms": {k: v for k, v in stages.items() if k != "forwards"},
-            "roofline": {"bound": "hbm", "kernel": "decode_gemm_kernel<gate_up>",
-                         "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / pk["hbm_gbs"], "peak_source": pk["source"],
-                         "algorithmic_bytes": alg["gate_up_bytes"], "kernel_ms": gu_ms, "traffic": None},
+                       "l2": l2, "distinct_experts": alg["distinct_experts"]},
+            **whole,
+            "stage_ms": stages,
+            "roofline": roof,
             "e2e": {"value": world * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": T * GLM["H"] * 2, "d2h_bytes_per_step": T * GLM["H"] * 4},
-            "gpu_launches": 8 * args.steps,
+            "gpu_launches": (12 if prefill else 8) * args.steps,
             "clocks": clocks,
         }
+        line.update(extra)
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_port_baseline(layer_to_np(Lt), x.float().cpu().numpy(),
                                                      min(T, args.cpu_tokens))
-        traffic_file = os.path.join(ROOT, "profiles", "decode_gate_up_traffic.json")
+        traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(traffic_file):
             with open(traffic_file) as f:
                 tr = json.load(f)
-            line["roofline"]["traffic"] = tr.get("dram_bytes_per_launch_T64") if T == 64 else None
+            key = f"{shape}_gate_up_T{T}"
+            line["roofline"]["traffic"] = tr.get(key)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -302,6 +376,9 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=16, help="token sample of the CPU baseline leg")
     ap.add_argument("--ref-tokens", type=int, default=4, help="token sample of --impl reference")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the T=1, T=8 and T=8192 legs")
+    ap.add_argument("--path", default="auto", choices=["auto", "decode", "prefill"],
+                    help="auto: tcgen05 grouped GEMM from 256 tokens, split-K decode kernels below")
     ap.add_argument("--experts", type=int, default=256,
                     help="routed experts (256 = the benchmark layer; fewer = a small case for profiler captures)")
     args = ap.parse_args()

@@ -178,7 +178,9 @@ class MoELayer:
     upload.
     """
 
-    def __init__(self, L: dict, prepack: bool | None = None, keep_raw: bool = True):
+    def __init__(self, L: dict, prepack: bool | None = None, keep_raw: bool = True, share_from=None):
+        """``share_from``: another MoELayer over the same weight tensors whose prepacked
+        streams are reused (only router weight / bias / flags are taken from ``L``)."""
         self.H, self.E, self.topk, self.I, self.Is, self.group = (int(L[k]) for k in
                                                                    ("H", "E", "topk", "I", "Is", "group"))
         shared = L.get("sg_q") is not None
@@ -202,13 +204,18 @@ class MoELayer:
         if L.get("e_bias") is not None:
             cfg.e_bias = hold("e_bias", L["e_bias"].float().contiguous())
         names = ["gate", "up", "down"] + (["sg", "su", "sd"] if shared else [])
-        if prepack:
+        if prepack and share_from is not None:
+            for nm, fld in (("gup", "gate_up_packed"), ("dp", "down_packed"), ("sgup", "shared_gate_up_packed"),
+                            ("sdp", "shared_down_packed")):
+                if nm in share_from._keep:
+                    setattr(cfg, fld, hold(nm, share_from._keep[nm]))
+        elif prepack:
             cfg.gate_up_packed = hold("gup", prepack_gate_up(L["gate_q"], L["gate_sc"], L["up_q"], L["up_sc"]))
             cfg.down_packed = hold("dp", prepack_down(L["down_q"], L["down_sc"]))
             if shared:
                 cfg.shared_gate_up_packed = hold("sgup", prepack_gate_up(L["sg_q"], L["sg_sc"], L["su_q"], L["su_sc"]))
                 cfg.shared_down_packed = hold("sdp", prepack_down(L["sd_q"], L["sd_sc"]))
-        if keep_raw or not prepack:
+        if (keep_raw and share_from is None) or not prepack:
             for nm in names:
                 setattr(cfg, nm + "_q", hold(nm + "_q", L[nm + "_q"].contiguous()))
                 setattr(cfg, nm + "_sc", hold(nm + "_sc", L[nm + "_sc"].to(torch.float16).contiguous()))

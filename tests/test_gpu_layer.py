@@ -79,7 +79,7 @@ def test_mid_config_prefill_path(dev, n):
 
 def test_mid_config_prefill_skewed_no_shared(dev):
     from glmserve_b200 import ops
-    L = make_layer_np(CONFIGS["mid"], seed=24, shared=False, zipf_amplitude=0.6)
+    L = make_layer_np(CONFIGS["mid"], seed=24, shared=False, zipf_amplitude=0.1)
     layer = ops.MoELayer(layer_to_torch(L, dev))
     x = make_x_np(1000, L["H"], seed=6)
     _check_layer(layer, L, x, dev, ops.PATH_PREFILL, "mid prefill skewed")
@@ -87,7 +87,7 @@ def test_mid_config_prefill_skewed_no_shared(dev):
 
 def test_mid_config_without_shared_expert_and_skew(dev):
     from glmserve_b200 import ops
-    L = make_layer_np(CONFIGS["mid"], seed=22, shared=False, zipf_amplitude=0.6)
+    L = make_layer_np(CONFIGS["mid"], seed=22, shared=False, zipf_amplitude=0.1)
     layer = ops.MoELayer(layer_to_torch(L, dev))
     x = make_x_np(96, L["H"], seed=5)
     _check_layer(layer, L, x, dev, ops.PATH_DECODE, "mid no-shared skewed")
