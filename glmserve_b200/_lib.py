@@ -9,7 +9,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libglmserve_b200.so")
 
 STATUS = {0: "ok", 1: "invalid argument", 2: "unsupported shape or format", 3: "kernel launch failed",
-          4: "device-side wait timed out", 5: "CUDA runtime call failed", 6: "workspace too small"}
+          4: "device-side wait timed out", 5: "CUDA runtime call failed", 6: "workspace too small",
+          7: "problem larger than the built-in fixed-size buffer"}
 
 
 class GsbError(RuntimeError):

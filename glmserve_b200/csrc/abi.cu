@@ -102,6 +102,7 @@ const char* gsb_status_string(int status) {
         case GSB_ERR_TIMEOUT: return "device-side wait timed out";
         case GSB_ERR_CUDA: return "CUDA runtime call failed";
         case GSB_ERR_WORKSPACE: return "workspace too small";
+        case GSB_ERR_TOO_LARGE: return "problem larger than the built-in fixed-size buffer";
         default: return "unknown status";
     }
 }

@@ -35,7 +35,8 @@ enum {
     GSB_ERR_LAUNCH = 3,      /* cudaGetLastError() after the launch was not cudaSuccess */
     GSB_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up (status word set) */
     GSB_ERR_CUDA = 5,        /* another CUDA runtime call failed */
-    GSB_ERR_WORKSPACE = 6    /* caller scratch smaller than gsb_moe_workspace_bytes() */
+    GSB_ERR_WORKSPACE = 6,   /* caller scratch smaller than gsb_moe_workspace_bytes() */
+    GSB_ERR_TOO_LARGE = 7    /* problem larger than a built-in fixed-size buffer */
 };
 
 /* Text for a status code (static storage). */
@@ -246,6 +247,33 @@ GSB_API int gsb_router_logits(const void* x_bf16, const void* router_w_bf16, int
 #define GSB_N_STAGES 5
 GSB_API int gsb_moe_layer_profile_enable(gsb_moe_layer* layer, int max_forwards);
 GSB_API int gsb_moe_layer_profile_read(gsb_moe_layer* layer, float* stage_ms, int* n_forwards);
+
+/* Routing without any allocation: x bf16 [n,hidden] and the bf16 router weight [E,hidden]
+ * in, topk_ids i32 [n,topk] and topk_weights f32 [n,topk] out - the same result as
+ * gsb_router_logits followed by gsb_moe_router, but the [n,E] logits in between are kept in
+ * a fixed 256 KiB array inside the library instead of in a buffer the caller supplies.
+ * This entry point has no counterpart in the reference.
+ * It is meant for callers that cannot obtain device memory at the point of the call: an
+ * engine that handed its whole memory budget to a weight/KV arena at start-up and has no
+ * allocator left for per-call scratch, a plug-in running inside a host that forbids
+ * cudaMalloc on its threads, or a latency-critical loop where an allocation's implicit
+ * device synchronisation is not acceptable.  It calls no cudaMalloc / cudaFree and no
+ * allocating library routine.
+ * Limits and rules:
+ *   - n * E must not exceed gsb_moe_route_static_max_floats() (65536); larger problems
+ *     return GSB_ERR_TOO_LARGE and launch nothing.  Other shape limits as gsb_moe_router.
+ *   - every GPU that loads the library holds the 256 KiB array until the process exits.
+ *   - the first call on each device looks up the array's device address (a host-side
+ *     runtime query, done once per device with that device current); make that first call
+ *     before starting any stream capture.
+ *   - all calls on a device share the one array: the call overwrites every element it later
+ *     reads, so stale contents are harmless, but two calls whose kernels can overlap on the
+ *     GPU (different streams, no ordering between them) race on it.  Serialise them. */
+GSB_API int gsb_moe_route_static(const void* x_bf16, const void* router_w_bf16,
+                                 const float* e_bias, int n, int hidden, int E, int topk,
+                                 int norm_topk, float routed_scale, int* topk_ids,
+                                 float* topk_weights, void* stream);
+GSB_API int gsb_moe_route_static_max_floats(void);
 
 /* Reads (and clears) the device status word of the last forward on this layer after the
  * caller synchronised the stream: GSB_OK or GSB_ERR_TIMEOUT.  Host call. */

@@ -1,0 +1,59 @@
+"""gsb_moe_route_static: routing for callers that cannot allocate device memory at call time
+(an engine whose memory budget is already committed to its weight/KV arena, a plug-in host
+that forbids cudaMalloc, a loop that cannot afford an allocation's implicit sync).  The
+logits between the two kernels live in a fixed array inside the library, so every call
+shares it; the test runs two different problems back to back and checks each against the
+regular entry points (gsb_router_logits + gsb_moe_router with a caller-owned logits
+buffer), which must give identical ids and weights.  This file sorts last on purpose.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def _route_static(x, wr, bias, topk, norm=True, scale=2.5):
+    from glmserve_b200._lib import lib
+    n, H = x.shape
+    E = wr.shape[0]
+    ids = torch.full((n, topk), -1, dtype=torch.int32, device=x.device)
+    w = torch.full((n, topk), float("nan"), dtype=torch.float32, device=x.device)
+    st = lib().gsb_moe_route_static(C.c_void_p(x.data_ptr()), C.c_void_p(wr.data_ptr()),
+                                    C.c_void_p(bias.data_ptr() if bias is not None else 0), n, H, E, topk,
+                                    int(norm), C.c_float(scale), C.c_void_p(ids.data_ptr()),
+                                    C.c_void_p(w.data_ptr()),
+                                    C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    return st, ids, w
+
+
+def test_route_static_matches_regular_entry_points_twice_in_a_row():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from glmserve_b200 import ops
+    from glmserve_b200._lib import lib
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+    # two calls in a row with different shapes: the second must not see the first's logits
+    for n, H, E, topk, with_bias in ((64, 6144, 256, 8, True), (200, 512, 48, 4, False)):
+        x = torch.randn((n, H), generator=gen, device=dev).to(torch.bfloat16)
+        wr = (torch.randn((E, H), generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+        bias = (torch.randn((E,), generator=gen, device=dev) * 0.01) if with_bias else None
+        st, ids, w = _route_static(x, wr, bias, topk)
+        assert st == 0
+        logits = ops.router_logits(x, wr)
+        ids_ref, w_ref = ops.moe_router(logits, bias, topk, True, 2.5)
+        torch.cuda.synchronize()
+        assert torch.equal(ids, ids_ref)
+        np.testing.assert_allclose(w.cpu().numpy(), w_ref.cpu().numpy(), rtol=0, atol=1e-6)
+    # beyond the built-in buffer: refused with a clear status, nothing launched
+    limit = lib().gsb_moe_route_static_max_floats()
+    n_big = limit // 256 + 1
+    xb = torch.zeros((n_big, 512), dtype=torch.bfloat16, device=dev)
+    wb = torch.zeros((256, 512), dtype=torch.bfloat16, device=dev)
+    st, ids, _ = _route_static(xb, wb, None, 8)
+    assert st == 7
+    assert int(ids.min()) == -1 and int(ids.max()) == -1
+    assert lib().gsb_status_string(7).decode().startswith("problem larger")
