@@ -1,0 +1,50 @@
+"""The C-ABI library loads without a GPU and exports every symbol the headers declare
+(no compute calls here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    names = []
+    for fn in os.listdir(os.path.join(ROOT, "include")):
+        if fn.endswith(".h"):
+            text = open(os.path.join(ROOT, "include", fn)).read()
+            names += re.findall(r"GSB_API\s+[\w\s\*]+?\b(gsb_\w+)\s*\(", text)
+    return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol():
+    from glmserve_b200 import build
+    from glmserve_b200._lib import LIB_PATH
+    if not os.path.exists(LIB_PATH):
+        build.build()
+    lib = ctypes.CDLL(LIB_PATH)
+    names = _declared()
+    assert len(names) >= 25
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+    lib.gsb_status_string.restype = ctypes.c_char_p
+    assert lib.gsb_status_string(0) == b"ok"
+    assert lib.gsb_status_string(2) == b"unsupported shape or format"
+
+
+def test_pure_host_entry_points_validate_arguments():
+    from glmserve_b200._lib import lib
+    L = lib()
+    assert L.gsb_prepack_bytes(1, 64, 1024) == 2 * 2 * 8448
+    assert L.gsb_prepack_bytes(1, 64, 1000) == 0
+    assert L.gsb_moe_layer_create(None, None) == 1
+    assert L.gsb_moe_route_static_max_floats() == 65536
+
+
+def test_shim_header_names_match_reference_surface():
+    text = open(os.path.join(ROOT, "include", "glmserve_cuda_shim.cuh")).read()
+    for name in ("moe_router", "moe_dispatch", "moe_expert_ffn", "moe_expert_ffn_w4a16", "gemm_w4a16",
+                 "gemm_q", "gemm_q_i8", "quantize_act_q8", "qtype_has_i8", "moe_expert_ffn_q",
+                 "moe_expert_ffn_q_i8"):
+        assert re.search(r"inline\s+\w+\s+%s\s*\(" % name, text), name
