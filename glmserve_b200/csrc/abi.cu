@@ -31,6 +31,7 @@ namespace {
 struct Workspace {
     int* status;              // int32[64]
     float* logits;            // [n, E]
+    float* scores;            // [n, E] sigmoid(logits)
     int* ids;                 // [n, topk]
     float* w;                 // [n, topk]
     int* expert_offsets;      // [E + 1]
@@ -61,6 +62,7 @@ Workspace carve(const gsb_moe_config& c, int n, void* base) {
     };
     ws.status = reinterpret_cast<int*>(take(64 * sizeof(int)));
     ws.logits = reinterpret_cast<float*>(take((size_t)n * c.n_experts * sizeof(float)));
+    ws.scores = reinterpret_cast<float*>(take((size_t)n * c.n_experts * sizeof(float)));
     ws.ids = reinterpret_cast<int*>(take(P * sizeof(int)));
     ws.w = reinterpret_cast<float*>(take(P * sizeof(float)));
     ws.expert_offsets = reinterpret_cast<int*>(take((size_t)(c.n_experts + 1) * sizeof(int)));
@@ -280,7 +282,7 @@ int gsb_router_logits(const void* x_bf16, const void* router_w_bf16, int n, int 
         return GSB_ERR_INVALID_ARG;
     return launch_router_logits(reinterpret_cast<const __nv_bfloat16*>(x_bf16),
                                 reinterpret_cast<const __nv_bfloat16*>(router_w_bf16), n, hidden, E,
-                                logits, as_stream(stream));
+                                logits, nullptr, as_stream(stream));
 }
 
 int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float* out,
@@ -300,15 +302,15 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
     auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], s); };
     mark(0);
     if (path == GSB_PATH_AUTO) path = layer->tiles_ok ? GSB_PATH_DECODE : GSB_PATH_DIRECT;
-    if ((path == GSB_PATH_DECODE || path == GSB_PATH_PREFILL) && !layer->tiles_ok)
+    if ((path == GSB_PATH_DECODE || path == GSB_PATH_PREFILL || path == GSB_PATH_DECODE_SMEM) && !layer->tiles_ok)
         return GSB_ERR_UNSUPPORTED;
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
 
     int st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden,
-                                  c.n_experts, ws.logits, s);
+                                  c.n_experts, ws.logits, ws.scores, s);
     if (st) return st;
-    st = launch_router_topk(ws.logits, c.e_bias, n, c.n_experts, c.topk, c.norm_topk,
-                            c.routed_scale, ws.ids, ws.w, s);
+    st = launch_router_topk(ws.scores, c.e_bias, n, c.n_experts, c.topk, c.norm_topk,
+                            c.routed_scale, ws.ids, ws.w, s, true);
     if (st) return st;
     if (logits_out && cudaMemcpyAsync(logits_out, ws.logits, (size_t)n * c.n_experts * sizeof(float),
                                       cudaMemcpyDeviceToDevice, s) != cudaSuccess)
@@ -344,8 +346,9 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
     st = launch_dispatch(ws.ids, n, c.topk, c.n_experts, ws.expert_offsets, ws.sorted_tok,
                          ws.sorted_row, ws.slot_pos, s);
     if (st) return st;
-    if (path == GSB_PATH_DECODE) {
+    if (path == GSB_PATH_DECODE || path == GSB_PATH_DECODE_SMEM) {
         DecodeArgs d{};
+        d.force_smem_variant = path == GSB_PATH_DECODE_SMEM ? 1 : 0;
         d.x = x; d.n = n; d.topk = c.topk; d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter;
         d.E = c.n_experts;
         d.gate_up_packed = c.gate_up_packed; d.down_packed = c.down_packed;

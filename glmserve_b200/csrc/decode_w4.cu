@@ -101,6 +101,35 @@ struct ItemIter {
     }
 };
 
+// A maximal run of consecutive items inside one segment: units [ubeg, uend) of segment seg.
+// A CTA's item range splits into a handful of runs, so the per-item work of the inner loops
+// is a counter increment (the units of a segment are contiguous in the tile stream).
+struct SegRun {
+    int seg, ubeg, uend, expert, slot_begin, ntok;
+    const uint8_t* chunks;  // first chunk of unit ubeg
+};
+__device__ __forceinline__ bool next_run(const DecodeKArgs& a, long long& it, long long it1, int nshared,
+                                         int nchunk_routed, int nchunk_shared, SegRun& r) {
+    if (it >= it1) return false;
+    const long long shared_items = (long long)nshared * a.units_s;
+    const bool sh = it < shared_items;
+    const int U = sh ? a.units_s : a.units;
+    const long long l = sh ? it : it - shared_items;
+    const int sg = (int)(l / U);
+    r.ubeg = (int)(l - (long long)sg * U);
+    r.seg = sg + (sh ? 0 : nshared);
+    const long long left = it1 - it;
+    r.uend = (int)((long long)(U - r.ubeg) < left ? U : r.ubeg + left);
+    const int4 rec = reinterpret_cast<const int4*>(a.segs + kSegHeader)[r.seg];
+    r.expert = rec.x; r.slot_begin = rec.y; r.ntok = rec.z;
+    const int nchunk = sh ? nchunk_shared : nchunk_routed;
+    const uint8_t* base = sh ? a.shared_packed : a.packed;
+    const long long e_local = sh ? 0 : rec.x;
+    r.chunks = base + ((e_local * U + r.ubeg) * (long long)nchunk) * kChunkBytes;
+    it += r.uend - r.ubeg;
+    return true;
+}
+
 __device__ __forceinline__ void record_timeout(const DecodeKArgs& a, volatile int* abort_flag,
                                                int where) {
     *abort_flag = 1;
@@ -170,7 +199,7 @@ decode_gemm_kernel(const DecodeKArgs a) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int i = 0; i < nstage; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], kConsumerWarps); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&red_full[i], kConsumerWarps * 32); mbar_init(&red_free[i], kEpiWarps * 32); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&red_full[i], kConsumerWarps); mbar_init(&red_free[i], kEpiWarps); }
         mbar_init(xbar, kConsumerWarps * 32);
         *abort_flag = 0;
         fence_barrier_init();
@@ -301,7 +330,8 @@ decode_gemm_kernel(const DecodeKArgs a) {
             if (!mbar_wait(&red_free[rb], ((item_local >> 1) & 1u) ^ 1u, kWaitLimit)) { record_timeout(a, abort_flag, 5); break; }
             float* r = red + (size_t)rb * (kRedBytes / 4) + (size_t)cw * 128 + lane;
             r[0] = tot[0]; r[32] = tot[1]; r[64] = tot[2]; r[96] = tot[3];
-            mbar_arrive(&red_full[rb]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&red_full[rb]);
         }
     } else {
         // ---------------- epilogue ----------------
@@ -335,7 +365,207 @@ decode_gemm_kernel(const DecodeKArgs a) {
                     y[16] = s1;
                 }
             }
-            mbar_arrive(&red_free[rb]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&red_free[rb]);
+        }
+    }
+}
+
+// ---- register-resident variant ------------------------------------------------------------
+// Same work split and arithmetic, for input dims that are multiples of 2048 (NKB = K / 2048
+// <= 3): a stage is four chunks (33 KiB, one bulk copy), consumer warp (ck, ks) owns chunk ck
+// and kstep ks of every stage and BOTH half units, and keeps the activation fragments it will
+// ever need for the segment - NKB x 4 x 16 bytes per lane - and their per-group sums in
+// registers.  No activation copy in shared memory (the whole 227 KiB minus the partial-sum
+// buffers is ring: more bytes in flight per SM), no CTA-wide synchronisation when the
+// segment changes, a quarter fewer instructions per byte.
+constexpr int kRConsumerWarps = 16;
+// epilogue warps / partial-sum buffers: the down kernel finishes an item per stage and has
+// twice the outputs per item, so it gets three warps and three buffers; gate/up one and two
+// Warp roles (warpgroup aligned so register budgets can be moved with setmaxnreg):
+// warps 0..15 consumers, warp 16 producer, warps 17..19 epilogue.
+template <bool GU> struct RCfg { static constexpr int kEpiWarps = 3; static constexpr int kRed = GU ? 2 : 3;
+                                 static constexpr int kThreads = (16 + 1 + kEpiWarps) * 32; };
+constexpr int kRConsumerRegs = 104;   // 16 warps x 32 x 104 + 4 warps x 32 x 56 = 60416 <= 65536
+constexpr int kRHelperRegs = 56;
+constexpr int kRStageChunks = 4;
+constexpr int kRStageBytes = kRStageChunks * kChunkBytes;           // 33792
+constexpr int kRRedFloats = kRConsumerWarps * 8 * 32;               // 16 KiB per buffer
+constexpr int kRMaxStages = 6;
+
+template <bool GU, int NKB>
+__global__ void __launch_bounds__(RCfg<GU>::kThreads, 1)
+decode_reg_kernel(const DecodeKArgs a) {
+    constexpr int kREpiWarps = RCfg<GU>::kEpiWarps;
+    constexpr int kRed = RCfg<GU>::kRed;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int nstage = a.nstage;
+    uint8_t* ring = smem;
+    float* red = reinterpret_cast<float*>(ring + (size_t)nstage * kRStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(red + kRed * kRRedFloats);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kRMaxStages;
+    uint64_t* red_full = bars + 2 * kRMaxStages;
+    uint64_t* red_free = red_full + 4;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(red_free + 4);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int i = 0; i < nstage; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], kRConsumerWarps); }
+        for (int i = 0; i < kRed; ++i) { mbar_init(&red_full[i], kRConsumerWarps); mbar_init(&red_free[i], kREpiWarps); }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    const int nseg = a.segs[0];
+    const int nshared_seg = a.segs[1];
+    const long long total = (long long)nshared_seg * a.units_s + (long long)(nseg - nshared_seg) * a.units;
+    const long long it0 = total * blockIdx.x / gridDim.x;
+    const long long it1 = total * (blockIdx.x + 1) / gridDim.x;
+    if (it0 >= it1) return;
+    long long it = it0;
+    SegRun run;
+
+    if (warp < kRConsumerWarps) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRConsumerRegs));
+    else asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRHelperRegs));
+
+    if (warp == kRConsumerWarps) {
+        if (lane == 0) {  // register-resident variant: producer
+            uint32_t q = 0;
+            bool dead = false;
+            while (!dead && !*abort_flag && next_run(a, it, it1, nshared_seg, NKB * 4, NKB * 4, run)) {
+                const uint8_t* src = run.chunks;
+                const int nst = (run.uend - run.ubeg) * NKB;  // the run's units are contiguous in memory
+                for (int i = 0; i < nst; ++i, ++q, src += kRStageBytes) {
+                    const uint32_t slot = q % nstage, ph = (q / nstage) & 1u;
+                    if (!mbar_wait(&empty[slot], ph ^ 1u, kWaitLimit)) { record_timeout(a, abort_flag, 11); dead = true; break; }
+                    mbar_arrive_expect_tx(&full[slot], kRStageBytes);
+                    bulk_g2s(ring + (size_t)slot * kRStageBytes, src, kRStageBytes, &full[slot]);
+                }
+            }
+        }
+    } else if (warp < kRConsumerWarps) {
+        const int cw = warp;
+        const int ck = cw >> 2, ks = cw & 3;
+        const int g = lane >> 2, t = lane & 3;
+        const uint32_t w_off = (uint32_t)ck * kChunkBytes + (ks * 2) * 1024 + lane * 16;
+        const uint32_t sc_off = (uint32_t)ck * kChunkBytes + kChunkWeightBytes + ((ks * 2) * 16 + g) * 2;
+        float* red_lane = red + (size_t)cw * 256 + lane;
+        uint4 xf[NKB][4];
+        float2 sxv[NKB];
+        uint32_t q = 0, item_local = 0;
+        bool dead = false;
+        while (!dead && next_run(a, it, it1, nshared_seg, NKB * 4, NKB * 4, run)) {
+            {   // this segment's activation fragments and per-group sums, straight into registers
+                const bool valid = g < run.ntok;
+                long long row = 0;
+                if (valid) {
+                    if (GU) row = (run.slot_begin + g < a.P) ? a.sorted_tok[run.slot_begin + g] : (run.slot_begin + g - a.P);
+                    else row = run.slot_begin + g;
+                }
+                const uint4* src = reinterpret_cast<const uint4*>(a.bsrc + row * a.ldb);
+#pragma unroll
+                for (int st = 0; st < NKB; ++st) {
+                    const int kb = (st * kRStageChunks + ck) * 4 + ks;
+                    float sg = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        xf[st][j] = valid ? __ldg(src + kb * 16 + j * 4 + t) : make_uint4(0u, 0u, 0u, 0u);
+                        const __half2* hp = reinterpret_cast<const __half2*>(&xf[st][j]);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(hp[e]); sg += f.x; sg += f.y; }
+                    }
+                    sg += __shfl_xor_sync(0xffffffffu, sg, 1);
+                    sg += __shfl_xor_sync(0xffffffffu, sg, 2);
+                    sxv[st].x = __shfl_sync(0xffffffffu, sg, (2 * t) * 4);
+                    sxv[st].y = __shfl_sync(0xffffffffu, sg, (2 * t + 1) * 4);
+                }
+            }
+            for (int unit = run.ubeg; unit < run.uend && !dead; ++unit, ++item_local) {
+                float tot[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+                for (int st = 0; st < NKB; ++st, ++q) {
+                    const uint32_t slot = q % nstage, ph = (q / nstage) & 1u;
+                    if (!mbar_wait(&full[slot], ph, kWaitLimit)) { record_timeout(a, abort_flag, 14); dead = true; break; }
+                    const uint8_t* stage = ring + (size_t)slot * kRStageBytes;
+#pragma unroll
+                    for (int m = 0; m < 2; ++m) {
+                        const uint4 w0 = lds128(stage + w_off + m * 1024);
+                        const uint4 w1 = lds128(stage + w_off + m * 1024 + 512);
+                        const __half* sc = reinterpret_cast<const __half*>(stage + sc_off + m * 32);
+                        const float s0 = __half2float(sc[0]), s1 = __half2float(sc[8]);
+                        float alo[4] = {0.f, 0.f, 0.f, 0.f}, ahi[4] = {0.f, 0.f, 0.f, 0.f};
+                        const uint32_t wa[4] = {w0.x, w0.y, w0.z, w0.w};
+                        const uint32_t wb[4] = {w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            uint32_t al0, ah0, al1, ah1, bl0, bh0, bl1, bh1;
+                            unpack8(wa[j], al0, ah0, al1, ah1);
+                            unpack8(wb[j], bl0, bh0, bl1, bh1);
+                            mma_16816(alo, al0, bl0, al1, bl1, xf[st][j].x, xf[st][j].z);
+                            mma_16816(ahi, ah0, bh0, ah1, bh1, xf[st][j].y, xf[st][j].w);
+                        }
+                        // sum x*(n-8) = 2^24*(alo + ahi/16) - 8*sum(x); then the group scale
+                        const float S0 = s0 * 16777216.f, C0 = s0 * -8.f, S1 = s1 * 16777216.f, C1 = s1 * -8.f;
+                        tot[m][0] = fmaf(S0, fmaf(ahi[0], 0.0625f, alo[0]), fmaf(C0, sxv[st].x, tot[m][0]));
+                        tot[m][1] = fmaf(S0, fmaf(ahi[1], 0.0625f, alo[1]), fmaf(C0, sxv[st].y, tot[m][1]));
+                        tot[m][2] = fmaf(S1, fmaf(ahi[2], 0.0625f, alo[2]), fmaf(C1, sxv[st].x, tot[m][2]));
+                        tot[m][3] = fmaf(S1, fmaf(ahi[3], 0.0625f, alo[3]), fmaf(C1, sxv[st].y, tot[m][3]));
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[slot]);
+                }
+                if (dead) break;
+                const uint32_t rb = item_local % kRed;
+                if (!mbar_wait(&red_free[rb], ((item_local / kRed) & 1u) ^ 1u, kWaitLimit)) { record_timeout(a, abort_flag, 15); dead = true; break; }
+                float* r = red_lane + (size_t)rb * kRRedFloats;
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) r[m * 128 + c * 32] = tot[m][c];
+                __syncwarp();  // orders every lane's partials before the one arrive below
+                if (lane == 0) mbar_arrive(&red_full[rb]);
+            }
+        }
+    } else {
+        const int et = tid - (1 + kRConsumerWarps) * 32;
+        constexpr int kNOut = GU ? 16 * kDecodeTokens : 32 * kDecodeTokens;  // outputs per item
+        uint32_t item_local = 0;
+        bool dead = false;
+        while (!dead && next_run(a, it, it1, nshared_seg, NKB * 4, NKB * 4, run)) {
+            for (int unit = run.ubeg; unit < run.uend; ++unit, ++item_local) {
+                const uint32_t rb = item_local % kRed;
+                if (*abort_flag || !mbar_wait(&red_full[rb], (item_local / kRed) & 1u, kWaitLimit)) {
+                    if (!*abort_flag) record_timeout(a, abort_flag, 16);
+                    dead = true;
+                    break;
+                }
+                for (int o = et; o < kNOut; o += kREpiWarps * 32) {
+                    // gate/up: o = n*16 + r, sums of both half units; down: o = n*32 + m*16 + r
+                    const int r = o & 15;
+                    const int m = GU ? 0 : (o >> 4) & 1;
+                    const int n = GU ? o >> 4 : o >> 5;
+                    if (n >= run.ntok) continue;
+                    const int L = ((r & 7) << 2) + (n >> 1);
+                    const int c = ((r >> 3) << 1) + (n & 1);
+                    const float* rbuf = red + (size_t)rb * kRRedFloats + m * 128 + c * 32 + L;
+                    const long long slot = run.slot_begin + n;
+                    if (GU) {
+                        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                        for (int w = 0; w < kRConsumerWarps; ++w) { s0 += rbuf[(size_t)w * 256]; s1 += rbuf[(size_t)w * 256 + 128]; }
+                        a.hbuf[slot * a.ldh + frag_pos(unit * 16 + r)] = __float2half_rn(__fmul_rn(silu_ref(s0), s1));
+                    } else {
+                        float s0 = 0.f;
+#pragma unroll
+                        for (int w = 0; w < kRConsumerWarps; ++w) s0 += rbuf[(size_t)w * 256];
+                        a.ybuf[slot * a.H + unit * 32 + m * 16 + r] = s0;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&red_free[rb]);
+            }
         }
     }
 }
@@ -458,6 +688,31 @@ size_t decode_seg_bytes(int n, int topk, int E) {
     return (kSegHeader + 4 * (max_segs + 1)) * sizeof(int);
 }
 
+constexpr size_t decode_reg_smem(int nstage, int nred) {
+    return (size_t)nstage * kRStageBytes + (size_t)nred * kRRedFloats * sizeof(float) + (2 * kRMaxStages + 8) * sizeof(uint64_t) + 16;
+}
+
+template <bool GU>
+static int launch_reg(const DecodeKArgs& k, int nkb, int grid, cudaStream_t s) {
+    DecodeKArgs a = k;
+    a.nstage = 5;
+    const size_t smem = decode_reg_smem(a.nstage, RCfg<GU>::kRed);
+#define GSB_LAUNCH_REG(N)                                                                              \
+    case N:                                                                                            \
+        if (cudaFuncSetAttribute(decode_reg_kernel<GU, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)smem) != cudaSuccess)                                            \
+            return GSB_ERR_CUDA;                                                                       \
+        decode_reg_kernel<GU, N><<<grid, RCfg<GU>::kThreads, smem, s>>>(a);                                    \
+        return GSB_OK;
+    switch (nkb) {
+        GSB_LAUNCH_REG(1)
+        GSB_LAUNCH_REG(2)
+        GSB_LAUNCH_REG(3)
+        default: return GSB_ERR_UNSUPPORTED;
+    }
+#undef GSB_LAUNCH_REG
+}
+
 int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     const int P = d.n * d.topk;
     const bool shared = d.Is > 0;
@@ -476,13 +731,20 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     g.bsrc = d.xp; g.ldb = d.H; g.K = d.H; g.Ks = d.H;
     g.units = d.I / 16; g.units_s = d.Is / 16; g.E = d.E; g.P = P;
     g.hbuf = d.hbuf; g.ldh = imax; g.ybuf = nullptr; g.H = d.H; g.status = d.status;
-    g.nstage = pick_stages(d.H);
-    if (!g.nstage) return GSB_ERR_UNSUPPORTED;
-    size_t smem = decode_smem_bytes(d.H, g.nstage);
-    if (cudaFuncSetAttribute(decode_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
-        return GSB_ERR_CUDA;
-    decode_gemm_kernel<true><<<d.sm_count, kDecodeThreads, smem, s>>>(g);
+    // register-resident variant when the input dim is a multiple of 2048 (at most 3 x 2048)
+    const bool gu_reg = !d.force_smem_variant && d.H % 2048 == 0 && d.H / 2048 <= 3;
+    if (gu_reg) {
+        const int st = launch_reg<true>(g, d.H / 2048, d.sm_count, s);
+        if (st) return st;
+    } else {
+        g.nstage = pick_stages(d.H);
+        if (!g.nstage) return GSB_ERR_UNSUPPORTED;
+        const size_t smem = decode_smem_bytes(d.H, g.nstage);
+        if (cudaFuncSetAttribute(decode_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return GSB_ERR_CUDA;
+        decode_gemm_kernel<true><<<d.sm_count, kDecodeThreads, smem, s>>>(g);
+    }
     if (d.ev_gate_up) cudaEventRecord(d.ev_gate_up, s);
 
     DecodeKArgs w = g;
@@ -491,13 +753,19 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     w.bsrc = d.hbuf; w.ldb = imax; w.K = d.I; w.Ks = shared ? d.Is : d.I;
     w.units = d.H / 32; w.units_s = d.H / 32;
     w.hbuf = nullptr; w.ybuf = d.ybuf;
-    w.nstage = pick_stages(imax);
-    if (!w.nstage) return GSB_ERR_UNSUPPORTED;
-    smem = decode_smem_bytes(imax, w.nstage);
-    if (cudaFuncSetAttribute(decode_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
-        return GSB_ERR_CUDA;
-    decode_gemm_kernel<false><<<d.sm_count, kDecodeThreads, smem, s>>>(w);
+    const bool dn_reg = !d.force_smem_variant && d.I % 2048 == 0 && d.I / 2048 <= 3 && w.Ks == w.K;
+    if (dn_reg) {
+        const int st = launch_reg<false>(w, d.I / 2048, d.sm_count, s);
+        if (st) return st;
+    } else {
+        w.nstage = pick_stages(imax);
+        if (!w.nstage) return GSB_ERR_UNSUPPORTED;
+        const size_t smem = decode_smem_bytes(imax, w.nstage);
+        if (cudaFuncSetAttribute(decode_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return GSB_ERR_CUDA;
+        decode_gemm_kernel<false><<<d.sm_count, kDecodeThreads, smem, s>>>(w);
+    }
     if (d.ev_down) cudaEventRecord(d.ev_down, s);
 
     dim3 cgrid((unsigned)(((d.H >> 2) + 255) / 256), (unsigned)d.n);

@@ -18,10 +18,13 @@ constexpr int kChunkWeightBytes = 8192;
 constexpr int kChunkBytes = 8448;
 constexpr int kDecodeTokens = 8;  // token rows per work item of the decode kernels
 
+// from_scores: `logits` already holds sigmoid scores
 int launch_router_topk(const float* logits, const float* e_bias, int n, int E, int topk,
-                       int norm_topk, float routed_scale, int* ids, float* w, cudaStream_t s);
+                       int norm_topk, float routed_scale, int* ids, float* w, cudaStream_t s,
+                       bool from_scores = false);
+// scores (nullable): also store sigmoid(logit)
 int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n, int H, int E,
-                         float* logits, cudaStream_t s);
+                         float* logits, float* scores, cudaStream_t s);
 int launch_dispatch(const int* topk_ids, int n, int topk, int E, int* expert_offsets,
                     int* sorted_token_ids, int* sorted_row, int* slot_pos, cudaStream_t s);
 
@@ -79,6 +82,7 @@ struct DecodeArgs {
     int* status;
     float* out;
     int sm_count;
+    int force_smem_variant;  // 1: always use the shared-memory-activation variant (testing)
     cudaEvent_t ev_prep, ev_gate_up, ev_down;  // optional stage marks (null = none)
 };
 int launch_decode_layer(const DecodeArgs& a, cudaStream_t s);

@@ -171,8 +171,8 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int i = 0; i < kPfStages; ++i) { mbar_init(&full_a[i], 256); mbar_init(&full_b[i], 1); mbar_init(&empty[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 8); mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128); }
+        for (int i = 0; i < kPfStages; ++i) { mbar_init(&full_a[i], 8); mbar_init(&full_b[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 8); mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -279,7 +279,8 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
                 }
             }
             tc_fence_before();
-            mbar_arrive(&acc_empty[buf]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     } else if (warp >= 8) {
         // ------------- dequant: int4 chunk pieces -> swizzled fp16 A tile -------------
@@ -314,8 +315,9 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
                     const int c = tlb * 4 + j;         // 16-byte piece of the 128-byte row
                     *reinterpret_cast<uint4*>(arow + ((c ^ (R & 7)) << 4)) = dequant8(wq[j], s2);
                 }
-                fence_proxy_async();
-                mbar_arrive(&full_a[s]);
+                fence_proxy_async();   // this thread's stores, visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_a[s]);
                 if (kb8 == 7 || kb == t.nkb - 1) {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&q_empty[qs]);

@@ -58,7 +58,7 @@ int gsb_moe_route_static(const void* x_bf16, const void* router_w_bf16, const fl
     // array by an earlier call can leak into this one and nothing needs clearing
     st = gsb::launch_router_logits(reinterpret_cast<const __nv_bfloat16*>(x_bf16),
                                    reinterpret_cast<const __nv_bfloat16*>(router_w_bf16), n, hidden, E,
-                                   logits, s);
+                                   logits, nullptr, s);
     if (st) return st;
     return gsb::launch_router_topk(logits, e_bias, n, E, topk, norm_topk, routed_scale, topk_ids,
                                    topk_weights, s);

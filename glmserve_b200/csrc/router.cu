@@ -18,7 +18,9 @@ __device__ __forceinline__ float sigmoid_ref(float x) {
 }
 
 // One warp per token.  Lane l owns experts l, l+32, ...; NS = slots per lane.
-template <int NS>
+// FROM_SCORES: the input already holds sigmoid scores (written by the logits kernel's
+// epilogue with the same sigmoid_ref), so no transcendental is evaluated here.
+template <int NS, bool FROM_SCORES>
 __global__ void __launch_bounds__(128)
 router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ e_bias, int n,
                    int E, int topk, int norm_topk, float routed_scale, int* __restrict__ topk_ids,
@@ -32,7 +34,7 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ e
     for (int j = 0; j < NS; ++j) {
         const int e = lane + (j << 5);
         if (e < E) {
-            const float sc = sigmoid_ref(lt[e]);
+            const float sc = FROM_SCORES ? lt[e] : sigmoid_ref(lt[e]);
             score[j] = sc;
             key[j] = __fadd_rn(sc, e_bias ? e_bias[e] : 0.0f);
         } else {
@@ -77,16 +79,15 @@ router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ e
 }
 
 int launch_router_topk(const float* logits, const float* e_bias, int n, int E, int topk,
-                       int norm_topk, float routed_scale, int* ids, float* w, cudaStream_t s) {
+                       int norm_topk, float routed_scale, int* ids, float* w, cudaStream_t s,
+                       bool from_scores) {
     if (n == 0) return GSB_OK;
     const int warps = 4;
     const unsigned grid = (unsigned)((n + warps - 1) / warps);
-    if (E <= 256)
-        router_topk_kernel<8><<<grid, warps * 32, 0, s>>>(logits, e_bias, n, E, topk, norm_topk,
-                                                         routed_scale, ids, w);
-    else
-        router_topk_kernel<32><<<grid, warps * 32, 0, s>>>(logits, e_bias, n, E, topk, norm_topk,
-                                                          routed_scale, ids, w);
+#define GSB_TOPK(NS, FS) router_topk_kernel<NS, FS><<<grid, warps * 32, 0, s>>>(logits, e_bias, n, E, topk, norm_topk, routed_scale, ids, w)
+    if (E <= 256) { if (from_scores) GSB_TOPK(8, true); else GSB_TOPK(8, false); }
+    else { if (from_scores) GSB_TOPK(32, true); else GSB_TOPK(32, false); }
+#undef GSB_TOPK
     return launch_status();
 }
 
@@ -145,10 +146,115 @@ router_logits_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     }
 }
 
+// Tensor-core form for input dims that are multiples of 256: mma.sync m16n8k16 (bf16 in,
+// fp32 accumulate) with 16 experts as M and 8 tokens as N.  Both operands come straight from
+// global memory as 16-byte loads: lane (g,t) reads columns 8t..8t+7 of every 32-column block
+// of expert rows g, g+8 and of token g, and the two k16 steps of the block use the first and
+// second half of those 16 bytes - the k index of an mma is only a label, so any assignment
+// of columns works as long as A and B use the same one.
+//   KSPLIT = 8, NT = 1 (n <= 128): the 8 warps of a block split the input dim and their
+//     partial tiles are added in warp order through shared memory -> many small blocks.
+//   KSPLIT = 1, NT = 4: a warp owns 16 experts x 32 tokens over the whole input dim.
+// The result for a (token, expert) depends only on the variant, never on n or the grid.
+// The epilogue also stores sigmoid(logit) (scores, nullable) for the fused top-k.
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                               uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT, int KSPLIT>
+__global__ void __launch_bounds__(256)
+router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr,
+                         int n, int H, int E, float* __restrict__ logits, float* __restrict__ scores) {
+    __shared__ float red[KSPLIT > 1 ? 8 * 4 * 32 : 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int egroup = KSPLIT > 1 ? blockIdx.x : blockIdx.x * 8 + warp;
+    const int e0 = egroup * 16;
+    const int t0 = blockIdx.y * (8 * NT);
+    const int kslice = H / KSPLIT;
+    const int kbeg = KSPLIT > 1 ? warp * kslice : 0;
+    const bool ra_ok = e0 + g < E, rb_ok = e0 + g + 8 < E;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const uint4* pa = reinterpret_cast<const uint4*>(wr + (size_t)(ra_ok ? e0 + g : 0) * H + kbeg) + t;
+    const uint4* pb = reinterpret_cast<const uint4*>(wr + (size_t)(rb_ok ? e0 + g + 8 : 0) * H + kbeg) + t;
+    const uint4* px[NT];
+    bool x_ok[NT];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+        const int tok = t0 + i * 8 + g;
+        x_ok[i] = tok < n;
+        px[i] = reinterpret_cast<const uint4*>(x + (size_t)(x_ok[i] ? tok : 0) * H + kbeg) + t;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    const int iters = kslice >> 5;
+    if (e0 < E) {
+#pragma unroll 4
+        for (int it = 0; it < iters; ++it) {
+            const uint4 va = ra_ok ? __ldg(pa + it * 4) : zero;
+            const uint4 vb = rb_ok ? __ldg(pb + it * 4) : zero;
+#pragma unroll
+            for (int i = 0; i < NT; ++i) {
+                const uint4 vx = x_ok[i] ? __ldg(px[i] + it * 4) : zero;
+                mma_bf16_16816(acc[i], va.x, vb.x, va.y, vb.y, vx.x, vx.y);
+                mma_bf16_16816(acc[i], va.z, vb.z, va.w, vb.w, vx.z, vx.w);
+            }
+        }
+    }
+    if (KSPLIT > 1) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) red[(warp * 4 + c) * 32 + lane] = acc[0][c];
+        __syncthreads();
+        if (threadIdx.x < 128) {
+            const int c = threadIdx.x >> 5;   // lane keeps its (g,t); c = accumulator index
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) v += red[(w * 4 + c) * 32 + lane];
+            const int e = e0 + g + ((c >> 1) << 3), tok = t0 + 2 * t + (c & 1);
+            if (e < E && tok < n) {
+                logits[(size_t)tok * E + e] = v;
+                if (scores) scores[(size_t)tok * E + e] = sigmoid_ref(v);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int e = e0 + g + ((c >> 1) << 3), tok = t0 + i * 8 + 2 * t + (c & 1);
+                if (e < E && tok < n) {
+                    logits[(size_t)tok * E + e] = acc[i][c];
+                    if (scores) scores[(size_t)tok * E + e] = sigmoid_ref(acc[i][c]);
+                }
+            }
+    }
+}
+
+__global__ void sigmoid_scores_kernel(const float* __restrict__ logits, float* __restrict__ scores, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) scores[i] = sigmoid_ref(logits[i]);
+}
+
 int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n, int H, int E,
-                         float* logits, cudaStream_t s) {
+                         float* logits, float* scores, cudaStream_t s) {
     if (n == 0) return GSB_OK;
     if (H % 8 != 0) return GSB_ERR_UNSUPPORTED;
+    if (H % 256 == 0) {
+        if (n <= 128) {
+            dim3 grid((unsigned)((E + 15) / 16), (unsigned)((n + 7) / 8));
+            router_logits_mma_kernel<1, 8><<<grid, 256, 0, s>>>(x, wr, n, H, E, logits, scores);
+        } else {
+            dim3 grid((unsigned)((E + 127) / 128), (unsigned)((n + 31) / 32));
+            router_logits_mma_kernel<4, 1><<<grid, 256, 0, s>>>(x, wr, n, H, E, logits, scores);
+        }
+        return launch_status();
+    }
     constexpr int TT = 8;
     const size_t smem = (size_t)TT * H * 2;
     if (smem > 200 * 1024) return GSB_ERR_UNSUPPORTED;
@@ -158,6 +264,7 @@ int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n,
         return GSB_ERR_CUDA;
     dim3 grid((unsigned)((E + 7) / 8), (unsigned)((n + TT - 1) / TT));
     router_logits_kernel<TT><<<grid, 256, smem, s>>>(x, wr, n, H, E, logits);
+    if (scores) sigmoid_scores_kernel<<<(unsigned)(((int64_t)n * E + 255) / 256), 256, 0, s>>>(logits, scores, (int64_t)n * E);
     return launch_status();
 }
 

@@ -12,7 +12,7 @@ import torch
 
 from ._lib import MoeConfig, check, lib
 
-PATH_AUTO, PATH_DIRECT, PATH_DECODE, PATH_PREFILL = 0, 1, 2, 3
+PATH_AUTO, PATH_DIRECT, PATH_DECODE, PATH_PREFILL, PATH_DECODE_SMEM = 0, 1, 2, 3, 4
 
 
 def _p(t):

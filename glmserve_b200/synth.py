@@ -17,6 +17,7 @@ CONFIGS = {
     # name: H, E, topk, I, Is, group
     "tiny": dict(H=256, E=16, topk=4, I=128, Is=128, group=32),
     "mid": dict(H=1024, E=32, topk=8, I=512, Is=512, group=128),
+    "wide": dict(H=4096, E=8, topk=2, I=2048, Is=2048, group=128),
     "glm": dict(H=6144, E=256, topk=8, I=2048, Is=2048, group=128),
 }
 

@@ -211,7 +211,9 @@ enum {
                              not cover, else decode-shaped or prefill-shaped tile kernels */
     GSB_PATH_DIRECT = 1,  /* direct-layout SIMT kernels (any shape) */
     GSB_PATH_DECODE = 2,  /* bandwidth-bound split-K tile-stream kernels */
-    GSB_PATH_PREFILL = 3  /* tcgen05 grouped GEMM */
+    GSB_PATH_PREFILL = 3, /* tcgen05 grouped GEMM */
+    GSB_PATH_DECODE_SMEM = 4 /* decode kernels, forcing the variant that keeps activations in shared
+                                memory (the one used when an input dim is not a multiple of 2048) */
 };
 
 /* The whole layer, replacing the MoE branch of run_layer_step (src/model_gpu.cpp:1446-1495):

@@ -85,6 +85,19 @@ def test_mid_config_prefill_skewed_no_shared(dev):
     _check_layer(layer, L, x, dev, ops.PATH_PREFILL, "mid prefill skewed")
 
 
+@pytest.mark.parametrize("n", [1, 5, 33])
+def test_wide_config_register_resident_decode(dev, n):
+    """Input dims that are multiples of 2048 take the register-resident decode variant
+    (H=4096: two 2048-column stages per item; I=2048: one)."""
+    from glmserve_b200 import ops
+    L = make_layer_np(CONFIGS["wide"], seed=25)
+    layer = ops.MoELayer(layer_to_torch(L, dev))
+    x = make_x_np(n, L["H"], seed=60 + n)
+    a = _check_layer(layer, L, x, dev, ops.PATH_DECODE, f"wide decode n={n}")
+    b = _check_layer(layer, L, x, dev, ops.PATH_DECODE_SMEM, f"wide decode (smem variant) n={n}")
+    assert torch.equal(layer.forward(bf16_tensor(x, dev), path=ops.PATH_DECODE), a["out"])
+
+
 def test_mid_config_without_shared_expert_and_skew(dev):
     from glmserve_b200 import ops
     L = make_layer_np(CONFIGS["mid"], seed=22, shared=False, zipf_amplitude=0.1)
@@ -128,6 +141,9 @@ def test_glm_scale_decode(dev, glm_layer, n):
     assert_layer_close(out.cpu().numpy(), r["out"], f"glm decode n={n}")
     out2 = layer.forward(x, path=ops.PATH_DECODE)
     assert torch.equal(out, out2)
+    out3 = layer.forward(x, path=ops.PATH_DECODE_SMEM)
+    assert layer.status() == 0
+    assert_layer_close(out3.cpu().numpy(), r["out"], f"glm decode (smem variant) n={n}")
 
 
 def test_glm_scale_prefill(dev, glm_layer):
