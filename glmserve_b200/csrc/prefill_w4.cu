@@ -151,7 +151,8 @@ __device__ __forceinline__ PfTile pf_tile(const PrefillKArgs& a, int idx) {
 
 template <bool GU>
 __global__ void __launch_bounds__(kPfThreads, 1)
-prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tmap_b) {
+prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tmap_b64,
+                    const __grid_constant__ CUtensorMap tmap_b128, const __grid_constant__ CUtensorMap tmap_b256) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base_u32 = smem_u32(smem_raw);
     uint8_t* smem = smem_raw + ((1024u - (base_u32 & 1023u)) & 1023u);
@@ -171,7 +172,7 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int i = 0; i < kPfStages; ++i) { mbar_init(&full_a[i], 8); mbar_init(&full_b[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < kPfStages; ++i) { mbar_init(&full_a[i], 4); mbar_init(&full_b[i], 1); mbar_init(&empty[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 8); mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
         *abort_flag = 0;
         fence_barrier_init();
@@ -203,8 +204,11 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
                     }
                     const uint32_t s = kc % kPfStages, ph = (kc / kPfStages) & 1u;
                     if (!mbar_wait(&empty[s], ph ^ 1u, kPfWaitLimit)) { pf_timeout(a, abort_flag, 2); break; }
-                    mbar_arrive_expect_tx(&full_b[s], kBBytes);
-                    tma_load_2d(sB + s * kBBytes, &tmap_b, kb * 64, t.slot0, &full_b[s]);
+                    // the smallest box that covers the tile's rows: a ragged tile does not pull 256 rows
+                    const CUtensorMap* tm = t.nround <= 64 ? &tmap_b64 : (t.nround <= 128 ? &tmap_b128 : &tmap_b256);
+                    const uint32_t rows = t.nround <= 64 ? 64u : (t.nround <= 128 ? 128u : 256u);
+                    mbar_arrive_expect_tx(&full_b[s], rows * 128u);
+                    tma_load_2d(sB + s * kBBytes, tm, kb * 64, t.slot0, &full_b[s]);
                 }
             }
         }
@@ -284,16 +288,20 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
         }
     } else if (warp >= 8) {
         // ------------- dequant: int4 chunk pieces -> swizzled fp16 A tile -------------
+        // Two groups of four warps take alternate k-blocks, so each group has two MMA periods
+        // per k-block; a thread owns one row of the 128-row tile (both 32-column halves).
         const int d = tid - 256;                       // 0..255
-        const int uu = d >> 6, m = (d >> 5) & 1, h = (d >> 4) & 1, g = (d >> 1) & 7, tlb = d & 1;
-        const int R = uu * 32 + m * 16 + g + 8 * h;    // row of the 128-row tile (= TMEM lane)
-        uint32_t kc = 0, qc = 0;
+        const int grp = d >> 7;                        // 0: even k-blocks, 1: odd
+        const int R = d & 127;                         // row of the tile (= TMEM lane)
+        const int uu = R >> 5, m = (R >> 4) & 1, h = (R >> 3) & 1, g = R & 7;
+        uint32_t kc = grp, qc = 0;
         bool dead = false;
         for (int ti = blockIdx.x; ti < ntiles && !dead; ti += gridDim.x) {
             const PfTile t = pf_tile(a, ti);
             uint32_t qs = 0;
-            for (int kb = 0; kb < t.nkb; ++kb, ++kc) {
-                if ((kb & 7) == 0) {
+            for (int kb = grp; kb < t.nkb; kb += 2, kc += 2) {
+                const int kb8 = kb & 7;
+                if (kb8 == grp) {
                     qs = qc & 1u;
                     if (*abort_flag || !mbar_wait(&q_full[qs], (qc >> 1) & 1u, kPfWaitLimit)) {
                         if (!*abort_flag) pf_timeout(a, abort_flag, 6);
@@ -303,22 +311,21 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
                 }
                 const uint32_t s = kc % kPfStages, ph = (kc / kPfStages) & 1u;
                 if (!mbar_wait(&empty[s], ph ^ 1u, kPfWaitLimit)) { pf_timeout(a, abort_flag, 7); dead = true; break; }
-                const int kb8 = kb & 7, ks = kb8 >> 1, tq = ((kb8 & 1) << 1) + tlb;
+                const int ks = kb8 >> 1, tq0 = grp << 1;
                 const uint8_t* chunk = sQ + qs * kQBytes + uu * kChunkBytes;
-                const uint4 wv = *reinterpret_cast<const uint4*>(chunk + (ks * 2 + m) * 1024 + h * 512 + (g * 4 + tq) * 16);
+                const uint4* piece = reinterpret_cast<const uint4*>(chunk + (ks * 2 + m) * 1024 + h * 512 + (g * 4 + tq0) * 16);
+                const uint4 wv0 = piece[0], wv1 = piece[1];
                 const __half sc = reinterpret_cast<const __half*>(chunk + kChunkWeightBytes)[(ks * 2 + m) * 16 + g + 8 * h];
                 const __half2 s2 = __half2half2(sc);
-                uint8_t* arow = sA + s * kABytes + (R >> 3) * 1024 + (R & 7) * 128;
-                const uint32_t wq[4] = {wv.x, wv.y, wv.z, wv.w};
+                uint8_t* arow = sA + s * kABytes + (R >> 3) * 1024 + g * 128;
+                const uint32_t wq[8] = {wv0.x, wv0.y, wv0.z, wv0.w, wv1.x, wv1.y, wv1.z, wv1.w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int c = tlb * 4 + j;         // 16-byte piece of the 128-byte row
-                    *reinterpret_cast<uint4*>(arow + ((c ^ (R & 7)) << 4)) = dequant8(wq[j], s2);
-                }
+                for (int c = 0; c < 8; ++c)             // c = 16-byte piece of the 128-byte row
+                    *reinterpret_cast<uint4*>(arow + ((c ^ g) << 4)) = dequant8(wq[c], s2);
                 fence_proxy_async();   // this thread's stores, visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&full_a[s]);
-                if (kb8 == 7 || kb == t.nkb - 1) {
+                if (kb8 >= 6) {        // this group's last k-block of the int4 super-stage
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&q_empty[qs]);
                 }
@@ -465,12 +472,12 @@ EncodeTiledFn encode_fn() {
 }
 
 // fp16 [rows, cols] row-major; box = 64 columns x kBN rows, 128-byte swizzle.
-int make_tmap(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld) {
+int make_tmap(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return GSB_ERR_CUDA;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)kBN};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                           estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -506,11 +513,14 @@ int launch_prefill_layer(const PrefillArgs& d, cudaStream_t s) {
     if (shared) tile_append_shared_kernel<<<1, 256, 0, s>>>(d.expert_offsets, d.E, d.n, P, d.H / 128, d.H / 128, d.tiles_dn);
     if (d.ev_prep) cudaEventRecord(d.ev_prep, s);
 
-    CUtensorMap tm_x, tm_h;
-    int st = make_tmap(&tm_x, d.xs, rows, d.H, d.H);
-    if (st) return st;
-    st = make_tmap(&tm_h, d.hbuf, rows, imax, imax);
-    if (st) return st;
+    CUtensorMap tm_x[3], tm_h[3];
+    const int boxes[3] = {64, 128, 256};
+    for (int i = 0; i < 3; ++i) {
+        int st = make_tmap(&tm_x[i], d.xs, rows, d.H, d.H, boxes[i]);
+        if (st) return st;
+        st = make_tmap(&tm_h[i], d.hbuf, rows, imax, imax, boxes[i]);
+        if (st) return st;
+    }
 
     PrefillKArgs g{};
     g.packed = reinterpret_cast<const uint8_t*>(d.gate_up_packed);
@@ -519,7 +529,7 @@ int launch_prefill_layer(const PrefillArgs& d, cudaStream_t s) {
     g.hbuf = d.hbuf; g.ldh = imax; g.ybuf = nullptr; g.H = d.H; g.status = d.status;
     if (cudaFuncSetAttribute(prefill_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem) != cudaSuccess)
         return GSB_ERR_CUDA;
-    prefill_gemm_kernel<true><<<d.sm_count, kPfThreads, kPfSmem, s>>>(g, tm_x);
+    prefill_gemm_kernel<true><<<d.sm_count, kPfThreads, kPfSmem, s>>>(g, tm_x[0], tm_x[1], tm_x[2]);
     if (d.ev_gate_up) cudaEventRecord(d.ev_gate_up, s);
 
     PrefillKArgs w = g;
@@ -529,7 +539,7 @@ int launch_prefill_layer(const PrefillArgs& d, cudaStream_t s) {
     w.hbuf = nullptr; w.ybuf = d.ybuf;
     if (cudaFuncSetAttribute(prefill_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem) != cudaSuccess)
         return GSB_ERR_CUDA;
-    prefill_gemm_kernel<false><<<d.sm_count, kPfThreads, kPfSmem, s>>>(w, tm_h);
+    prefill_gemm_kernel<false><<<d.sm_count, kPfThreads, kPfSmem, s>>>(w, tm_h[0], tm_h[1], tm_h[2]);
     if (d.ev_down) cudaEventRecord(d.ev_down, s);
 
     dim3 cgrid((unsigned)(((d.H >> 3) + 255) / 256), (unsigned)d.n);
