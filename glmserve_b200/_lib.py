@@ -29,7 +29,7 @@ class MoeConfig(C.Structure):
                 ("sg_q", C.c_void_p), ("sg_sc", C.c_void_p), ("su_q", C.c_void_p), ("su_sc", C.c_void_p),
                 ("sd_q", C.c_void_p), ("sd_sc", C.c_void_p), ("gate_up_packed", C.c_void_p),
                 ("down_packed", C.c_void_p), ("shared_gate_up_packed", C.c_void_p),
-                ("shared_down_packed", C.c_void_p)]
+                ("shared_down_packed", C.c_void_p), ("ep_size", C.c_int), ("ep_rank", C.c_int)]
 
 
 _lib = None
@@ -51,6 +51,12 @@ def lib():
         L.gsb_moe_layer_create.argtypes = [C.POINTER(MoeConfig), C.POINTER(C.c_void_p)]
         L.gsb_moe_layer_destroy.argtypes = [C.c_void_p]
         L.gsb_moe_layer_destroy.restype = None
+        L.gsb_comm_heap.restype = C.c_void_p
+        L.gsb_comm_heap_bytes.restype = C.c_size_t
+        L.gsb_comm_allreduce_reserve.restype = C.c_size_t
+        L.gsb_moe_ep_heap_bytes.restype = C.c_size_t
+        L.gsb_moe_ep_workspace_bytes.restype = C.c_size_t
+        L.gsb_comm_destroy.restype = None
         _lib = L
     return _lib
 

@@ -2,8 +2,7 @@
 // Declarations and per-entry documentation: include/glmserve_b200.h.
 #include <new>
 
-#include "common.cuh"
-#include "launchers.cuh"
+#include "internal.cuh"
 
 using namespace gsb;
 
@@ -14,16 +13,6 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace
-
-struct gsb_moe_layer {
-    gsb_moe_config cfg;
-    bool tiles_ok;       // shapes fit the tile-stream kernels and prepacked weights are given
-    int sm_count;
-    // stage profiler (counterpart of StageProf, src/model_gpu.cpp:328-388 of the reference)
-    cudaEvent_t* prof_ev = nullptr;   // [prof_sets][GSB_N_STAGES + 1]
-    int prof_sets = 0;
-    int prof_used = 0;
-};
 
 namespace {
 
@@ -242,6 +231,7 @@ int gsb_moe_layer_create(const gsb_moe_config* cfg, gsb_moe_layer** out) {
         c.shared_inter < 0)
         return GSB_ERR_INVALID_ARG;
     if (c.topk > c.n_experts || c.n_experts > 1024 || c.topk > 32) return GSB_ERR_UNSUPPORTED;
+    if (c.ep_size > 1 && (c.n_experts % c.ep_size || c.ep_rank < 0 || c.ep_rank >= c.ep_size)) return GSB_ERR_INVALID_ARG;
     if (c.hidden % c.group || c.moe_inter % c.group || c.hidden % 8 || c.moe_inter % 8 || c.group % 8)
         return GSB_ERR_UNSUPPORTED;
     if (c.shared_inter && (c.shared_inter % c.group || c.shared_inter % 8)) return GSB_ERR_UNSUPPORTED;
@@ -289,6 +279,7 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
                           void* workspace, size_t workspace_bytes, int path, float* logits_out,
                           int* ids_out, float* weights_out, void* stream) {
     if (!layer || n < 0) return GSB_ERR_INVALID_ARG;
+    if (layer->cfg.ep_size > 1) return GSB_ERR_UNSUPPORTED;  // expert-parallel layers: gsb_moe_layer_forward_ep
     if (n == 0) return GSB_OK;
     if (!x_bf16 || !out || !workspace || !aligned(workspace, 256) || !aligned(x_bf16, 16))
         return GSB_ERR_INVALID_ARG;

@@ -1,0 +1,141 @@
+// Expert-parallel forward of one MoE layer over the GPUs of one box (host orchestration).
+// The exchange kernels live in comm.cu, the GEMMs in prefill_w4.cu.
+#include "internal.cuh"
+
+using namespace gsb;
+
+namespace {
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct EpHeap { size_t recv_x, ybuf, total; };
+EpHeap ep_heap(const gsb_moe_config& c, int n, int recv_cap) {
+    EpHeap h{};
+    size_t off = 0;
+    h.recv_x = off; off = align_up(off + (size_t)recv_cap * c.hidden * sizeof(__half), 1024);
+    h.ybuf = off;   off = align_up(off + ((size_t)n * c.topk + n) * c.hidden * sizeof(__half), 1024);
+    h.total = off;
+    return h;
+}
+
+struct EpWs {
+    int* status; float* logits; float* scores; int* ids; float* w; int* expert_offsets; int* sorted_tok;
+    int* sorted_row; int* slot_pos; int* sorted_expert; int* recv_offsets; int* send_base; void** ydst;
+    int* recv_total; int* tiles_gu; int* tiles_dn; int* tiles_sh_gu; int* tiles_sh_dn;
+    __half* hbuf; __half* xs_local; __half* hbuf_sh;
+    size_t total;
+};
+EpWs ep_carve(const gsb_moe_config& c, int n, int recv_cap, void* base) {
+    EpWs ws{};
+    const size_t P = (size_t)n * c.topk;
+    const int El = c.n_experts / (c.ep_size > 0 ? c.ep_size : 1);
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        size_t o = off;
+        off = align_up(off + bytes, 256);
+        return base ? reinterpret_cast<char*>(base) + o : nullptr;
+    };
+    ws.status = reinterpret_cast<int*>(take(64 * sizeof(int)));
+    ws.logits = reinterpret_cast<float*>(take((size_t)n * c.n_experts * sizeof(float)));
+    ws.scores = reinterpret_cast<float*>(take((size_t)n * c.n_experts * sizeof(float)));
+    ws.ids = reinterpret_cast<int*>(take(P * sizeof(int)));
+    ws.w = reinterpret_cast<float*>(take(P * sizeof(float)));
+    ws.expert_offsets = reinterpret_cast<int*>(take((size_t)(c.n_experts + 1) * sizeof(int)));
+    ws.sorted_tok = reinterpret_cast<int*>(take(P * sizeof(int)));
+    ws.sorted_row = reinterpret_cast<int*>(take(P * sizeof(int)));
+    ws.slot_pos = reinterpret_cast<int*>(take(P * sizeof(int)));
+    ws.sorted_expert = reinterpret_cast<int*>(take(P * sizeof(int)));
+    ws.recv_offsets = reinterpret_cast<int*>(take((size_t)(El + 1) * sizeof(int)));
+    ws.send_base = reinterpret_cast<int*>(take((size_t)c.n_experts * sizeof(int)));
+    ws.ydst = reinterpret_cast<void**>(take((size_t)recv_cap * sizeof(void*)));
+    ws.recv_total = reinterpret_cast<int*>(take(sizeof(int)));
+    const size_t tb = prefill_tile_bytes(recv_cap / (c.topk > 0 ? c.topk : 1) + 1, c.topk, El, c.hidden,
+                                         c.moe_inter > c.shared_inter ? c.moe_inter : c.shared_inter);
+    ws.tiles_gu = reinterpret_cast<int*>(take(tb));
+    ws.tiles_dn = reinterpret_cast<int*>(take(tb));
+    const size_t tbs = prefill_tile_bytes(n, 1, 1, c.hidden, c.shared_inter > 0 ? c.shared_inter : 64);
+    ws.tiles_sh_gu = reinterpret_cast<int*>(take(tbs));
+    ws.tiles_sh_dn = reinterpret_cast<int*>(take(tbs));
+    ws.hbuf = reinterpret_cast<__half*>(take((size_t)recv_cap * c.moe_inter * sizeof(__half)));
+    ws.xs_local = reinterpret_cast<__half*>(take((size_t)n * c.hidden * sizeof(__half)));
+    ws.hbuf_sh = reinterpret_cast<__half*>(take((size_t)n * (c.shared_inter > 0 ? c.shared_inter : 1) * sizeof(__half)));
+    ws.total = off;
+    return ws;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t gsb_moe_ep_heap_bytes(const gsb_moe_layer* layer, int n_tokens, int recv_cap) {
+    if (!layer || n_tokens < 0 || recv_cap < 0) return 0;
+    return ep_heap(layer->cfg, n_tokens, recv_cap).total;
+}
+
+size_t gsb_moe_ep_workspace_bytes(const gsb_moe_layer* layer, int n_tokens, int recv_cap) {
+    if (!layer || n_tokens < 0 || recv_cap < 0) return 0;
+    return ep_carve(layer->cfg, n_tokens, recv_cap, nullptr).total;
+}
+
+int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, int n, float* out,
+                             void* workspace, size_t workspace_bytes, size_t heap_offset, int recv_cap,
+                             int* ids_out, void* stream) {
+    if (!layer || !comm || n < 0 || recv_cap <= 0) return GSB_ERR_INVALID_ARG;
+    const gsb_moe_config& c = layer->cfg;
+    if (c.ep_size != comm->world || c.ep_rank != comm->rank || c.ep_size < 1) return GSB_ERR_INVALID_ARG;
+    if (c.n_experts % c.ep_size || !layer->tiles_ok) return GSB_ERR_UNSUPPORTED;
+    if (n > 0 && (!x_bf16 || !out)) return GSB_ERR_INVALID_ARG;
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || (heap_offset & 1023)) return GSB_ERR_INVALID_ARG;
+    EpWs ws = ep_carve(c, n, recv_cap, workspace);
+    if (workspace_bytes < ws.total) return GSB_ERR_WORKSPACE;
+    const EpHeap hp = ep_heap(c, n, recv_cap);
+    if (heap_offset + hp.total > comm->heap_bytes) return GSB_ERR_WORKSPACE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
+    const int E = c.n_experts, El = E / c.ep_size, P = n * c.topk;
+    uint8_t* heap = comm->local + kCtrlBytes + heap_offset;
+    __half* recv_x = reinterpret_cast<__half*>(heap + hp.recv_x);
+    __half* ybuf = reinterpret_cast<__half*>(heap + hp.ybuf);
+
+    if (cudaMemsetAsync(ws.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
+    int st = GSB_OK;
+    if (n > 0) {
+        st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden, E, ws.logits, ws.scores, s);
+        if (st) return st;
+        st = launch_router_topk(ws.scores, c.e_bias, n, E, c.topk, c.norm_topk, c.routed_scale, ws.ids, ws.w, s, true);
+        if (st) return st;
+        if (ids_out && cudaMemcpyAsync(ids_out, ws.ids, (size_t)P * sizeof(int), cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+            return GSB_ERR_CUDA;
+    }
+    st = launch_dispatch(ws.ids, n, c.topk, E, ws.expert_offsets, ws.sorted_tok, ws.sorted_row, ws.slot_pos, s);
+    if (st) return st;
+    // counts -> plan -> push rows to their owners -> signal
+    st = comm_ep_exchange(comm, x, ws.expert_offsets, ws.sorted_tok, P, E, c.hidden, ws.sorted_expert,
+                          ws.recv_offsets, ws.send_base, ws.ydst, heap_offset + hp.ybuf, (int)sizeof(__half),
+                          heap_offset + hp.recv_x, recv_cap, ws.recv_total, s);
+    if (st) return st;
+
+    PrefillEpArgs a{};
+    a.gate_up_packed = c.gate_up_packed; a.down_packed = c.down_packed;
+    a.shared_gate_up_packed = c.shared_gate_up_packed; a.shared_down_packed = c.shared_down_packed;
+    a.H = c.hidden; a.I = c.moe_inter; a.Is = c.shared_inter; a.El = El;
+    a.recv_offsets = ws.recv_offsets; a.recv_x = recv_x; a.recv_cap = recv_cap; a.hbuf = ws.hbuf;
+    a.ydst = reinterpret_cast<__half* const*>(ws.ydst); a.tiles_gu = ws.tiles_gu; a.tiles_dn = ws.tiles_dn;
+    a.x = x; a.n = n; a.xs_local = ws.xs_local; a.hbuf_sh = ws.hbuf_sh; a.y_shared = ybuf + (size_t)P * c.hidden;
+    a.tiles_sh_gu = ws.tiles_sh_gu; a.tiles_sh_dn = ws.tiles_sh_dn; a.status = ws.status; a.sm_count = layer->sm_count;
+
+    // the shared expert needs only local tokens: it runs while the peers' rows are in flight
+    if (n > 0) { st = launch_prefill_ep_shared(a, s); if (st) return st; }
+    st = comm_launch_wait(comm, kChDispatch, s);
+    if (st) return st;
+    st = launch_prefill_ep_routed(a, s);
+    if (st) return st;
+    ++comm->seq[kChCombine];
+    st = comm_launch_signal(comm, kChCombine, s);
+    if (st) return st;
+    st = comm_launch_wait(comm, kChCombine, s);
+    if (st) return st;
+    return launch_combine_h(ybuf, ws.slot_pos, ws.w, n, c.topk, c.hidden, P, c.shared_inter > 0 ? 1 : 0, out, s);
+}
+
+}  // extern "C"

@@ -112,4 +112,30 @@ struct PrefillArgs {
 };
 int launch_prefill_layer(const PrefillArgs& a, cudaStream_t s);
 
+// Expert-parallel pieces of the tcgen05 path (see comm.cu / ep.cu for the exchange).
+struct PrefillEpArgs {
+    const void* gate_up_packed;         // resident (local) experts
+    const void* down_packed;
+    const void* shared_gate_up_packed;
+    const void* shared_down_packed;
+    int H, I, Is, El;                   // El = experts resident on this GPU
+    const int* recv_offsets;            // [El + 1] rows received per local expert (device)
+    const __half* recv_x;               // [recv_cap, H] received activations (fp16)
+    int recv_cap;
+    __half* hbuf;                       // [recv_cap, I]
+    __half* const* ydst;                // [recv_cap] where each received row's output goes
+    int* tiles_gu; int* tiles_dn;
+    const __nv_bfloat16* x; int n;      // this GPU's own tokens (shared expert)
+    __half* xs_local;                   // [n, H]
+    __half* hbuf_sh;                    // [n, Is]
+    __half* y_shared;                   // [n, H]
+    int* tiles_sh_gu; int* tiles_sh_dn;
+    int* status;
+    int sm_count;
+};
+int launch_prefill_ep_shared(const PrefillEpArgs& a, cudaStream_t s);
+int launch_prefill_ep_routed(const PrefillEpArgs& a, cudaStream_t s);
+int launch_combine_h(const __half* ybuf, const int* slot_pos, const float* topk_w, int n, int topk, int H,
+                     int P, int has_shared, float* out, cudaStream_t s);
+
 }  // namespace gsb

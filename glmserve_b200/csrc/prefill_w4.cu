@@ -42,6 +42,8 @@ struct PrefillKArgs {
     int E;
     __half* hbuf; int ldh;   // gate/up output, natural feature order
     __half* ybuf; int H;     // down output [slots, H]
+    __half* const* ydst;     // optional per-row output pointers (expert parallel: rows live on the
+                             // token's home GPU and are stored there over NVLink); overrides ybuf
     int* status;
 };
 
@@ -277,8 +279,10 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int n = c0 + j;
-                        if (n < t.ntok)
-                            a.ybuf[(int64_t)(t.slot0 + n) * a.H + feat] = __float2half_rn(__uint_as_float(r[j]));
+                        if (n < t.ntok) {
+                            __half* yrow = a.ydst ? a.ydst[t.slot0 + n] : a.ybuf + (int64_t)(t.slot0 + n) * a.H;
+                            yrow[feat] = __float2half_rn(__uint_as_float(r[j]));
+                        }
                     }
                 }
             }
@@ -485,6 +489,17 @@ int make_tmap(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int6
     return r == CUDA_SUCCESS ? GSB_OK : GSB_ERR_CUDA;
 }
 
+// Tile list holding only shared-expert tiles over n token rows starting at row 0.
+__global__ void tile_shared_only_kernel(int E_marker, int n, int row_blocks, int* __restrict__ tiles) {
+    const int nsh = (n + kBN - 1) / kBN;
+    if (threadIdx.x == 0) { tiles[0] = nsh * row_blocks; tiles[1] = tiles[2] = tiles[3] = 0; }
+    int4* out = reinterpret_cast<int4*>(tiles + kTileHeader);
+    for (int i = threadIdx.x; i < nsh * row_blocks; i += blockDim.x) {
+        const int j = i / row_blocks, rb = i - j * row_blocks;
+        out[i] = make_int4(E_marker, j * kBN, min(kBN, n - j * kBN), rb);
+    }
+}
+
 constexpr size_t kPfSmem = 1024 + kPfStages * (kABytes + kBBytes) + 2 * kQBytes + 256;
 
 }  // namespace
@@ -494,6 +509,69 @@ size_t prefill_tile_bytes(int n, int topk, int E, int H, int I) {
     const size_t tok_tiles = (size_t)E + P / kBN + (size_t)n / kBN + 2;
     const size_t rbmax = (size_t)((H / 128 > I / 64) ? H / 128 : I / 64);
     return (kTileHeader + 4 * tok_tiles * rbmax) * sizeof(int);
+}
+
+static int run_gemm_pair(const PrefillKArgs& g_in, const PrefillKArgs& w_in, const void* xbase, int64_t xrows,
+                         int H, const void* hbase, int64_t hrows, int ldh, int sm_count, cudaStream_t s,
+                         cudaEvent_t ev_mid) {
+    CUtensorMap tm_x[3], tm_h[3];
+    const int boxes[3] = {64, 128, 256};
+    for (int i = 0; i < 3; ++i) {
+        int st = make_tmap(&tm_x[i], xbase, xrows, H, H, boxes[i]);
+        if (st) return st;
+        st = make_tmap(&tm_h[i], hbase, hrows, ldh, ldh, boxes[i]);
+        if (st) return st;
+    }
+    if (cudaFuncSetAttribute(prefill_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem) != cudaSuccess)
+        return GSB_ERR_CUDA;
+    prefill_gemm_kernel<true><<<sm_count, kPfThreads, kPfSmem, s>>>(g_in, tm_x[0], tm_x[1], tm_x[2]);
+    if (ev_mid) cudaEventRecord(ev_mid, s);
+    prefill_gemm_kernel<false><<<sm_count, kPfThreads, kPfSmem, s>>>(w_in, tm_h[0], tm_h[1], tm_h[2]);
+    return launch_status();
+}
+
+// Expert parallel, shared expert: this GPU's own tokens through the shared expert, output rows
+// into y_shared [n, H] (the tail of the local per-slot row buffer).
+int launch_prefill_ep_shared(const PrefillEpArgs& d, cudaStream_t s) {
+    if (d.Is <= 0) return GSB_OK;
+    gather_x_kernel<<<(unsigned)(((int64_t)d.n * (d.H >> 3) + 255) / 256), 256, 0, s>>>(d.x, nullptr, 0, d.n, d.H, 1, d.xs_local);
+    tile_shared_only_kernel<<<1, 256, 0, s>>>(d.El, d.n, d.Is / 64, d.tiles_sh_gu);
+    tile_shared_only_kernel<<<1, 256, 0, s>>>(d.El, d.n, d.H / 128, d.tiles_sh_dn);
+    PrefillKArgs g{};
+    g.packed = nullptr; g.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_gate_up_packed);
+    g.tiles = d.tiles_sh_gu; g.K = d.H; g.Ks = d.H; g.units = d.I / 16; g.units_s = d.Is / 16; g.E = d.El;
+    g.hbuf = d.hbuf_sh; g.ldh = d.Is; g.ybuf = nullptr; g.H = d.H; g.ydst = nullptr; g.status = d.status;
+    PrefillKArgs w = g;
+    w.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_down_packed);
+    w.tiles = d.tiles_sh_dn; w.K = d.I; w.Ks = d.Is; w.units = d.H / 32; w.units_s = d.H / 32;
+    w.hbuf = nullptr; w.ybuf = d.y_shared;
+    return run_gemm_pair(g, w, d.xs_local, d.n, d.H, d.hbuf_sh, d.n, d.Is, d.sm_count, s, nullptr);
+}
+
+// Expert parallel, routed experts: the rows this GPU received (grouped by local expert in
+// recv_x) through its resident experts; the down kernel's epilogue stores every output row
+// straight to the GPU that owns the token (ydst) - compute and the return all-to-all in one kernel.
+int launch_prefill_ep_routed(const PrefillEpArgs& d, cudaStream_t s) {
+    tile_build_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, 0, 0, 0, d.I / 64, 1, d.tiles_gu);
+    tile_build_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, 0, 0, 0, d.H / 128, 1, d.tiles_dn);
+    PrefillKArgs g{};
+    g.packed = reinterpret_cast<const uint8_t*>(d.gate_up_packed); g.shared_packed = nullptr;
+    g.tiles = d.tiles_gu; g.K = d.H; g.Ks = d.H; g.units = d.I / 16; g.units_s = 1; g.E = d.El;
+    g.hbuf = d.hbuf; g.ldh = d.I; g.ybuf = nullptr; g.H = d.H; g.ydst = nullptr; g.status = d.status;
+    PrefillKArgs w = g;
+    w.packed = reinterpret_cast<const uint8_t*>(d.down_packed);
+    w.tiles = d.tiles_dn; w.K = d.I; w.Ks = d.I; w.units = d.H / 32; w.units_s = 1;
+    w.hbuf = nullptr; w.ybuf = nullptr; w.ydst = d.ydst;
+    return run_gemm_pair(g, w, d.recv_x, d.recv_cap, d.H, d.hbuf, d.recv_cap, d.I, d.sm_count, s, nullptr);
+}
+
+int launch_combine_h(const __half* ybuf, const int* slot_pos, const float* topk_w, int n, int topk, int H,
+                     int P, int has_shared, float* out, cudaStream_t s) {
+    if (n == 0) return GSB_OK;
+    dim3 cgrid((unsigned)(((H >> 3) + 255) / 256), (unsigned)n);
+    combine_h_kernel<<<cgrid, 256, 0, s>>>(ybuf, slot_pos, topk_w, n, topk, H, P, has_shared, out);
+    return launch_status();
 }
 
 int launch_prefill_layer(const PrefillArgs& d, cudaStream_t s) {

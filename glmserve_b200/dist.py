@@ -1,0 +1,145 @@
+"""One process per GPU: the NVLink peer-memory communicator of the C ABI (gsb_comm_*), driven
+through torch.distributed only for the one-time exchange of IPC handles.  Also host mirrors
+of the expert-parallel plan and of the tensor-parallel shard rule, used by the CPU tests.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from ._lib import check, lib
+
+
+class Comm:
+    """Symmetric heap + flags over all ranks of the default process group (one box)."""
+
+    def __init__(self, heap_bytes: int, allreduce_max_count: int = 0):
+        import torch
+        import torch.distributed as dist
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        hb = lib().gsb_comm_handle_bytes()
+        handle = (C.c_ubyte * hb)()
+        h = C.c_void_p()
+        check(lib().gsb_comm_create(self.rank, self.world, C.c_size_t(heap_bytes), handle, C.byref(h)), "comm_create")
+        self._h = h
+        dev = torch.device("cuda", torch.cuda.current_device())
+        mine = torch.tensor(list(bytes(handle)), dtype=torch.uint8, device=dev)
+        allh = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(allh, mine)
+        buf = b"".join(bytes(t.cpu().numpy().tobytes()) for t in allh)
+        self._handles = (C.c_ubyte * len(buf)).from_buffer_copy(buf)
+        st = lib().gsb_comm_open(self._h, self._handles)
+        ok = torch.tensor([1 if st == 0 else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)          # all-or-none, like the reference's bring-up
+        if int(ok) == 0:
+            self.close()
+            raise RuntimeError("peer memory could not be opened on every rank")
+        self.reserved = int(lib().gsb_comm_allreduce_reserve(self._h, C.c_int64(allreduce_max_count)))
+        dist.barrier()
+
+    def heap_bytes(self) -> int:
+        return int(lib().gsb_comm_heap_bytes(self._h))
+
+    def allreduce_sum(self, t):
+        """In-place sum of a contiguous float32 CUDA tensor over all ranks (rank order)."""
+        import torch
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.is_cuda
+        check(lib().gsb_comm_allreduce_sum(self._h, C.c_void_p(t.data_ptr()), C.c_int64(t.numel()),
+                                           C.c_void_p(torch.cuda.current_stream().cuda_stream)), "allreduce_sum")
+        return t
+
+    def allreduce_sum_rows(self, t):
+        """Row-by-row form (include/nccl_comm.hpp:53-59 of the reference); same bits as one call."""
+        for r in range(t.shape[0]):
+            self.allreduce_sum(t[r])
+        return t
+
+    def barrier(self):
+        import torch
+        check(lib().gsb_comm_barrier(self._h, C.c_void_p(torch.cuda.current_stream().cuda_stream)), "comm_barrier")
+
+    def status(self) -> int:
+        import torch
+        torch.cuda.current_stream().synchronize()
+        return int(lib().gsb_comm_status(self._h))
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().gsb_comm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+
+# ---- host mirrors (numpy) ------------------------------------------------------------------
+
+def ep_plan_np(cnt: np.ndarray, rank: int):
+    """Mirror of ep_plan_kernel.  cnt[src, e] = rows rank `src` routes to expert e.
+    Returns (recv_offsets[El+1], send_base[E], src_pos[world, E]): the receive layout of `rank`
+    (local expert major, then source rank), where this rank's rows for expert e start on the
+    owner's receive buffer, and where expert e's rows start in each source's sorted order."""
+    world, E = cnt.shape
+    El = E // world
+    tot = cnt.sum(axis=0)
+    base = np.zeros(E, np.int64)
+    for o in range(world):
+        base[o * El:(o + 1) * El] = np.concatenate([[0], np.cumsum(tot[o * El:(o + 1) * El])[:-1]])
+    send_base = base + cnt[:rank].sum(axis=0)
+    recv_offsets = np.concatenate([base[rank * El:(rank + 1) * El], [base[(rank + 1) * El - 1] + tot[(rank + 1) * El - 1]]])
+    src_pos = np.concatenate([np.zeros((world, 1), np.int64), np.cumsum(cnt, axis=1)[:, :-1]], axis=1)
+    return recv_offsets.astype(np.int64), send_base.astype(np.int64), src_pos
+
+
+def shard_layer_tp(L: dict, rank: int, tp: int, pad_to: int = 0) -> dict:
+    """Tensor-parallel shard of a numpy layer dict, the reference's rule
+    (src/model_glm52.cpp:314-422): gate/up split on their output rows (intermediate dim),
+    down on its input columns - contiguous, group-aligned slices; router replicated.  With
+    ``pad_to`` the local intermediate size is padded with zero weights (nibble 8, scale 1) up
+    to a multiple of ``pad_to`` so that the tile-stream kernels (512-column chunks) apply."""
+    g = int(L["group"])
+    out = dict(L)
+
+    def split(name_g, name_u, name_d, I):
+        assert I % tp == 0 and (I // tp) % g == 0, "slice must be group aligned"
+        Il = I // tp
+        r0, r1 = rank * Il, (rank + 1) * Il
+        Ip = ((Il + pad_to - 1) // pad_to * pad_to) if pad_to else Il
+        res = {}
+        for nm in (name_g, name_u):
+            q, sc = L[nm + "_q"][..., r0:r1, :], L[nm + "_sc"][..., r0:r1, :]
+            if Ip > Il:
+                padq = np.full(q.shape[:-2] + (Ip - Il, q.shape[-1]), 0x88, np.uint8)
+                pads = np.ones(sc.shape[:-2] + (Ip - Il, sc.shape[-1]), np.float32)
+                q, sc = np.concatenate([q, padq], axis=-2), np.concatenate([sc, pads], axis=-2)
+            res[nm + "_q"], res[nm + "_sc"] = np.ascontiguousarray(q), np.ascontiguousarray(sc)
+        q, sc = L[name_d + "_q"][..., r0 // 2:r1 // 2], L[name_d + "_sc"][..., r0 // g:r1 // g]
+        if Ip > Il:
+            padq = np.full(q.shape[:-1] + ((Ip - Il) // 2,), 0x88, np.uint8)
+            pads = np.ones(sc.shape[:-1] + ((Ip - Il) // g,), np.float32)
+            q, sc = np.concatenate([q, padq], axis=-1), np.concatenate([sc, pads], axis=-1)
+        res[name_d + "_q"], res[name_d + "_sc"] = np.ascontiguousarray(q), np.ascontiguousarray(sc)
+        return res, Ip
+
+    r, Ip = split("gate", "up", "down", int(L["I"]))
+    out.update(r)
+    out["I"] = Ip
+    if L.get("sg_q") is not None:
+        r, Isp = split("sg", "su", "sd", int(L["Is"]))
+        out.update(r)
+        out["Is"] = Isp
+    return out
+
+
+def shard_layer_ep(L: dict, rank: int, ep: int) -> dict:
+    """Expert-parallel shard: experts [rank*E/ep, (rank+1)*E/ep) resident; router, bias and
+    the shared expert replicated.  ``E`` stays the global count."""
+    E = int(L["E"])
+    El = E // ep
+    out = dict(L)
+    for nm in ("gate", "up", "down"):
+        out[nm + "_q"] = L[nm + "_q"][rank * El:(rank + 1) * El]
+        out[nm + "_sc"] = L[nm + "_sc"][rank * El:(rank + 1) * El]
+    out["ep"] = (rank, ep)
+    return out

@@ -195,6 +195,8 @@ class MoELayer:
         cfg.hidden, cfg.n_experts, cfg.topk, cfg.moe_inter = self.H, self.E, self.topk, self.I
         cfg.shared_inter = self.Is if shared else 0
         cfg.group, cfg.norm_topk, cfg.routed_scale = self.group, int(bool(L["norm_topk"])), float(L["routed_scale"])
+        self.ep_rank, self.ep_size = L.get("ep", (0, 1))
+        cfg.ep_rank, cfg.ep_size = self.ep_rank, self.ep_size
 
         def hold(name, t):
             self._keep[name] = t
@@ -268,6 +270,28 @@ class MoELayer:
                                                 _p(ws), C.c_size_t(ws.numel()), path, _p(ids_out), _stream()),
               "moe_block_layer_forward")
         return hidden_f32
+
+    def forward_ep(self, comm, x_bf16, out=None, recv_cap=None, heap_offset=None, ids_out=None):
+        """Expert-parallel forward over the communicator's ranks (this layer holds the experts
+        of rank ``comm.rank``).  x bf16 [n,H] = this GPU's tokens -> out f32 [n,H]."""
+        _need(x_bf16, torch.bfloat16, "x")
+        n = x_bf16.shape[0]
+        if out is None:
+            out = torch.empty((n, self.H), dtype=torch.float32, device=x_bf16.device)
+        if recv_cap is None:
+            recv_cap = n * self.topk * self.ep_size
+        if heap_offset is None:
+            heap_offset = (comm.reserved + 1023) // 1024 * 1024
+        need = int(lib().gsb_moe_ep_workspace_bytes(self._h, n, recv_cap))
+        if getattr(self, "_ep_ws", None) is None or self._ep_ws.numel() < need + 256:
+            self._ep_ws = torch.zeros(need + 256, dtype=torch.uint8, device=self.device)
+        check(lib().gsb_moe_layer_forward_ep(self._h, comm._h, _p(x_bf16), n, _p(out), _p(self._ep_ws),
+                                             C.c_size_t(self._ep_ws.numel()), C.c_size_t(heap_offset), recv_cap,
+                                             _p(ids_out), _stream()), "moe_layer_forward_ep")
+        return out
+
+    def ep_heap_bytes(self, n: int, recv_cap: int) -> int:
+        return int(lib().gsb_moe_ep_heap_bytes(self._h, n, recv_cap))
 
     def status(self) -> int:
         """After a stream synchronise: 0, or 4 when a bounded device wait gave up."""

@@ -191,6 +191,12 @@ typedef struct gsb_moe_config {
     const void* down_packed;
     const void* shared_gate_up_packed;
     const void* shared_down_packed;
+    /* expert parallelism (0 or 1 = off): n_experts stays the GLOBAL expert count E, the weight
+     * pointers above hold the E / ep_size experts [ep_rank*E/ep_size, (ep_rank+1)*E/ep_size)
+     * resident on this GPU; router_w / e_bias cover all E.  Such a layer runs through
+     * gsb_moe_layer_forward_ep only. */
+    int ep_size;
+    int ep_rank;
 } gsb_moe_config;
 
 typedef struct gsb_moe_layer gsb_moe_layer; /* opaque, host memory only */
@@ -276,6 +282,59 @@ GSB_API int gsb_moe_route_static(const void* x_bf16, const void* router_w_bf16,
                                  int norm_topk, float routed_scale, int* topk_ids,
                                  float* topk_weights, void* stream);
 GSB_API int gsb_moe_route_static_max_floats(void);
+
+/* ------------------------------------------------------------------------------------
+ * 3. One 8-GPU box: peer memory over NVLink (one process per GPU)
+ * ---------------------------------------------------------------------------------- */
+
+/* A symmetric heap per rank, mapped into every peer with CUDA IPC; flags with sequence numbers
+ * order the traffic; every device-side wait is bounded and reports GSB_ERR_TIMEOUT through
+ * gsb_comm_status instead of hanging.  Replaces custom_ar_create / custom_ar_open /
+ * custom_ar_run / custom_ar_destroy (cuda/custom_ar.h:26-43) and Communicator::all_reduce_sum
+ * (include/nccl_comm.hpp:50-59, src/nccl_comm.cpp:283-350) for the MoE path.
+ *   create: allocates (cudaMalloc) the local heap of heap_bytes (+ 1 MiB control area) and
+ *           writes a gsb_comm_handle_bytes()-byte handle for the other ranks.
+ *   open:   handles = world handles in rank order (entry [rank] ignored); all-or-none, like the
+ *           reference: on failure destroy the communicator on EVERY rank. */
+typedef struct gsb_comm gsb_comm;
+GSB_API int gsb_comm_handle_bytes(void);
+GSB_API int gsb_comm_create(int rank, int world, size_t heap_bytes, void* out_handle, gsb_comm** out);
+GSB_API int gsb_comm_open(gsb_comm* comm, const void* handles);
+GSB_API void gsb_comm_destroy(gsb_comm* comm);
+GSB_API void* gsb_comm_heap(gsb_comm* comm);
+GSB_API size_t gsb_comm_heap_bytes(gsb_comm* comm);
+GSB_API int gsb_comm_rank(gsb_comm* comm);
+GSB_API int gsb_comm_world(gsb_comm* comm);
+/* After a stream synchronise: GSB_OK, GSB_ERR_TIMEOUT (a peer never posted) or
+ * GSB_ERR_TOO_LARGE (more rows received than the receive capacity); clears the word. */
+GSB_API int gsb_comm_status(gsb_comm* comm);
+/* Device-side barrier over all ranks on `stream` (signal + bounded wait). */
+GSB_API int gsb_comm_barrier(gsb_comm* comm, void* stream);
+
+/* In-place sum of `count` floats over all ranks (count % 4 == 0, data 16-byte aligned, device
+ * memory anywhere on this GPU).  Every element is summed in rank order 0..world-1, so the bits
+ * do not depend on count or grid: reducing rows one by one or as one batch gives the same
+ * result (what all_reduce_sum_rows guarantees in the reference).  Messages up to 2^21 / world
+ * floats take a one-shot pull over NVLink, larger ones reduce-scatter + all-gather.
+ * gsb_comm_allreduce_reserve(max_count) must be called once (same value on every rank): it
+ * returns the bytes at the START of the heap that the all-reduce staging occupies. */
+GSB_API size_t gsb_comm_allreduce_reserve(gsb_comm* comm, int64_t max_count);
+GSB_API int gsb_comm_allreduce_sum(gsb_comm* comm, float* data, int64_t count, void* stream);
+
+/* Expert-parallel forward of one layer (cfg.ep_size = world): router and dispatch on this GPU's
+ * n tokens, per-expert counts exchanged, rows pushed over NVLink into the owners' receive
+ * buffers, grouped GEMMs over the resident experts whose down-projection epilogue stores each
+ * output row straight to the token's home GPU, the shared expert on the local tokens meanwhile,
+ * then the deterministic combine.  No counterpart in the reference (it has no expert
+ * parallelism); results equal the single-GPU layer's bit for bit on the tcgen05 path.
+ *   heap_offset: byte offset into the comm heap (same on all ranks, after the all-reduce
+ *                reserve) of gsb_moe_ep_heap_bytes() bytes for the receive and return buffers.
+ *   recv_cap:    rows this GPU can receive; n*topk*ep_size can never overflow. */
+GSB_API size_t gsb_moe_ep_heap_bytes(const gsb_moe_layer* layer, int n_tokens, int recv_cap);
+GSB_API size_t gsb_moe_ep_workspace_bytes(const gsb_moe_layer* layer, int n_tokens, int recv_cap);
+GSB_API int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, int n,
+                                     float* out, void* workspace, size_t workspace_bytes,
+                                     size_t heap_offset, int recv_cap, int* ids_out, void* stream);
 
 /* Reads (and clears) the device status word of the last forward on this layer after the
  * caller synchronised the stream: GSB_OK or GSB_ERR_TIMEOUT.  Host call. */
