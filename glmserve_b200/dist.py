@@ -143,3 +143,38 @@ def shard_layer_ep(L: dict, rank: int, ep: int) -> dict:
         out[nm + "_sc"] = L[nm + "_sc"][rank * El:(rank + 1) * El]
     out["ep"] = (rank, ep)
     return out
+
+
+def shard_layer_tp_torch(L: dict, rank: int, tp: int, pad_to: int = 512) -> dict:
+    """torch form of shard_layer_tp for layers generated on the GPU (scales fp16)."""
+    import torch
+    g = int(L["group"])
+    out = dict(L)
+
+    def split(ng, nu, nd, I):
+        Il = I // tp
+        assert I % tp == 0 and Il % g == 0
+        r0, r1 = rank * Il, (rank + 1) * Il
+        Ip = (Il + pad_to - 1) // pad_to * pad_to if pad_to else Il
+        res = {}
+        for nm in (ng, nu):
+            q, sc = L[nm + "_q"][..., r0:r1, :], L[nm + "_sc"][..., r0:r1, :]
+            if Ip > Il:
+                q = torch.cat([q, torch.full(q.shape[:-2] + (Ip - Il, q.shape[-1]), 0x88, dtype=torch.uint8, device=q.device)], dim=-2)
+                sc = torch.cat([sc, torch.ones(sc.shape[:-2] + (Ip - Il, sc.shape[-1]), dtype=sc.dtype, device=sc.device)], dim=-2)
+            res[nm + "_q"], res[nm + "_sc"] = q.contiguous(), sc.contiguous()
+        q, sc = L[nd + "_q"][..., r0 // 2:r1 // 2], L[nd + "_sc"][..., r0 // g:r1 // g]
+        if Ip > Il:
+            q = torch.cat([q, torch.full(q.shape[:-1] + ((Ip - Il) // 2,), 0x88, dtype=torch.uint8, device=q.device)], dim=-1)
+            sc = torch.cat([sc, torch.ones(sc.shape[:-1] + ((Ip - Il) // g,), dtype=sc.dtype, device=sc.device)], dim=-1)
+        res[nd + "_q"], res[nd + "_sc"] = q.contiguous(), sc.contiguous()
+        return res, Ip
+
+    r, Ip = split("gate", "up", "down", int(L["I"]))
+    out.update(r)
+    out["I"] = Ip
+    if L.get("sg_q") is not None:
+        r, Isp = split("sg", "su", "sd", int(L["Is"]))
+        out.update(r)
+        out["Is"] = Isp
+    return out
