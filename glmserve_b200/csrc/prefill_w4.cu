@@ -25,7 +25,8 @@ namespace gsb {
 namespace {
 
 constexpr int kPfThreads = 512;        // 16 warps
-constexpr int kPfStages = 3;           // A/B shared-memory stages (one 64-column k-block each)
+// A (dequantised weights, 16 KiB) and B (activations, 32 KiB) stages are template parameters
+// AS / BS of the kernel; one stage = one 64-column k-block.
 constexpr int kBN = 256;               // token rows per tile (TMA box rows)
 constexpr int kABytes = 128 * 128;     // 128 weight rows x 64 fp16
 constexpr int kBBytes = kBN * 128;     // 256 token rows x 64 fp16
@@ -151,21 +152,23 @@ __device__ __forceinline__ PfTile pf_tile(const PrefillKArgs& a, int idx) {
     return r;
 }
 
-template <bool GU>
+template <bool GU, int AS, int BS>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tmap_b64,
                     const __grid_constant__ CUtensorMap tmap_b128, const __grid_constant__ CUtensorMap tmap_b256) {
     extern __shared__ uint8_t smem_raw[];
-    const uint32_t base_u32 = smem_u32(smem_raw);
-    uint8_t* smem = smem_raw + ((1024u - (base_u32 & 1023u)) & 1023u);
-    uint8_t* sA = smem;                                   // [kPfStages][16 KiB]
-    uint8_t* sB = sA + kPfStages * kABytes;               // [kPfStages][32 KiB]
-    uint8_t* sQ = sB + kPfStages * kBBytes;               // [2][4 chunks]
+    // the kernel has no static shared memory, so the dynamic window starts 1024-byte aligned (the
+    // swizzled tiles need that); checked below, a misaligned base is reported instead of used
+    uint8_t* smem = smem_raw;
+    uint8_t* sA = smem;                                   // [AS][16 KiB]
+    uint8_t* sB = sA + AS * kABytes;                      // [BS][32 KiB]
+    uint8_t* sQ = sB + BS * kBBytes;                      // [2][4 chunks]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + 2 * kQBytes);
-    uint64_t* full_a = bars;                   // [stages] dequant warps -> MMA
-    uint64_t* full_b = bars + kPfStages;       // [stages] TMA -> MMA
-    uint64_t* empty = bars + 2 * kPfStages;    // [stages] MMA commit -> producer, dequant
-    uint64_t* q_full = bars + 3 * kPfStages;   // [2] bulk copy -> dequant
+    uint64_t* full_a = bars;                   // [AS] dequant warps -> MMA
+    uint64_t* empty = full_a + AS;             // [AS] MMA commit -> dequant
+    uint64_t* full_b = empty + AS;             // [BS] TMA -> MMA
+    uint64_t* empty_b = full_b + BS;           // [BS] MMA commit -> producer
+    uint64_t* q_full = empty_b + BS;           // [2] bulk copy -> dequant
     uint64_t* q_empty = q_full + 2;            // [2] dequant -> producer
     uint64_t* acc_full = q_empty + 2;          // [2] MMA commit -> epilogue
     uint64_t* acc_empty = acc_full + 2;        // [2] epilogue -> MMA
@@ -173,8 +176,13 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (smem_u32(smem_raw) & 1023u) {
+        if (tid == 0 && atomicCAS(a.status + kStatusCode, 0, GSB_ERR_LAUNCH) == 0) a.status[kStatusWhere] = 199;
+        return;
+    }
     if (tid == 0) {
-        for (int i = 0; i < kPfStages; ++i) { mbar_init(&full_a[i], 4); mbar_init(&full_b[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < AS; ++i) { mbar_init(&full_a[i], 4); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < BS; ++i) { mbar_init(&full_b[i], 1); mbar_init(&empty_b[i], 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 8); mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
         *abort_flag = 0;
         fence_barrier_init();
@@ -204,8 +212,8 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
                                      t.chunks + (int64_t)u * t.unit_stride + (int64_t)c * kChunkBytes, kChunkBytes, &q_full[qs]);
                         ++qc;
                     }
-                    const uint32_t s = kc % kPfStages, ph = (kc / kPfStages) & 1u;
-                    if (!mbar_wait(&empty[s], ph ^ 1u, kPfWaitLimit)) { pf_timeout(a, abort_flag, 2); break; }
+                    const uint32_t s = kc % BS, ph = (kc / BS) & 1u;
+                    if (!mbar_wait(&empty_b[s], ph ^ 1u, kPfWaitLimit)) { pf_timeout(a, abort_flag, 2); break; }
                     // the smallest box that covers the tile's rows: a ragged tile does not pull 256 rows
                     const CUtensorMap* tm = t.nround <= 64 ? &tmap_b64 : (t.nround <= 128 ? &tmap_b128 : &tmap_b256);
                     const uint32_t rows = t.nround <= 64 ? 64u : (t.nround <= 128 ? 128u : 256u);
@@ -227,17 +235,19 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
                 const uint32_t idesc = make_idesc((uint32_t)t.nround);
                 bool dead = false;
                 for (int kb = 0; kb < t.nkb; ++kb, ++kc) {
-                    const uint32_t s = kc % kPfStages, ph = (kc / kPfStages) & 1u;
-                    if (!mbar_wait(&full_a[s], ph, kPfWaitLimit) || !mbar_wait(&full_b[s], ph, kPfWaitLimit)) {
+                    const uint32_t s = kc % AS, ph = (kc / AS) & 1u;
+                    const uint32_t sb = kc % BS, phb = (kc / BS) & 1u;
+                    if (!mbar_wait(&full_a[s], ph, kPfWaitLimit) || !mbar_wait(&full_b[sb], phb, kPfWaitLimit)) {
                         pf_timeout(a, abort_flag, 4); dead = true; break;
                     }
                     tc_fence_after();
                     const uint64_t ad = make_desc_sw128(smem_u32(sA + s * kABytes));
-                    const uint64_t bd = make_desc_sw128(smem_u32(sB + s * kBBytes));
+                    const uint64_t bd = make_desc_sw128(smem_u32(sB + sb * kBBytes));
 #pragma unroll
                     for (int k4 = 0; k4 < 4; ++k4)
                         tc_mma_f16(d_tmem, ad + (uint64_t)(k4 * 2), bd + (uint64_t)(k4 * 2), idesc, (kb | k4) ? 1u : 0u);
                     tc_commit(&empty[s]);
+                    tc_commit(&empty_b[sb]);
                 }
                 if (dead) break;
                 tc_commit(&acc_full[buf]);
@@ -313,19 +323,22 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
                     }
                     ++qc;
                 }
-                const uint32_t s = kc % kPfStages, ph = (kc / kPfStages) & 1u;
-                if (!mbar_wait(&empty[s], ph ^ 1u, kPfWaitLimit)) { pf_timeout(a, abort_flag, 7); dead = true; break; }
                 const int ks = kb8 >> 1, tq0 = grp << 1;
                 const uint8_t* chunk = sQ + qs * kQBytes + uu * kChunkBytes;
                 const uint4* piece = reinterpret_cast<const uint4*>(chunk + (ks * 2 + m) * 1024 + h * 512 + (g * 4 + tq0) * 16);
                 const uint4 wv0 = piece[0], wv1 = piece[1];
                 const __half sc = reinterpret_cast<const __half*>(chunk + kChunkWeightBytes)[(ks * 2 + m) * 16 + g + 8 * h];
                 const __half2 s2 = __half2half2(sc);
-                uint8_t* arow = sA + s * kABytes + (R >> 3) * 1024 + g * 128;
                 const uint32_t wq[8] = {wv0.x, wv0.y, wv0.z, wv0.w, wv1.x, wv1.y, wv1.z, wv1.w};
+                uint4 dq[8];   // unpacked in registers first: only the stores need the stage to be free
+#pragma unroll
+                for (int c = 0; c < 8; ++c) dq[c] = dequant8(wq[c], s2);
+                const uint32_t s = kc % AS, ph = (kc / AS) & 1u;
+                if (!mbar_wait(&empty[s], ph ^ 1u, kPfWaitLimit)) { pf_timeout(a, abort_flag, 7); dead = true; break; }
+                uint8_t* arow = sA + s * kABytes + (R >> 3) * 1024 + g * 128;
 #pragma unroll
                 for (int c = 0; c < 8; ++c)             // c = 16-byte piece of the 128-byte row
-                    *reinterpret_cast<uint4*>(arow + ((c ^ g) << 4)) = dequant8(wq[c], s2);
+                    *reinterpret_cast<uint4*>(arow + ((c ^ g) << 4)) = dq[c];
                 fence_proxy_async();   // this thread's stores, visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&full_a[s]);
@@ -500,7 +513,7 @@ __global__ void tile_shared_only_kernel(int E_marker, int n, int row_blocks, int
     }
 }
 
-constexpr size_t kPfSmem = 1024 + kPfStages * (kABytes + kBBytes) + 2 * kQBytes + 256;
+constexpr size_t pf_smem(int as, int bs) { return (size_t)as * kABytes + (size_t)bs * kBBytes + 2 * kQBytes + 256; }
 
 }  // namespace
 
@@ -509,6 +522,20 @@ size_t prefill_tile_bytes(int n, int topk, int E, int H, int I) {
     const size_t tok_tiles = (size_t)E + P / kBN + (size_t)n / kBN + 2;
     const size_t rbmax = (size_t)((H / 128 > I / 64) ? H / 128 : I / 64);
     return (kTileHeader + 4 * tok_tiles * rbmax) * sizeof(int);
+}
+
+template <int AS, int BS>
+static int launch_pair(const PrefillKArgs& g, const PrefillKArgs& w, const CUtensorMap* tm_x, const CUtensorMap* tm_h,
+                       int sm_count, cudaStream_t s, cudaEvent_t ev_mid) {
+    const size_t smem = pf_smem(AS, BS);
+    if (smem > 227 * 1024) return GSB_ERR_UNSUPPORTED;
+    if (cudaFuncSetAttribute(prefill_gemm_kernel<true, AS, BS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_gemm_kernel<false, AS, BS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return GSB_ERR_CUDA;
+    prefill_gemm_kernel<true, AS, BS><<<sm_count, kPfThreads, smem, s>>>(g, tm_x[0], tm_x[1], tm_x[2]);
+    if (ev_mid) cudaEventRecord(ev_mid, s);
+    prefill_gemm_kernel<false, AS, BS><<<sm_count, kPfThreads, smem, s>>>(w, tm_h[0], tm_h[1], tm_h[2]);
+    return launch_status();
 }
 
 static int run_gemm_pair(const PrefillKArgs& g_in, const PrefillKArgs& w_in, const void* xbase, int64_t xrows,
@@ -522,13 +549,8 @@ static int run_gemm_pair(const PrefillKArgs& g_in, const PrefillKArgs& w_in, con
         st = make_tmap(&tm_h[i], hbase, hrows, ldh, ldh, boxes[i]);
         if (st) return st;
     }
-    if (cudaFuncSetAttribute(prefill_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(prefill_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem) != cudaSuccess)
-        return GSB_ERR_CUDA;
-    prefill_gemm_kernel<true><<<sm_count, kPfThreads, kPfSmem, s>>>(g_in, tm_x[0], tm_x[1], tm_x[2]);
-    if (ev_mid) cudaEventRecord(ev_mid, s);
-    prefill_gemm_kernel<false><<<sm_count, kPfThreads, kPfSmem, s>>>(w_in, tm_h[0], tm_h[1], tm_h[2]);
-    return launch_status();
+    // two weight stages and four activation stages measured best on the skewed GLM-scale layer
+    return launch_pair<2, 4>(g_in, w_in, tm_x, tm_h, sm_count, s, ev_mid);
 }
 
 // Expert parallel, shared expert: this GPU's own tokens through the shared expert, output rows
@@ -591,33 +613,18 @@ int launch_prefill_layer(const PrefillArgs& d, cudaStream_t s) {
     if (shared) tile_append_shared_kernel<<<1, 256, 0, s>>>(d.expert_offsets, d.E, d.n, P, d.H / 128, d.H / 128, d.tiles_dn);
     if (d.ev_prep) cudaEventRecord(d.ev_prep, s);
 
-    CUtensorMap tm_x[3], tm_h[3];
-    const int boxes[3] = {64, 128, 256};
-    for (int i = 0; i < 3; ++i) {
-        int st = make_tmap(&tm_x[i], d.xs, rows, d.H, d.H, boxes[i]);
-        if (st) return st;
-        st = make_tmap(&tm_h[i], d.hbuf, rows, imax, imax, boxes[i]);
-        if (st) return st;
-    }
-
     PrefillKArgs g{};
     g.packed = reinterpret_cast<const uint8_t*>(d.gate_up_packed);
     g.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_gate_up_packed);
     g.tiles = d.tiles_gu; g.K = d.H; g.Ks = d.H; g.units = d.I / 16; g.units_s = d.Is / 16; g.E = d.E;
     g.hbuf = d.hbuf; g.ldh = imax; g.ybuf = nullptr; g.H = d.H; g.status = d.status;
-    if (cudaFuncSetAttribute(prefill_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem) != cudaSuccess)
-        return GSB_ERR_CUDA;
-    prefill_gemm_kernel<true><<<d.sm_count, kPfThreads, kPfSmem, s>>>(g, tm_x[0], tm_x[1], tm_x[2]);
-    if (d.ev_gate_up) cudaEventRecord(d.ev_gate_up, s);
-
     PrefillKArgs w = g;
     w.packed = reinterpret_cast<const uint8_t*>(d.down_packed);
     w.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_down_packed);
     w.tiles = d.tiles_dn; w.K = d.I; w.Ks = shared ? d.Is : d.I; w.units = d.H / 32; w.units_s = d.H / 32;
     w.hbuf = nullptr; w.ybuf = d.ybuf;
-    if (cudaFuncSetAttribute(prefill_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem) != cudaSuccess)
-        return GSB_ERR_CUDA;
-    prefill_gemm_kernel<false><<<d.sm_count, kPfThreads, kPfSmem, s>>>(w, tm_h[0], tm_h[1], tm_h[2]);
+    const int st = run_gemm_pair(g, w, d.xs, rows, d.H, d.hbuf, rows, imax, d.sm_count, s, d.ev_gate_up);
+    if (st) return st;
     if (d.ev_down) cudaEventRecord(d.ev_down, s);
 
     dim3 cgrid((unsigned)(((d.H >> 3) + 255) / 256), (unsigned)d.n);
