@@ -19,6 +19,7 @@
 // Nothing is accumulated with atomics; every reduction order is fixed, so results do not
 // depend on the grid or on timing.  Every wait is bounded: on a timeout the CTA records
 // where in the status word and all its loops leave.
+
 #include "common.cuh"
 #include "launchers.cuh"
 
@@ -56,6 +57,8 @@ struct DecodeKArgs {
     int H;
     int nstage;
     int* status;
+    const int* xsegs;              // expert list of the register-resident variant (see xseg_* below)
+    int x_which;                   // 0: gate/up item numbering, 1: down
 };
 
 struct Item {
@@ -127,6 +130,52 @@ __device__ __forceinline__ bool next_run(const DecodeKArgs& a, long long& it, lo
     const long long e_local = sh ? 0 : rec.x;
     r.chunks = base + ((e_local * U + r.ubeg) * (long long)nchunk) * kChunkBytes;
     it += r.uend - r.ubeg;
+    return true;
+}
+
+// ---- expert list (register-resident variant) ----------------------------------------------
+// One entry per expert that has tokens (the shared expert first, then the routed experts in order):
+//   xsegs[0] = entries, [1] / [2] = total items of the gate/up / down kernel, [3] = grid size,
+//   entries from [kXHeader]: {expert, first slot, tokens, groups of 8 tokens, first gate/up item,
+//   first down item, 0, 0}, then cta_start[2][grid + 1]: the entry each CTA's first item falls in.
+// An expert with G > 1 token groups enumerates its items group by group (all units of group 0,
+// then of group 1, ...).  Interleaving the groups over small blocks of units, so that a block's
+// weights come from L2 for every group after the first, measured slower: each switch of group
+// reloads the group's activation fragments (as many bytes as one unit of weights) and drains
+// the pipeline.
+constexpr int kXHeader = 4;
+constexpr int kXEntry = 8;
+
+template <bool GU>
+__device__ __forceinline__ bool next_run_x(const DecodeKArgs& a, long long& it, long long it1, int& cur,
+                                           int nchunk, SegRun& r) {
+    if (it >= it1) return false;
+    const int* ent = a.xsegs + kXHeader + cur * kXEntry;
+    int U, G;
+    long long ib;
+    for (;;) {
+        U = ent[0] >= a.E ? a.units_s : a.units;
+        G = ent[3];
+        ib = ent[GU ? 4 : 5];
+        if (it < ib + (long long)U * G) break;
+        ++cur;
+        ent += kXEntry;
+    }
+    const int l = (int)(it - ib);
+    const long long left = it1 - it;
+    const int g = G == 1 ? 0 : l / U;
+    const int unit = l - g * U;
+    const int uend = (long long)(U - unit) < left ? U : unit + (int)left;
+    r.seg = cur * 4096 + g;
+    r.ubeg = unit; r.uend = uend;
+    r.expert = ent[0];
+    r.slot_begin = ent[1] + g * kDecodeTokens;
+    r.ntok = min(kDecodeTokens, ent[2] - g * kDecodeTokens);
+    const bool sh = ent[0] >= a.E;
+    const uint8_t* base = sh ? a.shared_packed : a.packed;
+    const long long e_local = sh ? 0 : ent[0];
+    r.chunks = base + ((e_local * U + unit) * (long long)nchunk) * kChunkBytes;
+    it += uend - unit;
     return true;
 }
 
@@ -322,6 +371,7 @@ decode_gemm_kernel(const DecodeKArgs a) {
                     tot[2] = fmaf(s1a, alo[2], fmaf(s1b, ahi[2], fmaf(s1c, sxv.x, tot[2])));
                     tot[3] = fmaf(s1a, alo[3], fmaf(s1b, ahi[3], fmaf(s1c, sxv.y, tot[3])));
                 }
+                fence_proxy_async();  // as in the register-resident kernel: this warp's reads before the refill
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[slot]);
             }
@@ -330,7 +380,7 @@ decode_gemm_kernel(const DecodeKArgs a) {
             if (!mbar_wait(&red_free[rb], ((item_local >> 1) & 1u) ^ 1u, kWaitLimit)) { record_timeout(a, abort_flag, 5); break; }
             float* r = red + (size_t)rb * (kRedBytes / 4) + (size_t)cw * 128 + lane;
             r[0] = tot[0]; r[32] = tot[1]; r[64] = tot[2]; r[96] = tot[3];
-            __syncwarp();
+            __syncwarp();  // orders every lane's partials before the one release-arrive below
             if (lane == 0) mbar_arrive(&red_full[rb]);
         }
     } else {
@@ -418,13 +468,12 @@ decode_reg_kernel(const DecodeKArgs a) {
     }
     __syncthreads();
 
-    const int nseg = a.segs[0];
-    const int nshared_seg = a.segs[1];
-    const long long total = (long long)nshared_seg * a.units_s + (long long)(nseg - nshared_seg) * a.units;
+    const long long total = a.xsegs[1 + a.x_which];
     const long long it0 = total * blockIdx.x / gridDim.x;
     const long long it1 = total * (blockIdx.x + 1) / gridDim.x;
     if (it0 >= it1) return;
     long long it = it0;
+    int cur = a.xsegs[kXHeader + a.xsegs[0] * kXEntry + a.x_which * ((int)gridDim.x + 1) + blockIdx.x];
     SegRun run;
 
     if (warp < kRConsumerWarps) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRConsumerRegs));
@@ -434,7 +483,7 @@ decode_reg_kernel(const DecodeKArgs a) {
         if (lane == 0) {  // register-resident variant: producer
             uint32_t q = 0;
             bool dead = false;
-            while (!dead && !*abort_flag && next_run(a, it, it1, nshared_seg, NKB * 4, NKB * 4, run)) {
+            while (!dead && !*abort_flag && next_run_x<GU>(a, it, it1, cur, NKB * 4, run)) {
                 const uint8_t* src = run.chunks;
                 const int nst = (run.uend - run.ubeg) * NKB;  // the run's units are contiguous in memory
                 for (int i = 0; i < nst; ++i, ++q, src += kRStageBytes) {
@@ -456,8 +505,10 @@ decode_reg_kernel(const DecodeKArgs a) {
         float2 sxv[NKB];
         uint32_t q = 0, item_local = 0;
         bool dead = false;
-        while (!dead && next_run(a, it, it1, nshared_seg, NKB * 4, NKB * 4, run)) {
-            {   // this segment's activation fragments and per-group sums, straight into registers
+        int cur_key = -1;
+        while (!dead && next_run_x<GU>(a, it, it1, cur, NKB * 4, run)) {
+            if (run.seg != cur_key) {   // this group's activation fragments and sums, into registers
+                cur_key = run.seg;
                 const bool valid = g < run.ntok;
                 long long row = 0;
                 if (valid) {
@@ -488,6 +539,7 @@ decode_reg_kernel(const DecodeKArgs a) {
                 for (int st = 0; st < NKB; ++st, ++q) {
                     const uint32_t slot = q % nstage, ph = (q / nstage) & 1u;
                     if (!mbar_wait(&full[slot], ph, kWaitLimit)) { record_timeout(a, abort_flag, 14); dead = true; break; }
+                    __syncwarp();  // lanes leave the poll loop one by one; mma.sync wants them together
                     const uint8_t* stage = ring + (size_t)slot * kRStageBytes;
 #pragma unroll
                     for (int m = 0; m < 2; ++m) {
@@ -513,6 +565,12 @@ decode_reg_kernel(const DecodeKArgs a) {
                         tot[m][2] = fmaf(S1, fmaf(ahi[2], 0.0625f, alo[2]), fmaf(C1, sxv[st].x, tot[m][2]));
                         tot[m][3] = fmaf(S1, fmaf(ahi[3], 0.0625f, alo[3]), fmaf(C1, sxv[st].y, tot[m][3]));
                     }
+                    // The stage goes back to the producer, whose bulk copy writes it through the async
+                    // proxy.  Loads of this warp that are still in flight (the scale words feed only
+                    // `tot`, which nothing needs before the unit ends) are generic-proxy accesses: only
+                    // a proxy fence before the release orders them ahead of that copy.  Without it a
+                    // layer whose weights sit in L2 returned wrong sums in up to 40% of its forwards.
+                    fence_proxy_async();  // generic-proxy reads of the stage before the async-proxy refill
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty[slot]);
                 }
@@ -524,7 +582,7 @@ decode_reg_kernel(const DecodeKArgs a) {
                 for (int m = 0; m < 2; ++m)
 #pragma unroll
                     for (int c = 0; c < 4; ++c) r[m * 128 + c * 32] = tot[m][c];
-                __syncwarp();  // orders every lane's partials before the one arrive below
+                __syncwarp();  // orders every lane's partials before the one release-arrive below
                 if (lane == 0) mbar_arrive(&red_full[rb]);
             }
         }
@@ -533,7 +591,7 @@ decode_reg_kernel(const DecodeKArgs a) {
         constexpr int kNOut = GU ? 16 * kDecodeTokens : 32 * kDecodeTokens;  // outputs per item
         uint32_t item_local = 0;
         bool dead = false;
-        while (!dead && next_run(a, it, it1, nshared_seg, NKB * 4, NKB * 4, run)) {
+        while (!dead && next_run_x<GU>(a, it, it1, cur, NKB * 4, run)) {
             for (int unit = run.ubeg; unit < run.uend; ++unit, ++item_local) {
                 const uint32_t rb = item_local % kRed;
                 if (*abort_flag || !mbar_wait(&red_full[rb], (item_local / kRed) & 1u, kWaitLimit)) {
@@ -576,8 +634,10 @@ decode_reg_kernel(const DecodeKArgs a) {
 // from the dispatch offsets - no host synchronisation.
 __global__ void __launch_bounds__(1024)
 seg_build_kernel(const int* __restrict__ expert_offsets, int E, int n, int P, int has_shared,
-                 int* __restrict__ segs) {
+                 int* __restrict__ segs, int* __restrict__ xsegs, int units_gu, int units_gu_s, int units_dn,
+                 int grid) {
     __shared__ int wsum[32];
+    __shared__ int pre_s[1025];   // exclusive prefix of token groups over routed experts
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int nsh = has_shared ? (n + kDecodeTokens - 1) / kDecodeTokens : 0;
     int cnt = 0, beg = 0;
@@ -609,6 +669,76 @@ seg_build_kernel(const int* __restrict__ expert_offsets, int E, int n, int P, in
         out[base + j] = make_int4(tid, beg + j * kDecodeTokens, min(kDecodeTokens, cnt - j * kDecodeTokens), 0);
     for (int j = tid; j < nsh; j += blockDim.x)
         out[j] = make_int4(E, P + j * kDecodeTokens, min(kDecodeTokens, n - j * kDecodeTokens), 0);
+    if (!xsegs) return;
+    // expert list of the register-resident variant: experts that received tokens only, so that
+    // a CTA stepping from one expert to the next never walks over empty entries
+    __shared__ int nz_w[32];
+    const int gpre = incl - ng + wsum[w];             // groups of the routed experts before this one
+    const int nz = ng > 0 ? 1 : 0;
+    int nzi = nz;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, nzi, o);
+        if (lane >= o) nzi += u;
+    }
+    if (lane == 31) nz_w[w] = nzi;
+    __syncthreads();
+    if (w == 0) {
+        const int v = nz_w[lane];
+        int vi = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, vi, o);
+            if (lane >= o) vi += u;
+        }
+        nz_w[lane] = vi - v;
+        if (lane == 31) pre_s[1024] = vi;             // experts with tokens
+    }
+    __syncthreads();
+    const int nnz = pre_s[1024];
+    const int ci = nzi - nz + nz_w[w];                // this expert's place among those with tokens
+    __syncthreads();                                  // pre_s[1024] is read before it may be rewritten
+    if (nz) pre_s[ci] = gpre;
+    if (tid == E - 1) pre_s[nnz] = gpre + ng;
+    __syncthreads();
+    const int groups = pre_s[nnz];
+    const int nent = has_shared + nnz;
+    const long long sh_gu = (long long)nsh * units_gu_s, sh_dn = (long long)nsh * units_dn;
+    if (nz) {
+        int* e8 = xsegs + kXHeader + (has_shared + ci) * kXEntry;
+        e8[0] = tid; e8[1] = beg; e8[2] = cnt; e8[3] = ng;
+        e8[4] = (int)(sh_gu + (long long)gpre * units_gu);
+        e8[5] = (int)(sh_dn + (long long)gpre * units_dn);
+        e8[6] = e8[7] = 0;
+    }
+    if (tid == 0) {
+        if (has_shared) {
+            int* e8 = xsegs + kXHeader;
+            e8[0] = E; e8[1] = P; e8[2] = n; e8[3] = nsh; e8[4] = 0; e8[5] = 0; e8[6] = e8[7] = 0;
+        }
+        xsegs[0] = nent;
+        xsegs[1] = (int)(sh_gu + (long long)groups * units_gu);
+        xsegs[2] = (int)(sh_dn + (long long)groups * units_dn);
+        xsegs[3] = grid;
+    }
+    // entry in which each CTA's first item falls (largest entry whose first item <= target)
+    int* cta = xsegs + kXHeader + nent * kXEntry;
+    for (int job = tid; job < 2 * (grid + 1); job += blockDim.x) {
+        const int which = job / (grid + 1), c = job - which * (grid + 1);
+        const long long U = which ? units_dn : units_gu, shi = which ? sh_dn : sh_gu;
+        const long long total = shi + (long long)groups * U;
+        const long long target = total * c / grid;
+        int ent = 0;
+        if (!(has_shared && target < shi) && nnz > 0) {
+            int lo = 0, hi = nnz - 1;   // last listed routed expert with first item <= target
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (shi + (long long)pre_s[mid] * U <= target) lo = mid; else hi = mid - 1;
+            }
+            ent = has_shared + lo;
+        }
+        cta[job] = ent;
+    }
 }
 
 // bf16 activations -> fp16 in fragment order (exact for |x| in the fp16 normal range; values
@@ -685,7 +815,16 @@ size_t decode_seg_bytes(int n, int topk, int E) {
     const size_t P = (size_t)n * topk;
     const size_t max_segs = (size_t)E + (P + kDecodeTokens - 1) / kDecodeTokens +
                             ((size_t)n + kDecodeTokens - 1) / kDecodeTokens + 1;
-    return (kSegHeader + 4 * (max_segs + 1)) * sizeof(int);
+    const size_t old_ints = kSegHeader + 4 * (max_segs + 1);
+    const size_t x_ints = kXHeader + ((size_t)E + 1) * kXEntry + 2 * (1024 + 1);
+    return ((old_ints + 3) / 4 * 4 + x_ints) * sizeof(int);
+}
+
+static size_t xsegs_offset_ints(int n, int topk, int E) {
+    const size_t P = (size_t)n * topk;
+    const size_t max_segs = (size_t)E + (P + kDecodeTokens - 1) / kDecodeTokens +
+                            ((size_t)n + kDecodeTokens - 1) / kDecodeTokens + 1;
+    return (kSegHeader + 4 * (max_segs + 1) + 3) / 4 * 4;
 }
 
 constexpr size_t decode_reg_smem(int nstage, int nred) {
@@ -721,7 +860,10 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     if (cudaMemsetAsync(d.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
 
     xprep_kernel<<<(unsigned)(((int64_t)d.n * (d.H >> 3) + 255) / 256), 256, 0, s>>>(d.x, d.xp, d.n, d.H);
-    seg_build_kernel<<<1, 1024, 0, s>>>(d.expert_offsets, d.E, d.n, P, shared ? 1 : 0, d.segs);
+    int* xsegs = d.segs + xsegs_offset_ints(d.n, d.topk, d.E);
+    if (d.sm_count > 1024) return GSB_ERR_UNSUPPORTED;
+    seg_build_kernel<<<1, 1024, 0, s>>>(d.expert_offsets, d.E, d.n, P, shared ? 1 : 0, d.segs, xsegs, d.I / 16,
+                                        shared ? d.Is / 16 : 1, d.H / 32, d.sm_count);
     if (d.ev_prep) cudaEventRecord(d.ev_prep, s);
 
     DecodeKArgs g{};
@@ -731,6 +873,7 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     g.bsrc = d.xp; g.ldb = d.H; g.K = d.H; g.Ks = d.H;
     g.units = d.I / 16; g.units_s = d.Is / 16; g.E = d.E; g.P = P;
     g.hbuf = d.hbuf; g.ldh = imax; g.ybuf = nullptr; g.H = d.H; g.status = d.status;
+    g.xsegs = xsegs; g.x_which = 0;
     // register-resident variant when the input dim is a multiple of 2048 (at most 3 x 2048)
     const bool gu_reg = !d.force_smem_variant && d.H % 2048 == 0 && d.H / 2048 <= 3;
     if (gu_reg) {
@@ -752,7 +895,7 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     w.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_down_packed);
     w.bsrc = d.hbuf; w.ldb = imax; w.K = d.I; w.Ks = shared ? d.Is : d.I;
     w.units = d.H / 32; w.units_s = d.H / 32;
-    w.hbuf = nullptr; w.ybuf = d.ybuf;
+    w.hbuf = nullptr; w.ybuf = d.ybuf; w.x_which = 1;
     const bool dn_reg = !d.force_smem_variant && d.I % 2048 == 0 && d.I / 2048 <= 3 && w.Ks == w.K;
     if (dn_reg) {
         const int st = launch_reg<false>(w, d.I / 2048, d.sm_count, s);

@@ -85,7 +85,7 @@ def test_mid_config_prefill_skewed_no_shared(dev):
     _check_layer(layer, L, x, dev, ops.PATH_PREFILL, "mid prefill skewed")
 
 
-@pytest.mark.parametrize("n", [1, 5, 33])
+@pytest.mark.parametrize("n", [1, 5, 33, 150])
 def test_wide_config_register_resident_decode(dev, n):
     """Input dims that are multiples of 2048 take the register-resident decode variant
     (H=4096: two 2048-column stages per item; I=2048: one)."""
@@ -96,6 +96,27 @@ def test_wide_config_register_resident_decode(dev, n):
     a = _check_layer(layer, L, x, dev, ops.PATH_DECODE, f"wide decode n={n}")
     b = _check_layer(layer, L, x, dev, ops.PATH_DECODE_SMEM, f"wide decode (smem variant) n={n}")
     assert torch.equal(layer.forward(bf16_tensor(x, dev), path=ops.PATH_DECODE), a["out"])
+
+
+@pytest.mark.parametrize("n,reps", [(200, 300), (500, 400)])
+def test_wide_config_repeated_forwards_with_weights_in_l2(dev, n, reps):
+    """A layer small enough to stay in L2 makes the weight ring turn over as fast as the
+    consumers can release it; a stage released before every load from it is ordered ahead of
+    the refill (the refill writes through the async proxy) showed up as wrong sums in up to 40%
+    of these forwards.  No atomics, fixed summation order: every forward returns the same bits
+    as the first one, which is checked against the oracle."""
+    from glmserve_b200 import ops
+    cfg = CONFIGS["wide"]
+    L = make_layer_np(cfg, seed=11)
+    layer = ops.MoELayer(layer_to_torch(L, dev))
+    x_np = make_x_np(n, cfg["H"], seed=40 + n)
+    x = bf16_tensor(x_np, dev)
+    first = _check_layer(layer, L, x_np, dev, ops.PATH_DECODE, f"wide decode n={n}")["out"].clone()
+    differing = torch.zeros((), dtype=torch.int32, device=dev)
+    for _ in range(reps):
+        differing += (layer.forward(x, path=ops.PATH_DECODE) != first).any().int()
+    assert layer.status() == 0
+    assert int(differing) == 0, f"{int(differing)} of {reps} forwards differ from the first"
 
 
 def test_mid_config_without_shared_expert_and_skew(dev):
@@ -144,6 +165,24 @@ def test_glm_scale_decode(dev, glm_layer, n):
     out3 = layer.forward(x, path=ops.PATH_DECODE_SMEM)
     assert layer.status() == 0
     assert_layer_close(out3.cpu().numpy(), r["out"], f"glm decode (smem variant) n={n}")
+
+
+@pytest.mark.parametrize("path_name,n,reps", [("PATH_DECODE", 64, 60), ("PATH_DECODE", 200, 30),
+                                              ("PATH_DECODE_SMEM", 64, 30), ("PATH_PREFILL", 512, 20)])
+def test_glm_scale_repeated_forwards_are_bit_identical(dev, glm_layer, path_name, n, reps):
+    """The layer has no atomics and a fixed summation order, so every forward of the same input
+    returns the same bits.  A stage of the weight ring that is handed back to the producer
+    while one of its loads is still in flight shows up here as a rare differing forward."""
+    from glmserve_b200 import ops
+    layer, _ = glm_layer
+    path = getattr(ops, path_name)
+    x = make_x_torch(n, 6144, seed=500 + n, device=dev)
+    first = layer.forward(x, path=path).clone()
+    differing = 0
+    for _ in range(reps):
+        differing += int(not torch.equal(layer.forward(x, path=path), first))
+    assert layer.status() == 0
+    assert differing == 0, f"{differing} of {reps} forwards differ from the first"
 
 
 def test_glm_scale_prefill(dev, glm_layer):
