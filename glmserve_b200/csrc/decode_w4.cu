@@ -436,12 +436,57 @@ constexpr int kRConsumerWarps = 16;
 // warps 0..15 consumers, warp 16 producer, warps 17..19 epilogue.
 template <bool GU> struct RCfg { static constexpr int kEpiWarps = 3; static constexpr int kRed = GU ? 2 : 3;
                                  static constexpr int kThreads = (16 + 1 + kEpiWarps) * 32; };
-constexpr int kRConsumerRegs = 104;   // 16 warps x 32 x 104 + 4 warps x 32 x 56 = 60416 <= 65536
-constexpr int kRHelperRegs = 56;
+// setmaxnreg moves registers between the warps of ONE CTA: what the consumers gain must have been
+// given up by the helper warps out of the CTA's launch allocation (640 threads x 96 registers); an
+// increase beyond that waits for ever.  16 x 32 x (104 - 96) = 4096 <= 4 x 32 x (96 - 64) = 4096.
+constexpr int kRLaunchRegs = 96;
+constexpr int kRConsumerRegs = 104;
+constexpr int kRHelperRegs = 64;
+static_assert(16 * (kRConsumerRegs - kRLaunchRegs) <= 4 * (kRLaunchRegs - kRHelperRegs),
+              "consumer warps would wait for registers the helper warps never release");
 constexpr int kRStageChunks = 4;
 constexpr int kRStageBytes = kRStageChunks * kChunkBytes;           // 33792
 constexpr int kRRedFloats = kRConsumerWarps * 8 * 32;               // 16 KiB per buffer
 constexpr int kRMaxStages = 6;
+
+// Sums the sixteen consumer warps' partials of one item and writes the item's outputs (gate/up:
+// silu(gate) * up as fp16 in fragment order; down: fp32 rows of the slot buffer).
+// A warp's partials lie as [m][c][lane] (c = accumulator register, lane = 4*g + t: row
+// g + 8*(c>>1) of the half unit, token 2t + (c&1)).  A thread takes V adjacent lanes (same g,
+// tokens two apart), so a warp reads consecutive words of each consumer warp's block: no bank
+// conflicts, sixteen vector loads per thread.
+template <bool GU>
+__device__ __forceinline__ void reduce_item(const DecodeKArgs& a, const float* __restrict__ redbuf, int et,
+                                         int unit, int slot_begin, int ntok) {
+    constexpr int V = GU ? 2 : 4;
+    if (et >= 64) return;
+    const int q = et * V;                              // first float of the m-block(s)
+    const int m = GU ? 0 : q >> 7;
+    const int c = (q >> 5) & 3, L0 = q & 31;
+    const int r = (L0 >> 2) + ((c >> 1) << 3);
+    const int n0 = ((L0 & 3) << 1) + (c & 1);
+    const float* rbuf = redbuf + q;
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[2] = {0.f, 0.f};
+#pragma unroll
+    for (int w = 0; w < kRConsumerWarps; ++w) {
+        if (GU) {
+            const float2 p0 = *reinterpret_cast<const float2*>(rbuf + w * 256);
+            const float2 p1 = *reinterpret_cast<const float2*>(rbuf + w * 256 + 128);
+            s0[0] += p0.x; s0[1] += p0.y; s1[0] += p1.x; s1[1] += p1.y;
+        } else {
+            const float4 p0 = *reinterpret_cast<const float4*>(rbuf + w * 256);
+            s0[0] += p0.x; s0[1] += p0.y; s0[2] += p0.z; s0[3] += p0.w;
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+        const int n = n0 + 2 * v;
+        if (n >= ntok) continue;
+        const long long slot = slot_begin + n;
+        if (GU) a.hbuf[slot * a.ldh + frag_pos(unit * 16 + r)] = __float2half_rn(__fmul_rn(silu_ref(s0[v]), s1[v & 1]));
+        else a.ybuf[slot * a.H + unit * 32 + m * 16 + r] = s0[v];
+    }
+}
 
 template <bool GU, int NKB>
 __global__ void __launch_bounds__(RCfg<GU>::kThreads, 1)
@@ -588,7 +633,6 @@ decode_reg_kernel(const DecodeKArgs a) {
         }
     } else {
         const int et = tid - (1 + kRConsumerWarps) * 32;
-        constexpr int kNOut = GU ? 16 * kDecodeTokens : 32 * kDecodeTokens;  // outputs per item
         uint32_t item_local = 0;
         bool dead = false;
         while (!dead && next_run_x<GU>(a, it, it1, cur, NKB * 4, run)) {
@@ -599,28 +643,7 @@ decode_reg_kernel(const DecodeKArgs a) {
                     dead = true;
                     break;
                 }
-                for (int o = et; o < kNOut; o += kREpiWarps * 32) {
-                    // gate/up: o = n*16 + r, sums of both half units; down: o = n*32 + m*16 + r
-                    const int r = o & 15;
-                    const int m = GU ? 0 : (o >> 4) & 1;
-                    const int n = GU ? o >> 4 : o >> 5;
-                    if (n >= run.ntok) continue;
-                    const int L = ((r & 7) << 2) + (n >> 1);
-                    const int c = ((r >> 3) << 1) + (n & 1);
-                    const float* rbuf = red + (size_t)rb * kRRedFloats + m * 128 + c * 32 + L;
-                    const long long slot = run.slot_begin + n;
-                    if (GU) {
-                        float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-                        for (int w = 0; w < kRConsumerWarps; ++w) { s0 += rbuf[(size_t)w * 256]; s1 += rbuf[(size_t)w * 256 + 128]; }
-                        a.hbuf[slot * a.ldh + frag_pos(unit * 16 + r)] = __float2half_rn(__fmul_rn(silu_ref(s0), s1));
-                    } else {
-                        float s0 = 0.f;
-#pragma unroll
-                        for (int w = 0; w < kRConsumerWarps; ++w) s0 += rbuf[(size_t)w * 256];
-                        a.ybuf[slot * a.H + unit * 32 + m * 16 + r] = s0;
-                    }
-                }
+                reduce_item<GU>(a, red + (size_t)rb * kRRedFloats, et, unit, run.slot_begin, run.ntok);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&red_free[rb]);
             }
