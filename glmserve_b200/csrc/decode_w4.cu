@@ -200,6 +200,16 @@ __device__ __forceinline__ void unpack8(uint32_t w, uint32_t& lo0, uint32_t& hi0
     hi1 = w8 & 0x00f000f0u;
 }
 
+// d = a * b (no accumulator input: the first product of a chain needs no zeroed registers)
+__device__ __forceinline__ void mma_16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                           uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -526,16 +536,16 @@ decode_reg_kernel(const DecodeKArgs a) {
 
     if (warp == kRConsumerWarps) {
         if (lane == 0) {  // register-resident variant: producer
-            uint32_t q = 0;
+            uint32_t slot = 0, ph = 0;   // ring position and the parity of its current use
             bool dead = false;
             while (!dead && !*abort_flag && next_run_x<GU>(a, it, it1, cur, NKB * 4, run)) {
                 const uint8_t* src = run.chunks;
                 const int nst = (run.uend - run.ubeg) * NKB;  // the run's units are contiguous in memory
-                for (int i = 0; i < nst; ++i, ++q, src += kRStageBytes) {
-                    const uint32_t slot = q % nstage, ph = (q / nstage) & 1u;
+                for (int i = 0; i < nst; ++i, src += kRStageBytes) {
                     if (!mbar_wait(&empty[slot], ph ^ 1u, kWaitLimit)) { record_timeout(a, abort_flag, 11); dead = true; break; }
                     mbar_arrive_expect_tx(&full[slot], kRStageBytes);
                     bulk_g2s(ring + (size_t)slot * kRStageBytes, src, kRStageBytes, &full[slot]);
+                    if (++slot == (uint32_t)nstage) { slot = 0; ph ^= 1u; }
                 }
             }
         }
@@ -548,7 +558,8 @@ decode_reg_kernel(const DecodeKArgs a) {
         float* red_lane = red + (size_t)cw * 256 + lane;
         uint4 xf[NKB][4];
         float2 sxv[NKB];
-        uint32_t q = 0, item_local = 0;
+        uint32_t slot = 0, ph = 0;   // ring position and parity, stepped instead of divided out
+        uint32_t rb = 0, rph = 0;    // partial-sum buffer and the parity of its current use
         bool dead = false;
         int cur_key = -1;
         while (!dead && next_run_x<GU>(a, it, it1, cur, NKB * 4, run)) {
@@ -574,15 +585,14 @@ decode_reg_kernel(const DecodeKArgs a) {
                     }
                     sg += __shfl_xor_sync(0xffffffffu, sg, 1);
                     sg += __shfl_xor_sync(0xffffffffu, sg, 2);
-                    sxv[st].x = __shfl_sync(0xffffffffu, sg, (2 * t) * 4);
-                    sxv[st].y = __shfl_sync(0xffffffffu, sg, (2 * t + 1) * 4);
+                    sxv[st].x = -8.f * __shfl_sync(0xffffffffu, sg, (2 * t) * 4);      // the zero-point term
+                    sxv[st].y = -8.f * __shfl_sync(0xffffffffu, sg, (2 * t + 1) * 4);
                 }
             }
-            for (int unit = run.ubeg; unit < run.uend && !dead; ++unit, ++item_local) {
+            for (int unit = run.ubeg; unit < run.uend && !dead; ++unit) {
                 float tot[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
-                for (int st = 0; st < NKB; ++st, ++q) {
-                    const uint32_t slot = q % nstage, ph = (q / nstage) & 1u;
+                for (int st = 0; st < NKB; ++st) {
                     if (!mbar_wait(&full[slot], ph, kWaitLimit)) { record_timeout(a, abort_flag, 14); dead = true; break; }
                     __syncwarp();  // lanes leave the poll loop one by one; mma.sync wants them together
                     const uint8_t* stage = ring + (size_t)slot * kRStageBytes;
@@ -592,7 +602,7 @@ decode_reg_kernel(const DecodeKArgs a) {
                         const uint4 w1 = lds128(stage + w_off + m * 1024 + 512);
                         const __half* sc = reinterpret_cast<const __half*>(stage + sc_off + m * 32);
                         const float s0 = __half2float(sc[0]), s1 = __half2float(sc[8]);
-                        float alo[4] = {0.f, 0.f, 0.f, 0.f}, ahi[4] = {0.f, 0.f, 0.f, 0.f};
+                        float alo[4], ahi[4];
                         const uint32_t wa[4] = {w0.x, w0.y, w0.z, w0.w};
                         const uint32_t wb[4] = {w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
@@ -600,15 +610,20 @@ decode_reg_kernel(const DecodeKArgs a) {
                             uint32_t al0, ah0, al1, ah1, bl0, bh0, bl1, bh1;
                             unpack8(wa[j], al0, ah0, al1, ah1);
                             unpack8(wb[j], bl0, bh0, bl1, bh1);
-                            mma_16816(alo, al0, bl0, al1, bl1, xf[st][j].x, xf[st][j].z);
-                            mma_16816(ahi, ah0, bh0, ah1, bh1, xf[st][j].y, xf[st][j].w);
+                            if (j == 0) {
+                                mma_16816_first(alo, al0, bl0, al1, bl1, xf[st][j].x, xf[st][j].z);
+                                mma_16816_first(ahi, ah0, bh0, ah1, bh1, xf[st][j].y, xf[st][j].w);
+                            } else {
+                                mma_16816(alo, al0, bl0, al1, bl1, xf[st][j].x, xf[st][j].z);
+                                mma_16816(ahi, ah0, bh0, ah1, bh1, xf[st][j].y, xf[st][j].w);
+                            }
                         }
-                        // sum x*(n-8) = 2^24*(alo + ahi/16) - 8*sum(x); then the group scale
-                        const float S0 = s0 * 16777216.f, C0 = s0 * -8.f, S1 = s1 * 16777216.f, C1 = s1 * -8.f;
-                        tot[m][0] = fmaf(S0, fmaf(ahi[0], 0.0625f, alo[0]), fmaf(C0, sxv[st].x, tot[m][0]));
-                        tot[m][1] = fmaf(S0, fmaf(ahi[1], 0.0625f, alo[1]), fmaf(C0, sxv[st].y, tot[m][1]));
-                        tot[m][2] = fmaf(S1, fmaf(ahi[2], 0.0625f, alo[2]), fmaf(C1, sxv[st].x, tot[m][2]));
-                        tot[m][3] = fmaf(S1, fmaf(ahi[3], 0.0625f, alo[3]), fmaf(C1, sxv[st].y, tot[m][3]));
+                        // sum x*(n-8) = 2^24*(alo + ahi/16) - 8*sum(x), then the group scale;
+                        // sxv holds -8*sum(x)
+                        tot[m][0] = fmaf(s0, fmaf(fmaf(ahi[0], 0.0625f, alo[0]), 16777216.f, sxv[st].x), tot[m][0]);
+                        tot[m][1] = fmaf(s0, fmaf(fmaf(ahi[1], 0.0625f, alo[1]), 16777216.f, sxv[st].y), tot[m][1]);
+                        tot[m][2] = fmaf(s1, fmaf(fmaf(ahi[2], 0.0625f, alo[2]), 16777216.f, sxv[st].x), tot[m][2]);
+                        tot[m][3] = fmaf(s1, fmaf(fmaf(ahi[3], 0.0625f, alo[3]), 16777216.f, sxv[st].y), tot[m][3]);
                     }
                     // The stage goes back to the producer, whose bulk copy writes it through the async
                     // proxy.  Loads of this warp that are still in flight (the scale words feed only
@@ -618,10 +633,10 @@ decode_reg_kernel(const DecodeKArgs a) {
                     fence_proxy_async();  // generic-proxy reads of the stage before the async-proxy refill
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&empty[slot]);
+                    if (++slot == (uint32_t)nstage) { slot = 0; ph ^= 1u; }
                 }
                 if (dead) break;
-                const uint32_t rb = item_local % kRed;
-                if (!mbar_wait(&red_free[rb], ((item_local / kRed) & 1u) ^ 1u, kWaitLimit)) { record_timeout(a, abort_flag, 15); dead = true; break; }
+                if (!mbar_wait(&red_free[rb], rph ^ 1u, kWaitLimit)) { record_timeout(a, abort_flag, 15); dead = true; break; }
                 float* r = red_lane + (size_t)rb * kRRedFloats;
 #pragma unroll
                 for (int m = 0; m < 2; ++m)
@@ -629,16 +644,16 @@ decode_reg_kernel(const DecodeKArgs a) {
                     for (int c = 0; c < 4; ++c) r[m * 128 + c * 32] = tot[m][c];
                 __syncwarp();  // orders every lane's partials before the one release-arrive below
                 if (lane == 0) mbar_arrive(&red_full[rb]);
+                if (++rb == (uint32_t)kRed) { rb = 0; rph ^= 1u; }
             }
         }
     } else {
         const int et = tid - (1 + kRConsumerWarps) * 32;
-        uint32_t item_local = 0;
+        uint32_t rb = 0, rph = 0;
         bool dead = false;
         while (!dead && next_run_x<GU>(a, it, it1, cur, NKB * 4, run)) {
-            for (int unit = run.ubeg; unit < run.uend; ++unit, ++item_local) {
-                const uint32_t rb = item_local % kRed;
-                if (*abort_flag || !mbar_wait(&red_full[rb], (item_local / kRed) & 1u, kWaitLimit)) {
+            for (int unit = run.ubeg; unit < run.uend; ++unit) {
+                if (*abort_flag || !mbar_wait(&red_full[rb], rph, kWaitLimit)) {
                     if (!*abort_flag) record_timeout(a, abort_flag, 16);
                     dead = true;
                     break;
@@ -646,6 +661,7 @@ decode_reg_kernel(const DecodeKArgs a) {
                 reduce_item<GU>(a, red + (size_t)rb * kRRedFloats, et, unit, run.slot_begin, run.ntok);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&red_free[rb]);
+                if (++rb == (uint32_t)kRed) { rb = 0; rph ^= 1u; }
             }
         }
     }

@@ -152,9 +152,12 @@ router_logits_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
 // of expert rows g, g+8 and of token g, and the two k16 steps of the block use the first and
 // second half of those 16 bytes - the k index of an mma is only a label, so any assignment
 // of columns works as long as A and B use the same one.
-//   KSPLIT = 8, NT = 1 (n <= 128): the 8 warps of a block split the input dim and their
-//     partial tiles are added in warp order through shared memory -> many small blocks.
-//   KSPLIT = 1, NT = 4: a warp owns 16 experts x 32 tokens over the whole input dim.
+// The 8 warps of a block split the input dim and their partial tiles are added in warp order
+// through shared memory, so even a few tokens make many blocks:
+//   MT = 1, NT = 1 (n <= 128): 16 experts x 8 tokens per block;
+//   MT = 4, NT = 4 (n > 128): 64 experts x 32 tokens per block - a quarter of the re-reads of the
+//     activations from L2 (at 8192 tokens 132 us; a warp that walks the whole input dim alone
+//     waits on every load and took 600 us).
 // The result for a (token, expert) depends only on the variant, never on n or the grid.
 // The epilogue also stores sigmoid(logit) (scores, nullable) for the fused top-k.
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -166,22 +169,29 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT, int KSPLIT>
+template <int MT, int NT, int KSPLIT>
 __global__ void __launch_bounds__(256)
 router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr,
                          int n, int H, int E, float* __restrict__ logits, float* __restrict__ scores) {
-    __shared__ float red[KSPLIT > 1 ? 8 * 4 * 32 : 1];
+    extern __shared__ float red[];   // KSPLIT > 1: [8 warps][MT][NT][4][32] partial tiles
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int egroup = KSPLIT > 1 ? blockIdx.x : blockIdx.x * 8 + warp;
-    const int e0 = egroup * 16;
+    const int e0 = egroup * (16 * MT);
     const int t0 = blockIdx.y * (8 * NT);
     const int kslice = H / KSPLIT;
     const int kbeg = KSPLIT > 1 ? warp * kslice : 0;
-    const bool ra_ok = e0 + g < E, rb_ok = e0 + g + 8 < E;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    const uint4* pa = reinterpret_cast<const uint4*>(wr + (size_t)(ra_ok ? e0 + g : 0) * H + kbeg) + t;
-    const uint4* pb = reinterpret_cast<const uint4*>(wr + (size_t)(rb_ok ? e0 + g + 8 : 0) * H + kbeg) + t;
+    const uint4* pa[MT];
+    const uint4* pb[MT];
+    bool ra_ok[MT], rb_ok[MT];
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+        ra_ok[j] = e0 + j * 16 + g < E;
+        rb_ok[j] = e0 + j * 16 + g + 8 < E;
+        pa[j] = reinterpret_cast<const uint4*>(wr + (size_t)(ra_ok[j] ? e0 + j * 16 + g : 0) * H + kbeg) + t;
+        pb[j] = reinterpret_cast<const uint4*>(wr + (size_t)(rb_ok[j] ? e0 + j * 16 + g + 8 : 0) * H + kbeg) + t;
+    }
     const uint4* px[NT];
     bool x_ok[NT];
 #pragma unroll
@@ -190,33 +200,47 @@ router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
         x_ok[i] = tok < n;
         px[i] = reinterpret_cast<const uint4*>(x + (size_t)(x_ok[i] ? tok : 0) * H + kbeg) + t;
     }
-    float acc[NT][4];
+    float acc[MT][NT][4];
 #pragma unroll
-    for (int i = 0; i < NT; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+    for (int j = 0; j < MT; ++j)
+#pragma unroll
+        for (int i = 0; i < NT; ++i) { acc[j][i][0] = acc[j][i][1] = acc[j][i][2] = acc[j][i][3] = 0.f; }
     const int iters = kslice >> 5;
     if (e0 < E) {
-#pragma unroll 4
+        constexpr int kUnroll = MT * NT >= 8 ? 1 : (MT * NT >= 4 ? 2 : 4);   // loads in flight vs registers
+#pragma unroll kUnroll
         for (int it = 0; it < iters; ++it) {
-            const uint4 va = ra_ok ? __ldg(pa + it * 4) : zero;
-            const uint4 vb = rb_ok ? __ldg(pb + it * 4) : zero;
+            uint4 va[MT], vb[MT], vx[NT];
 #pragma unroll
-            for (int i = 0; i < NT; ++i) {
-                const uint4 vx = x_ok[i] ? __ldg(px[i] + it * 4) : zero;
-                mma_bf16_16816(acc[i], va.x, vb.x, va.y, vb.y, vx.x, vx.y);
-                mma_bf16_16816(acc[i], va.z, vb.z, va.w, vb.w, vx.z, vx.w);
+            for (int j = 0; j < MT; ++j) {
+                va[j] = ra_ok[j] ? __ldg(pa[j] + it * 4) : zero;
+                vb[j] = rb_ok[j] ? __ldg(pb[j] + it * 4) : zero;
             }
+#pragma unroll
+            for (int i = 0; i < NT; ++i) vx[i] = x_ok[i] ? __ldg(px[i] + it * 4) : zero;
+#pragma unroll
+            for (int j = 0; j < MT; ++j)
+#pragma unroll
+                for (int i = 0; i < NT; ++i) {
+                    mma_bf16_16816(acc[j][i], va[j].x, vb[j].x, va[j].y, vb[j].y, vx[i].x, vx[i].y);
+                    mma_bf16_16816(acc[j][i], va[j].z, vb[j].z, va[j].w, vb[j].w, vx[i].z, vx[i].w);
+                }
         }
     }
     if (KSPLIT > 1) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) red[(warp * 4 + c) * 32 + lane] = acc[0][c];
+        for (int j = 0; j < MT; ++j)
+#pragma unroll
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) red[(((warp * MT + j) * NT + i) * 4 + c) * 32 + lane] = acc[j][i][c];
         __syncthreads();
-        if (threadIdx.x < 128) {
-            const int c = threadIdx.x >> 5;   // lane keeps its (g,t); c = accumulator index
+        for (int o = threadIdx.x; o < MT * NT * 128; o += 256) {
+            const int c = (o >> 5) & 3, i = (o >> 7) % NT, j = (o >> 7) / NT;   // lane keeps its (g,t)
             float v = 0.f;
 #pragma unroll
-            for (int w = 0; w < 8; ++w) v += red[(w * 4 + c) * 32 + lane];
-            const int e = e0 + g + ((c >> 1) << 3), tok = t0 + 2 * t + (c & 1);
+            for (int w = 0; w < 8; ++w) v += red[(((w * MT + j) * NT + i) * 4 + c) * 32 + lane];
+            const int e = e0 + j * 16 + g + ((c >> 1) << 3), tok = t0 + i * 8 + 2 * t + (c & 1);
             if (e < E && tok < n) {
                 logits[(size_t)tok * E + e] = v;
                 if (scores) scores[(size_t)tok * E + e] = sigmoid_ref(v);
@@ -224,15 +248,17 @@ router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
         }
     } else {
 #pragma unroll
-        for (int i = 0; i < NT; ++i)
+        for (int j = 0; j < MT; ++j)
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int e = e0 + g + ((c >> 1) << 3), tok = t0 + i * 8 + 2 * t + (c & 1);
-                if (e < E && tok < n) {
-                    logits[(size_t)tok * E + e] = acc[i][c];
-                    if (scores) scores[(size_t)tok * E + e] = sigmoid_ref(acc[i][c]);
+            for (int i = 0; i < NT; ++i)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int e = e0 + j * 16 + g + ((c >> 1) << 3), tok = t0 + i * 8 + 2 * t + (c & 1);
+                    if (e < E && tok < n) {
+                        logits[(size_t)tok * E + e] = acc[j][i][c];
+                        if (scores) scores[(size_t)tok * E + e] = sigmoid_ref(acc[j][i][c]);
+                    }
                 }
-            }
     }
 }
 
@@ -248,10 +274,14 @@ int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n,
     if (H % 256 == 0) {
         if (n <= 128) {
             dim3 grid((unsigned)((E + 15) / 16), (unsigned)((n + 7) / 8));
-            router_logits_mma_kernel<1, 8><<<grid, 256, 0, s>>>(x, wr, n, H, E, logits, scores);
+            router_logits_mma_kernel<1, 1, 8><<<grid, 256, 8 * 512, s>>>(x, wr, n, H, E, logits, scores);
         } else {
-            dim3 grid((unsigned)((E + 127) / 128), (unsigned)((n + 31) / 32));
-            router_logits_mma_kernel<4, 1><<<grid, 256, 0, s>>>(x, wr, n, H, E, logits, scores);
+            constexpr int smem = 8 * 4 * 4 * 512;   // 64 KiB of partial tiles
+            if (cudaFuncSetAttribute(router_logits_mma_kernel<4, 4, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     smem) != cudaSuccess)
+                return GSB_ERR_CUDA;
+            dim3 grid((unsigned)((E + 63) / 64), (unsigned)((n + 31) / 32));
+            router_logits_mma_kernel<4, 4, 8><<<grid, 256, smem, s>>>(x, wr, n, H, E, logits, scores);
         }
         return launch_status();
     }
