@@ -235,7 +235,8 @@ int gsb_moe_layer_create(const gsb_moe_config* cfg, gsb_moe_layer** out) {
     if (c.hidden % c.group || c.moe_inter % c.group || c.hidden % 8 || c.moe_inter % 8 || c.group % 8)
         return GSB_ERR_UNSUPPORTED;
     if (c.shared_inter && (c.shared_inter % c.group || c.shared_inter % 8)) return GSB_ERR_UNSUPPORTED;
-    if (!c.router_w) return GSB_ERR_INVALID_ARG;
+    if (!c.router_w && !c.fixed_routing) return GSB_ERR_INVALID_ARG;
+    if (c.fixed_routing && c.ep_size > 1) return GSB_ERR_UNSUPPORTED;
     const bool raw = c.gate_q && c.gate_sc && c.up_q && c.up_sc && c.down_q && c.down_sc;
     const bool tiles = tile_shapes_ok(c);
     if (!raw && !tiles) return GSB_ERR_INVALID_ARG;
@@ -297,11 +298,17 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
         return GSB_ERR_UNSUPPORTED;
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
 
-    int st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden,
+    int st;
+    if (c.fixed_routing) {
+        if (logits_out) return GSB_ERR_INVALID_ARG;   // there are no logits
+        st = launch_fixed_routing(n, c.topk, ws.ids, ws.w, s);
+    } else {
+        st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden,
                                   c.n_experts, ws.logits, ws.scores, s);
-    if (st) return st;
-    st = launch_router_topk(ws.scores, c.e_bias, n, c.n_experts, c.topk, c.norm_topk,
-                            c.routed_scale, ws.ids, ws.w, s, true);
+        if (st) return st;
+        st = launch_router_topk(ws.scores, c.e_bias, n, c.n_experts, c.topk, c.norm_topk,
+                                c.routed_scale, ws.ids, ws.w, s, true);
+    }
     if (st) return st;
     if (logits_out && cudaMemcpyAsync(logits_out, ws.logits, (size_t)n * c.n_experts * sizeof(float),
                                       cudaMemcpyDeviceToDevice, s) != cudaSuccess)

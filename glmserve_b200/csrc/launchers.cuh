@@ -19,6 +19,7 @@ constexpr int kChunkBytes = 8448;
 constexpr int kDecodeTokens = 8;  // token rows per work item of the decode kernels
 
 // from_scores: `logits` already holds sigmoid scores
+int launch_fixed_routing(int n, int topk, int* ids, float* w, cudaStream_t s);
 int launch_router_topk(const float* logits, const float* e_bias, int n, int E, int topk,
                        int norm_topk, float routed_scale, int* ids, float* w, cudaStream_t s,
                        bool from_scores = false);

@@ -91,6 +91,19 @@ int launch_router_topk(const float* logits, const float* e_bias, int n, int E, i
     return launch_status();
 }
 
+// Router-less layers (a dense MLP cut into topk slices): slot k of every token is expert k, weight 1.
+__global__ void fixed_routing_kernel(int64_t total, int topk, int* __restrict__ ids, float* __restrict__ w) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) { ids[i] = (int)(i % topk); w[i] = 1.0f; }
+}
+
+int launch_fixed_routing(int n, int topk, int* ids, float* w, cudaStream_t s) {
+    const int64_t total = (int64_t)n * topk;
+    if (total == 0) return GSB_OK;
+    fixed_routing_kernel<<<(unsigned)((total + 255) / 256), 256, 0, s>>>(total, topk, ids, w);
+    return launch_status();
+}
+
 // ---- router logits -----------------------------------------------------------------
 // logits[t,e] = sum_i x[t,i] * Wr[e,i], bf16 inputs, fp32 accumulation.  A block stages TT
 // token rows in shared memory once, then each of its 8 warps owns one expert row: lanes

@@ -178,7 +178,8 @@ class MoELayer:
     upload.
     """
 
-    def __init__(self, L: dict, prepack: bool | None = None, keep_raw: bool = True, share_from=None):
+    def __init__(self, L: dict, prepack: bool | None = None, keep_raw: bool = True, share_from=None,
+                 fixed_routing: bool = False):
         """``share_from``: another MoELayer over the same weight tensors whose prepacked
         streams are reused (only router weight / bias / flags are taken from ``L``)."""
         self.H, self.E, self.topk, self.I, self.Is, self.group = (int(L[k]) for k in
@@ -202,7 +203,9 @@ class MoELayer:
             self._keep[name] = t
             return t.data_ptr()
 
-        cfg.router_w = hold("router_w", L["router_w"].to(torch.bfloat16).contiguous())
+        cfg.fixed_routing = int(fixed_routing)
+        if not fixed_routing:
+            cfg.router_w = hold("router_w", L["router_w"].to(torch.bfloat16).contiguous())
         if L.get("e_bias") is not None:
             cfg.e_bias = hold("e_bias", L["e_bias"].float().contiguous())
         names = ["gate", "up", "down"] + (["sg", "su", "sd"] if shared else [])
@@ -228,7 +231,7 @@ class MoELayer:
         self._h = handle
         self._ws = None
         self._ws_n = -1
-        self.device = L["router_w"].device
+        self.device = L["gate_q"].device if L.get("gate_q") is not None else L["router_w"].device
 
     def __del__(self):
         h = getattr(self, "_h", None)
@@ -314,6 +317,35 @@ class MoELayer:
 
 
 STAGES = ("moe.router", "moe.dispatch", "moe.gate_up", "moe.down", "moe.combine")
+
+
+class DenseMLP:
+    """A dense W4A16 SwiGLU MLP (the model's first, non-MoE layers: gate/up ``[I, H]``, down
+    ``[H, I]``, src/model_gpu.cpp:1432-1445) on the grouped MoE kernels.  SwiGLU is elementwise
+    over the intermediate dim, so ``down(silu(gate x) * up x)`` is the sum over slices of I of the
+    same expression on the slice: the I columns are cut into ``I / slice`` experts that every
+    token visits with weight 1 (``fixed_routing``), and the combine adds the slices in order.
+
+    gate_q/up_q uint8 ``[I, H/2]``, down_q uint8 ``[H, I/2]``, scales ``[rows, cols/128]``."""
+
+    def __init__(self, gate_q, gate_sc, up_q, up_sc, down_q, down_sc, slice_cols: int = 2048):
+        I, hb = gate_q.shape
+        H = hb * 2
+        if I % slice_cols:
+            slice_cols = I
+        E = I // slice_cols
+        gs = slice_cols // 128
+        L = dict(H=H, E=E, topk=E, I=slice_cols, Is=0, group=128, norm_topk=False, routed_scale=1.0,
+                 router_w=None, e_bias=None,
+                 gate_q=gate_q.reshape(E, slice_cols, hb), gate_sc=gate_sc.reshape(E, slice_cols, -1),
+                 up_q=up_q.reshape(E, slice_cols, hb), up_sc=up_sc.reshape(E, slice_cols, -1),
+                 down_q=down_q.reshape(H, E, slice_cols // 2).permute(1, 0, 2).contiguous(),
+                 down_sc=down_sc.reshape(H, E, gs).permute(1, 0, 2).contiguous())
+        self.layer = MoELayer(L, keep_raw=False, fixed_routing=True)
+        self.H, self.I = H, I
+
+    def forward(self, x_bf16, out=None, path=PATH_AUTO):
+        return self.layer.forward(x_bf16, out=out, path=path)
 
 
 def profile_enable(layer: MoELayer, max_forwards: int) -> None:

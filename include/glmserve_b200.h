@@ -197,6 +197,11 @@ typedef struct gsb_moe_config {
      * gsb_moe_layer_forward_ep only. */
     int ep_size;
     int ep_rank;
+    /* 1 = no router: every token goes to experts 0..topk-1 in that order with weight 1.0
+     * (router_w may be NULL, norm_topk / routed_scale / e_bias are ignored).  A dense SwiGLU MLP
+     * whose intermediate dim is cut into E = topk slices is exactly such a layer: the first
+     * dense layers of the model (src/model_gpu.cpp:1432-1445) run through the same kernels. */
+    int fixed_routing;
 } gsb_moe_config;
 
 typedef struct gsb_moe_layer gsb_moe_layer; /* opaque, host memory only */

@@ -185,6 +185,31 @@ def test_glm_scale_repeated_forwards_are_bit_identical(dev, glm_layer, path_name
     assert differing == 0, f"{differing} of {reps} forwards differ from the first"
 
 
+def test_glm_scale_batch_geometry_bit_parity(dev, glm_layer):
+    """A token's output does not depend on which other tokens share its call: a 64-token
+    chunk (speculative verify), the same tokens one at a time (decode) and in chunks of 5 give
+    the same bits - logits, routing and output.  This is the property the reference's
+    n-invariant kernels exist for (cuda/kernels.cuh:112-115, include/server.hpp:128-143).
+    The 200-token call takes the other router tiling and more than one group per expert."""
+    from glmserve_b200 import ops
+    layer, _ = glm_layer
+    x = make_x_torch(200, 6144, seed=77, device=dev)
+    out_all, logits_all, ids_all, w_all = layer.forward(x, path=ops.PATH_DECODE, return_routing=True)
+    out_all, logits_all, ids_all, w_all = (t.clone() for t in (out_all, logits_all, ids_all, w_all))
+    out64, logits64, ids64, w64 = (t.clone() for t in layer.forward(x[:64], path=ops.PATH_DECODE, return_routing=True))
+    assert torch.equal(logits64, logits_all[:64]) and torch.equal(ids64, ids_all[:64])
+    assert torch.equal(w64, w_all[:64]) and torch.equal(out64, out_all[:64])
+    for t in (0, 1, 17, 63):
+        o, l, i, w = layer.forward(x[t:t + 1], path=ops.PATH_DECODE, return_routing=True)
+        assert torch.equal(l[0], logits_all[t]), f"token {t}: logits differ between n=1 and n=200"
+        assert torch.equal(i[0], ids_all[t]) and torch.equal(w[0], w_all[t])
+        assert torch.equal(o[0], out_all[t]), f"token {t}: output differs between n=1 and n=200"
+    for beg in range(0, 20, 5):
+        o = layer.forward(x[beg:beg + 5], path=ops.PATH_DECODE)
+        assert torch.equal(o, out_all[beg:beg + 5]), f"chunk at {beg}: output differs"
+    assert layer.status() == 0
+
+
 def test_glm_scale_prefill(dev, glm_layer):
     """GLM-scale layer through the tcgen05 path at 512 tokens (about 16 rows per expert)."""
     from glmserve_b200 import ops
