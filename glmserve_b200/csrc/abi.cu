@@ -299,17 +299,53 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
 
     int st;
+    // decode-sized batches on the tile-stream decode path: the logits launch also converts the
+    // activations, and one block does top-k + dispatch + work lists (inside launch_decode_layer)
+    const bool decode_path = path == GSB_PATH_DECODE || path == GSB_PATH_DECODE_SMEM;
+    const bool fused = decode_path && !c.fixed_routing && c.hidden % 256 == 0 &&
+                       decode_route_fusable(n, c.topk, c.n_experts);
     if (c.fixed_routing) {
         if (logits_out) return GSB_ERR_INVALID_ARG;   // there are no logits
         st = launch_fixed_routing(n, c.topk, ws.ids, ws.w, s);
     } else {
         st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden,
-                                  c.n_experts, ws.logits, ws.scores, s);
+                                  c.n_experts, ws.logits, ws.scores, s, fused ? ws.xp : nullptr);
         if (st) return st;
-        st = launch_router_topk(ws.scores, c.e_bias, n, c.n_experts, c.topk, c.norm_topk,
-                                c.routed_scale, ws.ids, ws.w, s, true);
+        if (!fused)
+            st = launch_router_topk(ws.scores, c.e_bias, n, c.n_experts, c.topk, c.norm_topk,
+                                    c.routed_scale, ws.ids, ws.w, s, true);
     }
     if (st) return st;
+    mark(1);
+    if (fused) {
+        DecodeArgs d{};
+        d.force_smem_variant = path == GSB_PATH_DECODE_SMEM ? 1 : 0;
+        d.x = x; d.n = n; d.topk = c.topk; d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter;
+        d.E = c.n_experts;
+        d.gate_up_packed = c.gate_up_packed; d.down_packed = c.down_packed;
+        d.shared_gate_up_packed = c.shared_gate_up_packed; d.shared_down_packed = c.shared_down_packed;
+        d.expert_offsets = ws.expert_offsets; d.sorted_tok = ws.sorted_tok; d.slot_pos = ws.slot_pos;
+        d.topk_w = ws.w; d.segs = ws.segs; d.xp = ws.xp; d.hbuf = ws.hbuf; d.ybuf = ws.ybuf;
+        d.status = ws.status; d.out = out; d.sm_count = layer->sm_count;
+        d.fused_route = 1; d.xp_ready = 1;
+        d.scores = ws.scores; d.e_bias = c.e_bias; d.norm_topk = c.norm_topk; d.routed_scale = c.routed_scale;
+        d.ids = ws.ids; d.w_out = ws.w; d.sorted_row = ws.sorted_row;
+        if (ev) { d.ev_prep = ev[2]; d.ev_gate_up = ev[3]; d.ev_down = ev[4]; }
+        st = launch_decode_layer(d, s);
+        mark(5);
+        if (st) return st;
+        // routing outputs exist only after the fused block has run
+        if (logits_out && cudaMemcpyAsync(logits_out, ws.logits, (size_t)n * c.n_experts * sizeof(float),
+                                          cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+            return GSB_ERR_CUDA;
+        if (ids_out && cudaMemcpyAsync(ids_out, ws.ids, (size_t)n * c.topk * sizeof(int),
+                                       cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+            return GSB_ERR_CUDA;
+        if (weights_out && cudaMemcpyAsync(weights_out, ws.w, (size_t)n * c.topk * sizeof(float),
+                                           cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+            return GSB_ERR_CUDA;
+        return GSB_OK;
+    }
     if (logits_out && cudaMemcpyAsync(logits_out, ws.logits, (size_t)n * c.n_experts * sizeof(float),
                                       cudaMemcpyDeviceToDevice, s) != cudaSuccess)
         return GSB_ERR_CUDA;
@@ -320,7 +356,6 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
                                        cudaMemcpyDeviceToDevice, s) != cudaSuccess)
         return GSB_ERR_CUDA;
 
-    mark(1);
     if (path == GSB_PATH_DIRECT) {
         if (!(c.gate_q && c.gate_sc && c.up_q && c.up_sc && c.down_q && c.down_sc))
             return GSB_ERR_UNSUPPORTED;

@@ -84,4 +84,32 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
         : "memory");
 }
 
+// position (in halves) of feature f inside a fragment-ordered row: within each block of
+// 128 features the sixteen 8-feature groups are stored transposed (group 4t+j at 4j+t), so
+// that the four lanes of a quad read adjacent 16-byte pieces.
+__device__ __host__ __forceinline__ int frag_pos(int f) {
+    const int kb = f >> 7, kk = f & 127;
+    const int t = kk >> 5, j = (kk >> 3) & 3, el = kk & 7;
+    return (kb << 7) + (((j << 2) + t) << 3) + el;
+}
+
+// One 8-feature group of a bf16 row -> fp16 at its fragment-order position (exact for |x| in
+// the fp16 normal range; values beyond +-65504 saturate to the largest finite fp16).
+__device__ __forceinline__ void xprep_group(const __nv_bfloat16* __restrict__ x, __half* __restrict__ xp,
+                                            int64_t row, int grp, int H) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + row * H) + grp);
+    const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&v);
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        float2 f = __bfloat1622float2(bp[q]);
+        f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
+        f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
+        const __half2 h = __floats2half2_rn(f.x, f.y);
+        op[q] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(xp + row * H + frag_pos(grp << 3)) = o;
+}
+
 }  // namespace gsb

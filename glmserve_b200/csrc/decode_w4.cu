@@ -20,8 +20,11 @@
 // depend on the grid or on timing.  Every wait is bounded: on a timeout the CTA records
 // where in the status word and all its loops leave.
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "launchers.cuh"
+#include "route_device.cuh"
 
 namespace gsb {
 
@@ -225,15 +228,6 @@ __device__ __forceinline__ uint4 lds128(const void* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "r"(smem_u32(p)));
     return v;
-}
-
-// position (in halves) of feature f inside a fragment-ordered row: within each block of
-// 128 features the sixteen 8-feature groups are stored transposed (group 4t+j at 4j+t), so
-// that the four lanes of a quad read adjacent 16-byte pieces.
-__device__ __host__ __forceinline__ int frag_pos(int f) {
-    const int kb = f >> 7, kk = f & 127;
-    const int t = kk >> 5, j = (kk >> 3) & 3, el = kk & 7;
-    return (kb << 7) + (((j << 2) + t) << 3) + el;
 }
 
 template <bool GU>
@@ -671,10 +665,9 @@ decode_reg_kernel(const DecodeKArgs a) {
 // segs[0] = number of segments, segs[1] = number of shared-expert segments (these come
 // first), then int4 {expert, first slot, tokens (<= 8), 0} per segment.  Built on the device
 // from the dispatch offsets - no host synchronisation.
-__global__ void __launch_bounds__(1024)
-seg_build_kernel(const int* __restrict__ expert_offsets, int E, int n, int P, int has_shared,
-                 int* __restrict__ segs, int* __restrict__ xsegs, int units_gu, int units_gu_s, int units_dn,
-                 int grid) {
+__device__ __forceinline__ void seg_build_block(const int* __restrict__ expert_offsets, int E, int n, int P,
+                                                int has_shared, int* __restrict__ segs, int* __restrict__ xsegs,
+                                                int units_gu, int units_gu_s, int units_dn, int grid) {
     __shared__ int wsum[32];
     __shared__ int pre_s[1025];   // exclusive prefix of token groups over routed experts
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
@@ -706,7 +699,7 @@ seg_build_kernel(const int* __restrict__ expert_offsets, int E, int n, int P, in
     int4* out = reinterpret_cast<int4*>(segs + kSegHeader);
     for (int j = 0; j < ng; ++j)
         out[base + j] = make_int4(tid, beg + j * kDecodeTokens, min(kDecodeTokens, cnt - j * kDecodeTokens), 0);
-    for (int j = tid; j < nsh; j += blockDim.x)
+    for (int j = tid; j < nsh; j += 1024)
         out[j] = make_int4(E, P + j * kDecodeTokens, min(kDecodeTokens, n - j * kDecodeTokens), 0);
     if (!xsegs) return;
     // expert list of the register-resident variant: experts that received tokens only, so that
@@ -762,7 +755,7 @@ seg_build_kernel(const int* __restrict__ expert_offsets, int E, int n, int P, in
     }
     // entry in which each CTA's first item falls (largest entry whose first item <= target)
     int* cta = xsegs + kXHeader + nent * kXEntry;
-    for (int job = tid; job < 2 * (grid + 1); job += blockDim.x) {
+    for (int job = tid; job < 2 * (grid + 1); job += 1024) {
         const int which = job / (grid + 1), c = job - which * (grid + 1);
         const long long U = which ? units_dn : units_gu, shi = which ? sh_dn : sh_gu;
         const long long total = shi + (long long)groups * U;
@@ -780,6 +773,48 @@ seg_build_kernel(const int* __restrict__ expert_offsets, int E, int n, int P, in
     }
 }
 
+__global__ void __launch_bounds__(1024)
+seg_build_kernel(const int* __restrict__ expert_offsets, int E, int n, int P, int has_shared,
+                 int* __restrict__ segs, int* __restrict__ xsegs, int units_gu, int units_gu_s, int units_dn,
+                 int grid) {
+    seg_build_block(expert_offsets, E, n, P, has_shared, segs, xsegs, units_gu, units_gu_s, units_dn, grid);
+}
+
+// Decode-sized batches (decode_route_fusable): top-k selection, dispatch and the work lists of
+// both GEMM kernels in ONE launch - a cluster of 8 blocks for the top-k, its first block for the
+// rest; three launches and their drain/fill gaps less per layer.  Each step is the stand-alone kernel's body, so ids, weights,
+// permutation and lists are the same bits.
+struct RouteFusedArgs {
+    const float* scores; const float* e_bias;
+    int n, E, topk, norm_topk; float routed_scale;
+    int* ids; float* w;
+    int* expert_offsets; int* sorted_tok; int* sorted_row; int* slot_pos;
+    int has_shared; int* segs; int* xsegs; int units_gu, units_gu_s, units_dn, grid;
+    int* status;
+};
+
+constexpr int kRouteCluster = 8;   // CTAs that share the top-k phase
+
+__global__ void __cluster_dims__(kRouteCluster, 1, 1) __launch_bounds__(1024)
+route_fused_kernel(const RouteFusedArgs a) {
+    extern __shared__ int route_smem[];
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (rank == 0 && threadIdx.x < 4) a.status[threadIdx.x] = 0;
+    // top-k: a warp per token over the whole cluster (one block alone spends 15 us on 64 tokens)
+    for (int t = rank * 32 + warp; t < a.n; t += kRouteCluster * 32)
+        topk_token<8, true>(a.scores + (size_t)t * a.E, a.e_bias, a.E, a.topk, a.norm_topk, a.routed_scale, lane,
+                            a.ids + (size_t)t * a.topk, a.w + (size_t)t * a.topk);
+    cluster.sync();    // hardware barrier with release/acquire: every CTA's ids are visible to CTA 0
+    if (rank != 0) return;
+    dispatch_block(a.ids, a.n * a.topk, a.topk, a.E, a.expert_offsets, a.sorted_tok, a.sorted_row, a.slot_pos, route_smem);
+    __syncthreads();   // the block's own global writes (expert_offsets) are visible to it from here
+    seg_build_block(a.expert_offsets, a.E, a.n, a.n * a.topk, a.has_shared, a.segs, a.xsegs, a.units_gu,
+                    a.units_gu_s, a.units_dn, a.grid);
+}
+
 // bf16 activations -> fp16 in fragment order (exact for |x| in the fp16 normal range; values
 // beyond +-65504 saturate to the largest finite fp16).
 __global__ void __launch_bounds__(256)
@@ -788,20 +823,7 @@ xprep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ xp, int64
     const int gpr = H >> 3;
     if (i >= n * gpr) return;
     const int64_t row = i / gpr;
-    const int grp = (int)(i - row * gpr);
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + row * H) + grp);
-    const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&v);
-    uint4 o;
-    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        float2 f = __bfloat1622float2(bp[q]);
-        f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
-        f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
-        const __half2 h = __floats2half2_rn(f.x, f.y);
-        op[q] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-    *reinterpret_cast<uint4*>(xp + row * H + frag_pos(grp << 3)) = o;
+    xprep_group(x, xp, row, (int)(i - row * gpr), H);
 }
 
 // Deterministic weighted combine (replaces the in-kernel slot sum of
@@ -896,13 +918,27 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     const bool shared = d.Is > 0;
     const int imax = d.I > d.Is ? d.I : d.Is;
     if (d.E > 1024) return GSB_ERR_UNSUPPORTED;
-    if (cudaMemsetAsync(d.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
-
-    xprep_kernel<<<(unsigned)(((int64_t)d.n * (d.H >> 3) + 255) / 256), 256, 0, s>>>(d.x, d.xp, d.n, d.H);
-    int* xsegs = d.segs + xsegs_offset_ints(d.n, d.topk, d.E);
     if (d.sm_count > 1024) return GSB_ERR_UNSUPPORTED;
-    seg_build_kernel<<<1, 1024, 0, s>>>(d.expert_offsets, d.E, d.n, P, shared ? 1 : 0, d.segs, xsegs, d.I / 16,
-                                        shared ? d.Is / 16 : 1, d.H / 32, d.sm_count);
+    if (!d.xp_ready)
+        xprep_kernel<<<(unsigned)(((int64_t)d.n * (d.H >> 3) + 255) / 256), 256, 0, s>>>(d.x, d.xp, d.n, d.H);
+    int* xsegs = d.segs + xsegs_offset_ints(d.n, d.topk, d.E);
+    if (d.fused_route) {
+        if (!decode_route_fusable(d.n, d.topk, d.E)) return GSB_ERR_INVALID_ARG;
+        RouteFusedArgs r{};
+        r.scores = d.scores; r.e_bias = d.e_bias; r.n = d.n; r.E = d.E; r.topk = d.topk;
+        r.norm_topk = d.norm_topk; r.routed_scale = d.routed_scale; r.ids = d.ids; r.w = d.w_out;
+        r.expert_offsets = const_cast<int*>(d.expert_offsets); r.sorted_tok = const_cast<int*>(d.sorted_tok);
+        r.sorted_row = d.sorted_row; r.slot_pos = const_cast<int*>(d.slot_pos);
+        r.has_shared = shared ? 1 : 0; r.segs = d.segs; r.xsegs = xsegs;
+        r.units_gu = d.I / 16; r.units_gu_s = shared ? d.Is / 16 : 1; r.units_dn = d.H / 32; r.grid = d.sm_count;
+        r.status = d.status;
+        const size_t smem = (size_t)(kDispWarps * d.E + 1024) * sizeof(int);   // 36 KiB at 256 experts
+        route_fused_kernel<<<kRouteCluster, 1024, smem, s>>>(r);
+    } else {
+        if (cudaMemsetAsync(d.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
+        seg_build_kernel<<<1, 1024, 0, s>>>(d.expert_offsets, d.E, d.n, P, shared ? 1 : 0, d.segs, xsegs, d.I / 16,
+                                            shared ? d.Is / 16 : 1, d.H / 32, d.sm_count);
+    }
     if (d.ev_prep) cudaEventRecord(d.ev_prep, s);
 
     DecodeKArgs g{};

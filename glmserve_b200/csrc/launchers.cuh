@@ -25,7 +25,7 @@ int launch_router_topk(const float* logits, const float* e_bias, int n, int E, i
                        bool from_scores = false);
 // scores (nullable): also store sigmoid(logit)
 int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n, int H, int E,
-                         float* logits, float* scores, cudaStream_t s);
+                         float* logits, float* scores, cudaStream_t s, __half* xp = nullptr);
 int launch_dispatch(const int* topk_ids, int n, int topk, int E, int* expert_offsets,
                     int* sorted_token_ids, int* sorted_row, int* slot_pos, cudaStream_t s);
 
@@ -85,8 +85,17 @@ struct DecodeArgs {
     int sm_count;
     int force_smem_variant;  // 1: always use the shared-memory-activation variant (testing)
     cudaEvent_t ev_prep, ev_gate_up, ev_down;  // optional stage marks (null = none)
+    // fused routing (decode_route_fusable): top-k, dispatch and the work lists run as one block
+    // inside launch_decode_layer; the caller has run neither launch_router_topk nor launch_dispatch,
+    // and expert_offsets / sorted_tok / slot_pos above are outputs as well
+    int fused_route;
+    const float* scores; const float* e_bias; int norm_topk; float routed_scale;
+    int* ids; float* w_out; int* sorted_row;
+    int xp_ready;            // 1: xp already holds the converted activations (logits launch did it)
 };
 int launch_decode_layer(const DecodeArgs& a, cudaStream_t s);
+// whether the single-block routing kernel covers this shape
+inline bool decode_route_fusable(int n, int topk, int E) { return n <= 128 && E <= 256 && topk <= 32 && n * topk <= 4096; }
 
 size_t prefill_tile_bytes(int n, int topk, int E, int H, int I);
 

@@ -6,76 +6,20 @@
 // are summed in selection order, divided by the sum when asked, and scaled.
 #include "common.cuh"
 #include "launchers.cuh"
+#include "route_device.cuh"
 
 namespace gsb {
 
-// sigmoid evaluated so it reproduces the CPU reference's 1.0f / (1.0f + std::exp(-x)):
-// exp in double then rounded once to float (what a correctly rounded expf returns), an
-// IEEE add and an IEEE divide.  No fast-math intrinsics on purpose.
-__device__ __forceinline__ float sigmoid_ref(float x) {
-    const float e = static_cast<float>(exp(static_cast<double>(-x)));
-    return __fdiv_rn(1.0f, __fadd_rn(1.0f, e));
-}
-
-// One warp per token.  Lane l owns experts l, l+32, ...; NS = slots per lane.
-// FROM_SCORES: the input already holds sigmoid scores (written by the logits kernel's
-// epilogue with the same sigmoid_ref), so no transcendental is evaluated here.
+// One warp per token.
 template <int NS, bool FROM_SCORES>
 __global__ void __launch_bounds__(128)
 router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ e_bias, int n,
                    int E, int topk, int norm_topk, float routed_scale, int* __restrict__ topk_ids,
                    float* __restrict__ topk_w) {
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
     if (t >= n) return;
-    const float* lt = logits + (size_t)t * E;
-    float score[NS], key[NS];
-#pragma unroll
-    for (int j = 0; j < NS; ++j) {
-        const int e = lane + (j << 5);
-        if (e < E) {
-            const float sc = FROM_SCORES ? lt[e] : sigmoid_ref(lt[e]);
-            score[j] = sc;
-            key[j] = __fadd_rn(sc, e_bias ? e_bias[e] : 0.0f);
-        } else {
-            score[j] = 0.0f;
-            key[j] = 0.0f;
-        }
-    }
-    uint32_t taken = 0;  // bit j: slot j already selected
-    float wsum = 0.0f;
-    float myw = 0.0f;    // lane k keeps the weight of selection k (topk <= 32)
-    for (int k = 0; k < topk; ++k) {
-        // lane-local best among the slots still free: ascending j = ascending expert id,
-        // strict > keeps the smaller id on equal keys.
-        int be = 0x7fffffff;
-        float bk = 0.0f, bs = 0.0f;
-#pragma unroll
-        for (int j = 0; j < NS; ++j) {
-            const int e = lane + (j << 5);
-            const bool ok = (e < E) && !((taken >> j) & 1u);
-            if (ok && (be == 0x7fffffff || key[j] > bk)) { be = e; bk = key[j]; bs = score[j]; }
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            const int oe = __shfl_xor_sync(0xffffffffu, be, off);
-            const float ok = __shfl_xor_sync(0xffffffffu, bk, off);
-            const float os = __shfl_xor_sync(0xffffffffu, bs, off);
-            const bool take = (oe != 0x7fffffff) &&
-                              (be == 0x7fffffff || ok > bk || (ok == bk && oe < be));
-            if (take) { be = oe; bk = ok; bs = os; }
-        }
-        // every lane now holds the same winner
-        if ((be & 31) == lane && be != 0x7fffffff) taken |= 1u << (be >> 5);
-        if (lane == 0) topk_ids[(size_t)t * topk + k] = be == 0x7fffffff ? 0 : be;
-        wsum = __fadd_rn(wsum, bs);
-        if (lane == k) myw = bs;
-    }
-    if (lane < topk) {
-        float v = myw;
-        if (norm_topk && wsum > 0.0f) v = __fdiv_rn(v, wsum);
-        topk_w[(size_t)t * topk + lane] = __fmul_rn(v, routed_scale);
-    }
+    topk_token<NS, FROM_SCORES>(logits + (size_t)t * E, e_bias, E, topk, norm_topk, routed_scale, threadIdx.x & 31,
+                                topk_ids + (size_t)t * topk, topk_w + (size_t)t * topk);
 }
 
 int launch_router_topk(const float* logits, const float* e_bias, int n, int E, int topk,
@@ -185,8 +129,17 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 template <int MT, int NT, int KSPLIT>
 __global__ void __launch_bounds__(256)
 router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr,
-                         int n, int H, int E, float* __restrict__ logits, float* __restrict__ scores) {
+                         int n, int H, int E, float* __restrict__ logits, float* __restrict__ scores,
+                         __half* __restrict__ xp) {
     extern __shared__ float red[];   // KSPLIT > 1: [8 warps][MT][NT][4][32] partial tiles
+    if (xp && (int)blockIdx.x * (16 * MT) >= E) {
+        // one column of blocks beyond the experts: this block's token rows as fp16 in the decode
+        // kernels' fragment order (saves a launch; the logits blocks read the same rows anyway)
+        const int gpr = H >> 3, rows = min(8 * NT, n - (int)blockIdx.y * (8 * NT));
+        for (int i = threadIdx.x; i < rows * gpr; i += 256)
+            xprep_group(x, xp, (int64_t)blockIdx.y * (8 * NT) + i / gpr, i % gpr, H);
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int egroup = KSPLIT > 1 ? blockIdx.x : blockIdx.x * 8 + warp;
@@ -281,23 +234,25 @@ __global__ void sigmoid_scores_kernel(const float* __restrict__ logits, float* _
 }
 
 int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n, int H, int E,
-                         float* logits, float* scores, cudaStream_t s) {
+                         float* logits, float* scores, cudaStream_t s, __half* xp) {
     if (n == 0) return GSB_OK;
     if (H % 8 != 0) return GSB_ERR_UNSUPPORTED;
     if (H % 256 == 0) {
         if (n <= 128) {
-            dim3 grid((unsigned)((E + 15) / 16), (unsigned)((n + 7) / 8));
-            router_logits_mma_kernel<1, 1, 8><<<grid, 256, 8 * 512, s>>>(x, wr, n, H, E, logits, scores);
+            dim3 grid((unsigned)((E + 15) / 16) + (xp ? 1u : 0u), (unsigned)((n + 7) / 8));
+            router_logits_mma_kernel<1, 1, 8><<<grid, 256, 8 * 512, s>>>(x, wr, n, H, E, logits, scores, xp);
         } else {
             constexpr int smem = 8 * 4 * 4 * 512;   // 64 KiB of partial tiles
             if (cudaFuncSetAttribute(router_logits_mma_kernel<4, 4, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      smem) != cudaSuccess)
                 return GSB_ERR_CUDA;
             dim3 grid((unsigned)((E + 63) / 64), (unsigned)((n + 31) / 32));
-            router_logits_mma_kernel<4, 4, 8><<<grid, 256, smem, s>>>(x, wr, n, H, E, logits, scores);
+            if (xp) return GSB_ERR_INVALID_ARG;   // the fused conversion exists for decode-sized batches only
+            router_logits_mma_kernel<4, 4, 8><<<grid, 256, smem, s>>>(x, wr, n, H, E, logits, scores, nullptr);
         }
         return launch_status();
     }
+    if (xp) return GSB_ERR_INVALID_ARG;
     constexpr int TT = 8;
     const size_t smem = (size_t)TT * H * 2;
     if (smem > 200 * 1024) return GSB_ERR_UNSUPPORTED;
