@@ -27,6 +27,7 @@ struct Workspace {
     int* sorted_tok;          // [P]
     int* sorted_row;          // [P]
     int* slot_pos;            // [P]
+    int* disp_scratch;        // many-block dispatch: per-block expert counts
     int* segs;                // decode segments: int4 per segment, [kMaxSegHeader + nseg_max]
     __half* xp;               // [n, H] fp16 activations in fragment order
     __half* hbuf;             // [P + n, Imax] fp16 SwiGLU output in fragment order
@@ -58,6 +59,7 @@ Workspace carve(const gsb_moe_config& c, int n, void* base) {
     ws.sorted_tok = reinterpret_cast<int*>(take(P * sizeof(int)));
     ws.sorted_row = reinterpret_cast<int*>(take(P * sizeof(int)));
     ws.slot_pos = reinterpret_cast<int*>(take(P * sizeof(int)));
+    ws.disp_scratch = reinterpret_cast<int*>(take(dispatch_scratch_bytes(n, c.topk, c.n_experts)));
     ws.segs = reinterpret_cast<int*>(take(decode_seg_bytes(n, c.topk, c.n_experts)));
     ws.xp = reinterpret_cast<__half*>(take((size_t)n * c.hidden * sizeof(__half)));
     ws.hbuf = reinterpret_cast<__half*>(take((P + n) * imax * sizeof(__half)));
@@ -117,6 +119,23 @@ int gsb_moe_dispatch(const int* topk_ids, int n, int topk, int E, int* expert_of
     if ((int64_t)n * topk > (int64_t)1 << 30) return GSB_ERR_UNSUPPORTED;
     return launch_dispatch(topk_ids, n, topk, E, expert_offsets, sorted_token_ids, sorted_row,
                            nullptr, as_stream(stream));
+}
+
+size_t gsb_moe_dispatch_scratch_bytes(int n, int topk, int E) {
+    if (n <= 0 || topk <= 0 || E <= 0) return 0;
+    return dispatch_scratch_bytes(n, topk, E);
+}
+
+int gsb_moe_dispatch_ws(const int* topk_ids, int n, int topk, int E, int* expert_offsets,
+                        int* sorted_token_ids, int* sorted_row, void* scratch, size_t scratch_bytes,
+                        void* stream) {
+    if (n < 0 || E <= 0 || topk <= 0 || !expert_offsets) return GSB_ERR_INVALID_ARG;
+    if (n > 0 && (!topk_ids || !sorted_token_ids || !sorted_row)) return GSB_ERR_INVALID_ARG;
+    if ((int64_t)n * topk > (int64_t)1 << 30) return GSB_ERR_UNSUPPORTED;
+    if (scratch && (scratch_bytes < dispatch_scratch_bytes(n, topk, E) || !aligned(scratch, 4)))
+        return GSB_ERR_WORKSPACE;
+    return launch_dispatch(topk_ids, n, topk, E, expert_offsets, sorted_token_ids, sorted_row,
+                           nullptr, as_stream(stream), reinterpret_cast<int*>(scratch));
 }
 
 int gsb_moe_expert_ffn_w4a16(const float* x, const int* topk_ids, const float* topk_weights,
@@ -377,7 +396,7 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
     }
 
     st = launch_dispatch(ws.ids, n, c.topk, c.n_experts, ws.expert_offsets, ws.sorted_tok,
-                         ws.sorted_row, ws.slot_pos, s);
+                         ws.sorted_row, ws.slot_pos, s, ws.disp_scratch);
     if (st) return st;
     if (path == GSB_PATH_DECODE || path == GSB_PATH_DECODE_SMEM) {
         DecodeArgs d{};

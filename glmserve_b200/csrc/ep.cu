@@ -20,7 +20,7 @@ EpHeap ep_heap(const gsb_moe_config& c, int n, int recv_cap) {
 
 struct EpWs {
     int* status; float* logits; float* scores; int* ids; float* w; int* expert_offsets; int* sorted_tok;
-    int* sorted_row; int* slot_pos; int* sorted_expert; int* recv_offsets; int* send_base; void** ydst;
+    int* sorted_row; int* slot_pos; int* sorted_expert; int* disp_scratch; int* recv_offsets; int* send_base; void** ydst;
     int* recv_total; int* tiles_gu; int* tiles_dn; int* tiles_sh_gu; int* tiles_sh_dn;
     __half* hbuf; __half* xs_local; __half* hbuf_sh;
     size_t total;
@@ -45,6 +45,7 @@ EpWs ep_carve(const gsb_moe_config& c, int n, int recv_cap, void* base) {
     ws.sorted_row = reinterpret_cast<int*>(take(P * sizeof(int)));
     ws.slot_pos = reinterpret_cast<int*>(take(P * sizeof(int)));
     ws.sorted_expert = reinterpret_cast<int*>(take(P * sizeof(int)));
+    ws.disp_scratch = reinterpret_cast<int*>(take(dispatch_scratch_bytes(n, c.topk, c.n_experts)));
     ws.recv_offsets = reinterpret_cast<int*>(take((size_t)(El + 1) * sizeof(int)));
     ws.send_base = reinterpret_cast<int*>(take((size_t)c.n_experts * sizeof(int)));
     ws.ydst = reinterpret_cast<void**>(take((size_t)recv_cap * sizeof(void*)));
@@ -107,7 +108,8 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
         if (ids_out && cudaMemcpyAsync(ids_out, ws.ids, (size_t)P * sizeof(int), cudaMemcpyDeviceToDevice, s) != cudaSuccess)
             return GSB_ERR_CUDA;
     }
-    st = launch_dispatch(ws.ids, n, c.topk, E, ws.expert_offsets, ws.sorted_tok, ws.sorted_row, ws.slot_pos, s);
+    st = launch_dispatch(ws.ids, n, c.topk, E, ws.expert_offsets, ws.sorted_tok, ws.sorted_row, ws.slot_pos, s,
+                         ws.disp_scratch);
     if (st) return st;
     // counts -> plan -> push rows to their owners -> signal
     st = comm_ep_exchange(comm, x, ws.expert_offsets, ws.sorted_tok, P, E, c.hidden, ws.sorted_expert,

@@ -26,8 +26,10 @@ int launch_router_topk(const float* logits, const float* e_bias, int n, int E, i
 // scores (nullable): also store sigmoid(logit)
 int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n, int H, int E,
                          float* logits, float* scores, cudaStream_t s, __half* xp = nullptr);
+// scratch: dispatch_scratch_bytes() of device memory, or null (then one block does everything)
 int launch_dispatch(const int* topk_ids, int n, int topk, int E, int* expert_offsets,
-                    int* sorted_token_ids, int* sorted_row, int* slot_pos, cudaStream_t s);
+                    int* sorted_token_ids, int* sorted_row, int* slot_pos, cudaStream_t s, int* scratch = nullptr);
+size_t dispatch_scratch_bytes(int n, int topk, int E);
 
 struct GenericExpertArgs {
     const void* x;

@@ -77,26 +77,37 @@ __device__ __forceinline__ void topk_token(const float* __restrict__ lt, const f
 
 constexpr int kDispWarps = 32;
 
-// Body of the dispatch for one block of kDispWarps warps; smem holds kDispWarps * E + 1024 ints.
-__device__ __forceinline__ void dispatch_block(const int* __restrict__ topk_ids, int P, int topk, int E,
-                                               int* __restrict__ expert_offsets, int* __restrict__ sorted_token_ids,
-                                               int* __restrict__ sorted_row, int* __restrict__ slot_pos, int* smem) {
-    int* hist = smem;                        // [kDispWarps][E]
-    int* tot = smem + kDispWarps * E;        // [E rounded to 1024]
-    __shared__ int warp_sums[32];
+// The dispatch in three phases, so that one block (decode-sized batches) or many blocks (prefill)
+// can run it.  A block owns the contiguous slot range [b0, b1); its 32 warps own contiguous
+// sub-ranges.  smem holds kDispWarps * E + 1024 ints: hist [kDispWarps][E], tot [E].
+
+struct DispRange { int beg, end; };
+
+__device__ __forceinline__ DispRange dispatch_warp_range(int b0, int b1) {
+    int chunk = (b1 - b0 + kDispWarps - 1) / kDispWarps;
+    chunk = (chunk + 31) & ~31;
+    const int w = threadIdx.x >> 5;
+    DispRange r;
+    r.beg = min(b1, b0 + w * chunk);
+    r.end = min(b1, r.beg + chunk);
+    return r;
+}
+
+// Phase 1: per-warp histograms (no atomics: the lowest lane of each group of equal ids adds the
+// group size), then per expert an exclusive scan over the block's warps.  On return
+// hist[w][e] = slots of expert e owned by warps < w of this block, tot[e] = the block's count.
+__device__ __forceinline__ void dispatch_hist(const int* __restrict__ topk_ids, int b0, int b1, int E, int* smem) {
+    int* hist = smem;
+    int* tot = smem + kDispWarps * E;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     for (int i = tid; i < kDispWarps * E; i += (kDispWarps * 32)) hist[i] = 0;
     __syncthreads();
-
-    int chunk = (P + kDispWarps - 1) / kDispWarps;
-    chunk = (chunk + 31) & ~31;
-    const int beg = min(P, w * chunk), end = min(P, beg + chunk);
+    const DispRange r = dispatch_warp_range(b0, b1);
     const uint32_t lt_mask = (1u << lane) - 1u;
     int* myhist = hist + w * E;
-
-    for (int base = beg; base < end; base += 32) {
+    for (int base = r.beg; base < r.end; base += 32) {
         const int i = base + lane;
-        int id = (i < end) ? topk_ids[i] : -1;
+        int id = (i < r.end) ? topk_ids[i] : -1;
         const bool valid = id >= 0 && id < E;
         const int key = valid ? id : (-1 - lane);
         const uint32_t peers = __match_any_sync(0xffffffffu, key);
@@ -104,8 +115,6 @@ __device__ __forceinline__ void dispatch_block(const int* __restrict__ topk_ids,
         __syncwarp();
     }
     __syncthreads();
-
-    // per expert: exclusive scan over warps, total into tot[]
     for (int e = tid; e < E; e += (kDispWarps * 32)) {
         int run = 0;
         for (int ww = 0; ww < kDispWarps; ++ww) {
@@ -116,42 +125,50 @@ __device__ __forceinline__ void dispatch_block(const int* __restrict__ topk_ids,
         tot[e] = run;
     }
     __syncthreads();
-    // exclusive scan of tot[0..E) (E <= 1024 = blockDim): warp scans + scan of warp sums
-    {
-        const int v = tid < E ? tot[tid] : 0;
-        int incl = v;
+}
+
+// Exclusive scan of v over the block's first E threads (E <= 1024 = blockDim); every thread calls.
+__device__ __forceinline__ int dispatch_block_scan(int v, int* total) {
+    __shared__ int warp_sums[32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
+    }
+    if (lane == 31) warp_sums[w] = incl;
+    __syncthreads();
+    if (w == 0) {
+        const int s = warp_sums[lane];
+        int si = s;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const int u = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += u;
+            const int u = __shfl_up_sync(0xffffffffu, si, o);
+            if (lane >= o) si += u;
         }
-        if (lane == 31) warp_sums[w] = incl;
-        __syncthreads();
-        if (w == 0) {
-            const int s = warp_sums[lane];
-            int si = s;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int u = __shfl_up_sync(0xffffffffu, si, o);
-                if (lane >= o) si += u;
-            }
-            warp_sums[lane] = si - s;
-        }
-        __syncthreads();
-        const int excl = incl - v + warp_sums[w];
-        if (tid < E) {
-            tot[tid] = excl;
-            expert_offsets[tid] = excl;
-            if (tid == E - 1) expert_offsets[E] = excl + v;
-        }
+        warp_sums[lane] = si - s;
+        if (lane == 31 && total) *total = si;
     }
     __syncthreads();
-    for (int i = tid; i < kDispWarps * E; i += (kDispWarps * 32)) hist[i] += tot[i % E];
-    __syncthreads();
+    const int excl = incl - v + warp_sums[w];
+    __syncthreads();   // warp_sums may be reused by a later call
+    return excl;
+}
 
-    for (int base = beg; base < end; base += 32) {
+// Phase 3: hist[w][e] already holds the absolute start of (warp, expert); every warp walks its range
+// again in the same order.  A slot's position is that start + the equal ids in lower lanes, and the
+// group leader advances the start.  No position depends on an atomic or on timing.
+__device__ __forceinline__ void dispatch_scatter(const int* __restrict__ topk_ids, int b0, int b1, int topk, int E,
+                                                 int* __restrict__ sorted_token_ids, int* __restrict__ sorted_row,
+                                                 int* __restrict__ slot_pos, int* smem) {
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const DispRange r = dispatch_warp_range(b0, b1);
+    const uint32_t lt_mask = (1u << lane) - 1u;
+    int* myhist = smem + w * E;
+    for (int base = r.beg; base < r.end; base += 32) {
         const int i = base + lane;
-        int id = (i < end) ? topk_ids[i] : -1;
+        int id = (i < r.end) ? topk_ids[i] : -1;
         const bool valid = id >= 0 && id < E;
         const int key = valid ? id : (-1 - lane);
         const uint32_t peers = __match_any_sync(0xffffffffu, key);
@@ -165,6 +182,27 @@ __device__ __forceinline__ void dispatch_block(const int* __restrict__ topk_ids,
         if (valid && (peers & lt_mask) == 0) myhist[id] += __popc(peers);
         __syncwarp();
     }
+}
+
+// The whole dispatch in one block.
+__device__ __forceinline__ void dispatch_block(const int* __restrict__ topk_ids, int P, int topk, int E,
+                                               int* __restrict__ expert_offsets, int* __restrict__ sorted_token_ids,
+                                               int* __restrict__ sorted_row, int* __restrict__ slot_pos, int* smem) {
+    int* hist = smem;
+    int* tot = smem + kDispWarps * E;
+    const int tid = threadIdx.x;
+    dispatch_hist(topk_ids, 0, P, E, smem);
+    const int v = tid < E ? tot[tid] : 0;
+    const int excl = dispatch_block_scan(v, nullptr);
+    if (tid < E) {
+        tot[tid] = excl;
+        expert_offsets[tid] = excl;
+        if (tid == E - 1) expert_offsets[E] = excl + v;
+    }
+    __syncthreads();
+    for (int i = tid; i < kDispWarps * E; i += (kDispWarps * 32)) hist[i] += tot[i % E];
+    __syncthreads();
+    dispatch_scatter(topk_ids, 0, P, topk, E, sorted_token_ids, sorted_row, slot_pos, smem);
 }
 
 }  // namespace gsb

@@ -41,6 +41,22 @@ def moe_router(logits, e_bias, topk, norm_topk=True, routed_scale=2.5):
     return ids, w
 
 
+def moe_dispatch_ws(topk_ids, E):
+    """moe_dispatch with scratch: the many-block form above 8192 slots (same permutation)."""
+    _need(topk_ids, torch.int32, "topk_ids")
+    n, topk = topk_ids.shape
+    dev = topk_ids.device
+    offs = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    tok = torch.empty(n * topk, dtype=torch.int32, device=dev)
+    row = torch.empty(n * topk, dtype=torch.int32, device=dev)
+    lib().gsb_moe_dispatch_scratch_bytes.restype = C.c_size_t
+    nb = int(lib().gsb_moe_dispatch_scratch_bytes(n, topk, E))
+    scratch = torch.empty(max(nb, 4), dtype=torch.uint8, device=dev)
+    check(lib().gsb_moe_dispatch_ws(_p(topk_ids), n, topk, E, _p(offs), _p(tok), _p(row), _p(scratch),
+                                    C.c_size_t(scratch.numel()), _stream()), "moe_dispatch_ws")
+    return offs, tok, row
+
+
 def moe_dispatch(topk_ids, E):
     """cuda/kernels.cuh:249 moe_dispatch.  Returns (expert_offsets [E+1], sorted_token_ids,
     sorted_row), all int32."""

@@ -66,6 +66,15 @@ GSB_API int gsb_moe_router(const float* logits, const float* e_bias, int n, int 
 GSB_API int gsb_moe_dispatch(const int* topk_ids, int n, int topk, int E, int* expert_offsets,
                              int* sorted_token_ids, int* sorted_row, void* stream);
 
+/* The same dispatch with caller scratch (gsb_moe_dispatch_scratch_bytes bytes, 4-byte aligned):
+ * above 8192 slots the work is spread over one block per 4096 slots (count, offsets, scatter
+ * launches) instead of one block for everything - the reference's signature has no scratch
+ * argument, so gsb_moe_dispatch cannot.  Same permutation, bit for bit.  scratch may be NULL. */
+GSB_API size_t gsb_moe_dispatch_scratch_bytes(int n, int topk, int E);
+GSB_API int gsb_moe_dispatch_ws(const int* topk_ids, int n, int topk, int E, int* expert_offsets,
+                                int* sorted_token_ids, int* sorted_row, void* scratch,
+                                size_t scratch_bytes, void* stream);
+
 /* Replaces moe_expert_ffn_w4a16 (cuda/kernels.cuh:259-268, cuda/moe_expert.cu:132-244).
  * x f32 [n,hidden]; gate_q/up_q u8 [E,moe_inter,hidden/2], gate_sc/up_sc f32
  * [E,moe_inter,hidden/group]; down_q u8 [E,hidden,moe_inter/2], down_sc f32
