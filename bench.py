@@ -305,6 +305,31 @@ def run_ours(args) -> None:
         barrier()
         ms_ep = ea.elapsed_time(eb) / 5
         st_ep = st_ep or comm.status()
+        # the all-reduce alone, both algorithms, against NCCL as the baseline; the faster one is then
+        # set for the tensor-parallel layer (the choice changes no bit of the result)
+        buf = torch.zeros(T * GLM["H"], device=dev)
+        us_alg = {}
+        for name, limit in (("one_shot", 1 << 40), ("two_shot", 1)):
+            comm.allreduce_one_shot_limit(limit)
+            for _ in range(5):
+                comm.allreduce_sum(buf)
+            barrier(); ea.record()
+            for _ in range(50):
+                comm.allreduce_sum(buf)
+            eb.record(); barrier()
+            us_alg[name] = ea.elapsed_time(eb) / 50 * 1e3
+        ta = torch.tensor([us_alg["one_shot"], us_alg["two_shot"]], device=dev, dtype=torch.float64)
+        dist.all_reduce(ta, op=dist.ReduceOp.MAX)
+        us_alg = {"one_shot": float(ta[0]), "two_shot": float(ta[1])}
+        comm.allreduce_one_shot_limit((1 << 40) if us_alg["one_shot"] <= us_alg["two_shot"] else 1)
+        us_ar = min(us_alg.values())
+        for _ in range(5):
+            dist.all_reduce(buf)
+        barrier(); ea.record()
+        for _ in range(50):
+            dist.all_reduce(buf)
+        eb.record(); barrier()
+        us_nccl = ea.elapsed_time(eb) / 50 * 1e3
         # tensor parallel: decode batch, gate/up column split, down row split, NVLink all-reduce
         Ltp = shard_layer_tp_torch(Lt, rank, world, pad_to=512)
         layer_tp = ops.MoELayer(Ltp, keep_raw=False)
@@ -321,22 +346,6 @@ def run_ours(args) -> None:
         eb.record()
         barrier()
         ms_tp = ea.elapsed_time(eb) / args.steps
-        # the all-reduce alone, against NCCL as the baseline
-        buf = torch.randn(T * GLM["H"], device=dev)
-        for _ in range(5):
-            comm.allreduce_sum(buf)
-        barrier(); ea.record()
-        for _ in range(50):
-            comm.allreduce_sum(buf)
-        eb.record(); barrier()
-        us_ar = ea.elapsed_time(eb) / 50 * 1e3
-        for _ in range(5):
-            dist.all_reduce(buf)
-        barrier(); ea.record()
-        for _ in range(50):
-            dist.all_reduce(buf)
-        eb.record(); barrier()
-        us_nccl = ea.elapsed_time(eb) / 50 * 1e3
         st_tp = comm.status()
         tt = torch.tensor([ms_ep, ms_tp, us_ar, us_nccl, float(st_ep), float(st_tp)], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
@@ -346,7 +355,7 @@ def run_ours(args) -> None:
             "tflops_per_gpu": layer_flops(Te)["layer"] / (ms_ep * 1e-3) / 1e12, "recv_cap_rows": recv_cap,
             "status": int(tt[4]), "exchange": "in-kernel NVLink stores (dispatch push, combine from the down-GEMM epilogue)"}
         extra[f"tensor_parallel_T{T}"] = {"us_per_layer": ms_tp * 1e3, "tp": world, "allreduce_us": us_ar,
-                                          "nccl_allreduce_us": us_nccl, "allreduce_floats": T * GLM["H"],
+                                          "allreduce_us_by_algorithm": us_alg, "nccl_allreduce_us": us_nccl, "allreduce_floats": T * GLM["H"],
                                           "status": int(tt[5])}
         comm.close()
 

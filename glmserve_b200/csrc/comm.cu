@@ -351,6 +351,12 @@ size_t gsb_comm_allreduce_reserve(gsb_comm* c, int64_t max_count) {
     return 4 * fl * sizeof(float);
 }
 
+int gsb_comm_allreduce_one_shot_limit(gsb_comm* c, int64_t total_floats) {
+    if (!c || total_floats < 0) return GSB_ERR_INVALID_ARG;
+    c->ar_one_shot_limit = total_floats ? total_floats : (int64_t)(1 << 21);
+    return GSB_OK;
+}
+
 int gsb_comm_allreduce_sum(gsb_comm* c, float* data, int64_t count, void* stream) {
     if (!c || count < 0 || (count > 0 && !data)) return GSB_ERR_INVALID_ARG;
     if (c->world == 1 || count == 0) return GSB_OK;
@@ -363,7 +369,7 @@ int gsb_comm_allreduce_sum(gsb_comm* c, float* data, int64_t count, void* stream
     const size_t stage_off = kCtrlBytes + (size_t)parity * 2 * c->ar_stage_floats * sizeof(float);
     const size_t stage2_off = stage_off + c->ar_stage_floats * sizeof(float);
     const int64_t count4 = count / 4;
-    const int two_shot = count * c->world > (int64_t)(1 << 21) ? 1 : 0;
+    const int two_shot = count * c->world > c->ar_one_shot_limit ? 1 : 0;
     int sms = 148;
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

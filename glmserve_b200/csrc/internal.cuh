@@ -31,6 +31,7 @@ struct gsb_comm {
     bool opened[gsb::kMaxWorld] = {};
     unsigned seq[gsb::kNumCh] = {};
     size_t ar_stage_floats = 0;                 // capacity of the all-reduce staging (per parity)
+    int64_t ar_one_shot_limit = 1 << 21;        // count * world up to which every rank pulls everything
 };
 
 

@@ -41,6 +41,10 @@ class Comm:
     def heap_bytes(self) -> int:
         return int(lib().gsb_comm_heap_bytes(self._h))
 
+    def allreduce_one_shot_limit(self, total_floats: int) -> None:
+        """count * world up to which the all-reduce is a one-shot pull (0 = default 2**21)."""
+        check(lib().gsb_comm_allreduce_one_shot_limit(self._h, C.c_int64(total_floats)), "allreduce_one_shot_limit")
+
     def allreduce_sum(self, t):
         """In-place sum of a contiguous float32 CUDA tensor over all ranks (rank order)."""
         import torch

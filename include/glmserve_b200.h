@@ -334,6 +334,11 @@ GSB_API int gsb_comm_barrier(gsb_comm* comm, void* stream);
  * returns the bytes at the START of the heap that the all-reduce staging occupies. */
 GSB_API size_t gsb_comm_allreduce_reserve(gsb_comm* comm, int64_t max_count);
 GSB_API int gsb_comm_allreduce_sum(gsb_comm* comm, float* data, int64_t count, void* stream);
+/* Algorithm switch: messages with count * world <= total_floats take the one-shot pull (every rank
+ * reads every staging: least latency, world x the NVLink bytes), larger ones reduce-scatter +
+ * all-gather.  0 restores the default (2^21).  Same value on every rank; both orders of summation
+ * are rank 0..world-1 per element, so the result does not depend on the choice. */
+GSB_API int gsb_comm_allreduce_one_shot_limit(gsb_comm* comm, int64_t total_floats);
 
 /* Expert-parallel forward of one layer (cfg.ep_size = world): router and dispatch on this GPU's
  * n tokens, per-expert counts exchanged, rows pushed over NVLink into the owners' receive
