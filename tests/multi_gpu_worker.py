@@ -42,6 +42,17 @@ def main():
             comm.allreduce_sum(y)
             assert comm.status() == 0
             assert torch.equal(y, want), f"allreduce count={count} rep={rep}"
+    # the algorithm switch changes no bit: the same message through both forms
+    gen = torch.Generator(device=dev); gen.manual_seed(300 + rank)
+    x = torch.randn(64 * 6144, generator=gen, device=dev)
+    got = []
+    for limit in (1 << 40, 1, 0):                       # one-shot, two-shot, default
+        comm.allreduce_one_shot_limit(limit)
+        y = x.clone()
+        comm.allreduce_sum(y)
+        assert comm.status() == 0
+        got.append(y)
+    assert torch.equal(got[0], got[1]) and torch.equal(got[0], got[2]), "one-shot vs two-shot"
     rows = torch.randn((5, 6144), generator=torch.Generator(device=dev).manual_seed(7 + rank), device=dev)
     a, b = rows.clone(), rows.clone()
     comm.allreduce_sum(a.view(-1))
