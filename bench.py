@@ -288,7 +288,7 @@ def run_ours(args) -> None:
         recv_cap = 2 * Te * GLM["topk"]
         Lep = shard_layer_ep(Lt, rank, world)
         layer_ep = ops.MoELayer(Lep, keep_raw=False)
-        ar_max = 64 * GLM["H"]
+        ar_max = ar_max_v = 256 * GLM["H"]
         heap = layer_ep.ep_heap_bytes(Te, recv_cap) + 4 * ar_max * 4 + (4 << 20)
         comm = Comm(heap_bytes=heap, allreduce_max_count=ar_max)
         xe = make_x_torch(Te, GLM["H"], seed=300 + rank, device=dev)
@@ -346,8 +346,32 @@ def run_ours(args) -> None:
         eb.record()
         barrier()
         ms_tp = ea.elapsed_time(eb) / args.steps
+        # speculative-verify block under tensor parallelism: 8 x (RMSNorm -> sharded layer -> all-reduce ->
+        # residual), 256 tokens.  The eight layers share one set of sharded weights (a shard is far larger
+        # than L2, so every layer still streams it from HBM): timing only.
+        Tv, nl = 256, 8
+        ar_v = Tv * GLM["H"]
+        us_blk = None
+        if ar_v <= ar_max_v:
+            norm_w = torch.ones(GLM["H"], device=dev)
+            hv = make_x_torch(Tv, GLM["H"], seed=400, device=dev).float()
+            ov = torch.empty((Tv, GLM["H"]), dtype=torch.float32, device=dev)
+            def verify_block():
+                for _ in range(nl):
+                    xn = ops.rmsnorm(hv, norm_w, 1e-5).to(torch.bfloat16)
+                    layer_tp.forward(xn, out=ov, path=ops.PATH_DECODE)
+                    comm.allreduce_sum(ov.view(-1))
+                    hv.add_(ov)
+            for _ in range(2):
+                verify_block()
+            barrier(); ea.record()
+            for _ in range(3):
+                verify_block()
+            eb.record(); barrier()
+            us_blk = ea.elapsed_time(eb) / 3 * 1e3
         st_tp = comm.status()
-        tt = torch.tensor([ms_ep, ms_tp, us_ar, us_nccl, float(st_ep), float(st_tp)], device=dev, dtype=torch.float64)
+        tt = torch.tensor([ms_ep, ms_tp, us_ar, us_nccl, float(st_ep), float(st_tp), us_blk or 0.0], device=dev,
+                          dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms_ep, ms_tp, us_ar, us_nccl = (float(v) for v in tt[:4])
         extra["expert_parallel_T4096_per_gpu"] = {
@@ -357,6 +381,11 @@ def run_ours(args) -> None:
         extra[f"tensor_parallel_T{T}"] = {"us_per_layer": ms_tp * 1e3, "tp": world, "allreduce_us": us_ar,
                                           "allreduce_us_by_algorithm": us_alg, "nccl_allreduce_us": us_nccl, "allreduce_floats": T * GLM["H"],
                                           "status": int(tt[5])}
+        if float(tt[6]) > 0:
+            extra[f"spec_verify_block_8_layers_T256_tp{world}"] = {
+                "us_per_block": float(tt[6]), "us_per_layer": float(tt[6]) / nl,
+                "note": "RMSNorm -> tensor-parallel layer (decode kernels) -> NVLink all-reduce -> residual, "
+                        "x 8; the layers share one set of sharded weights"}
         comm.close()
 
     if world > 1:
