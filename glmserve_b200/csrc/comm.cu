@@ -59,6 +59,22 @@ __global__ void wait_kernel(CommPeers pr, int rank, int world, int ch, int seq) 
 // Phase 3 (one-shot): out[i] = sum over ranks in rank order of staging_r[i], read over NVLink.
 // Two-shot: phase 3 reduces only this rank's slice into a second staging area, posts a second
 // flag, and phase 4 gathers every owner's reduced slice.
+// Element i of every rank's staging, added in rank order.  The loads of up to eight ranks are issued
+// before the first add: a loop that adds as it loads waits one NVLink round trip per rank.
+__device__ __forceinline__ float4 sum_over_ranks(const CommPeers& pr, int world, size_t stage_off, int64_t i) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r0 = 0; r0 < world; r0 += 8) {
+        float4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (r0 + j < world) v[j] = reinterpret_cast<const float4*>(pr.base[r0 + j] + stage_off)[i];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (r0 + j < world) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+    }
+    return acc;
+}
+
 __global__ void __launch_bounds__(512)
 allreduce_kernel(CommPeers pr, int rank, int world, float* __restrict__ data, int64_t count4,
                  size_t stage_off, size_t stage2_off, int seq, int two_shot) {
@@ -87,14 +103,7 @@ allreduce_kernel(CommPeers pr, int rank, int world, float* __restrict__ data, in
     if (!ok) return;
     float4* out = reinterpret_cast<float4*>(data);
     if (!two_shot) {
-        for (int64_t i = i0; i < count4; i += stride) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int r = 0; r < world; ++r) {
-                const float4 v = reinterpret_cast<const float4*>(pr.base[r] + stage_off)[i];
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
-            out[i] = acc;
-        }
+        for (int64_t i = i0; i < count4; i += stride) out[i] = sum_over_ranks(pr, world, stage_off, i);
         return;
     }
     // two-shot: this rank owns slice [lo, hi)
@@ -102,11 +111,7 @@ allreduce_kernel(CommPeers pr, int rank, int world, float* __restrict__ data, in
     const int64_t lo = min(count4, per * rank), hi = min(count4, lo + per);
     float4* stage2 = reinterpret_cast<float4*>(pr.base[rank] + stage2_off);
     for (int64_t i = lo + i0; i < hi; i += stride) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < world; ++r) {
-            const float4 v = reinterpret_cast<const float4*>(pr.base[r] + stage_off)[i];
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
+        const float4 acc = sum_over_ranks(pr, world, stage_off, i);
         stage2[i] = acc;
         out[i] = acc;
     }
