@@ -117,13 +117,23 @@ router_logits_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
 //     waits on every load and took 600 us).
 // The result for a (token, expert) depends only on the variant, never on n or the grid.
 // The epilogue also stores sigmoid(logit) (scores, nullable) for the fused top-k.
+// ORDERED = false lets the compiler move loads across the mma (the small tiling batches its loads and
+// needs that freedom); the large tiling keeps the volatile form, whose schedule fits 128 registers
+// without spills.
+template <bool ORDERED>
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    if (ORDERED)
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    else
+        asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+            "{%0,%1,%2,%3};"
+            : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 template <int MT, int NT, int KSPLIT>
@@ -173,24 +183,54 @@ router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
         for (int i = 0; i < NT; ++i) { acc[j][i][0] = acc[j][i][1] = acc[j][i][2] = acc[j][i][3] = 0.f; }
     const int iters = kslice >> 5;
     if (e0 < E) {
-        constexpr int kUnroll = MT * NT >= 8 ? 1 : (MT * NT >= 4 ? 2 : 4);   // loads in flight vs registers
-#pragma unroll kUnroll
-        for (int it = 0; it < iters; ++it) {
-            uint4 va[MT], vb[MT], vx[NT];
+        // kBatch iterations' loads are issued before their mma: the loop is a chain of L2 round
+        // trips otherwise (a 16-expert x 8-token block has only three loads per iteration)
+        constexpr int kBatch = MT * NT >= 8 ? 1 : (MT * NT >= 4 ? 2 : 8);
+        if (kBatch == 1) {
+#pragma unroll 1
+            for (int it = 0; it < iters; ++it) {
+                uint4 va[MT], vb[MT], vx[NT];
 #pragma unroll
-            for (int j = 0; j < MT; ++j) {
-                va[j] = ra_ok[j] ? __ldg(pa[j] + it * 4) : zero;
-                vb[j] = rb_ok[j] ? __ldg(pb[j] + it * 4) : zero;
+                for (int j = 0; j < MT; ++j) {
+                    va[j] = ra_ok[j] ? __ldg(pa[j] + it * 4) : zero;
+                    vb[j] = rb_ok[j] ? __ldg(pb[j] + it * 4) : zero;
+                }
+#pragma unroll
+                for (int i = 0; i < NT; ++i) vx[i] = x_ok[i] ? __ldg(px[i] + it * 4) : zero;
+#pragma unroll
+                for (int j = 0; j < MT; ++j)
+#pragma unroll
+                    for (int i = 0; i < NT; ++i) {
+                        mma_bf16_16816<true>(acc[j][i], va[j].x, vb[j].x, va[j].y, vb[j].y, vx[i].x, vx[i].y);
+                        mma_bf16_16816<true>(acc[j][i], va[j].z, vb[j].z, va[j].w, vb[j].w, vx[i].z, vx[i].w);
+                    }
+            }
+        } else
+        for (int it0 = 0; it0 < iters; it0 += kBatch) {
+            uint4 va[kBatch][MT], vb[kBatch][MT], vx[kBatch][NT];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+                const int it = it0 + u;
+                const bool in = it < iters;
+#pragma unroll
+                for (int j = 0; j < MT; ++j) {
+                    va[u][j] = (in && ra_ok[j]) ? __ldg(pa[j] + it * 4) : zero;
+                    vb[u][j] = (in && rb_ok[j]) ? __ldg(pb[j] + it * 4) : zero;
+                }
+#pragma unroll
+                for (int i = 0; i < NT; ++i) vx[u][i] = (in && x_ok[i]) ? __ldg(px[i] + it * 4) : zero;
             }
 #pragma unroll
-            for (int i = 0; i < NT; ++i) vx[i] = x_ok[i] ? __ldg(px[i] + it * 4) : zero;
+            for (int u = 0; u < kBatch; ++u) {
+                if (it0 + u >= iters) break;   // zeros would add nothing, but keep the count exact
 #pragma unroll
-            for (int j = 0; j < MT; ++j)
+                for (int j = 0; j < MT; ++j)
 #pragma unroll
-                for (int i = 0; i < NT; ++i) {
-                    mma_bf16_16816(acc[j][i], va[j].x, vb[j].x, va[j].y, vb[j].y, vx[i].x, vx[i].y);
-                    mma_bf16_16816(acc[j][i], va[j].z, vb[j].z, va[j].w, vb[j].w, vx[i].z, vx[i].w);
-                }
+                    for (int i = 0; i < NT; ++i) {
+                        mma_bf16_16816<false>(acc[j][i], va[u][j].x, vb[u][j].x, va[u][j].y, vb[u][j].y, vx[u][i].x, vx[u][i].y);
+                        mma_bf16_16816<false>(acc[j][i], va[u][j].z, vb[u][j].z, va[u][j].w, vb[u][j].w, vx[u][i].z, vx[u][i].w);
+                    }
+            }
         }
     }
     if (KSPLIT > 1) {
