@@ -804,7 +804,7 @@ route_fused_kernel(const RouteFusedArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (rank == 0 && threadIdx.x < 4) a.status[threadIdx.x] = 0;
     // top-k: a warp per token over the whole cluster (one block alone spends 15 us on 64 tokens)
-    for (int t = rank * 32 + warp; t < a.n; t += kRouteCluster * 32)
+    for (int t = rank + kRouteCluster * warp; t < a.n; t += kRouteCluster * 32)   // tokens dealt round-robin to the CTAs
         topk_token<8, true>(a.scores + (size_t)t * a.E, a.e_bias, a.E, a.topk, a.norm_topk, a.routed_scale, lane,
                             a.ids + (size_t)t * a.topk, a.w + (size_t)t * a.topk);
     cluster.sync();    // hardware barrier with release/acquire: every CTA's ids are visible to CTA 0
