@@ -133,7 +133,6 @@ def time_layer(layer, x, out, path, steps, warmup, barrier, ops):
     for _ in range(max(warmup, 3)):
         layer.forward(x, out=out, path=path)
     assert layer.status() == 0, "device-side wait timed out during warm-up"
-    ops.profile_enable(layer, steps)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
@@ -142,6 +141,12 @@ def time_layer(layer, x, out, path, steps, warmup, barrier, ops):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1) / steps
+    # stage marks in a pass of their own: an event recorded between two kernels keeps the second from
+    # being scheduled under the first one's tail (programmatic dependent launch), which the timed
+    # steps above are allowed to do
+    ops.profile_enable(layer, steps)
+    for _ in range(steps):
+        layer.forward(x, out=out, path=path)
     stages = ops.profile_read(layer)
     ops.profile_enable(layer, 0)
     assert layer.status() == 0, "device-side wait timed out"

@@ -60,6 +60,9 @@ struct DecodeKArgs {
     int H;
     int nstage;
     int* status;
+    int pdl_trigger;               // 1: let the next launch start early (programmatic dependent launch)
+    int pdl_wait;                  // 1: launched early: wait for the previous grid before reading its output
+    int pdl_wait_all;              // 1: launched early and every warp needs the previous grid's output at once
     const int* xsegs;              // expert list of the register-resident variant (see xseg_* below)
     int x_which;                   // 0: gate/up item numbering, 1: down
 };
@@ -517,6 +520,14 @@ decode_reg_kernel(const DecodeKArgs a) {
     }
     __syncthreads();
 
+    // Programmatic dependent launch along routing -> gate/up -> down -> combine: a grid lets its
+    // successor be scheduled as SMs free up, and the successor waits (griddepcontrol.wait = the
+    // predecessor has completed and its writes are visible) before it touches the predecessor's
+    // output.  Gate/up needs the work lists at once, so all of it waits; the down kernel's producer
+    // warp streams weights under gate/up's tail and only its consumers wait (pdl_wait below).  Every
+    // grid waits before it ends, so completion is transitive along the chain.
+    if (a.pdl_wait_all) asm volatile("griddepcontrol.wait;" ::: "memory");   // the work lists come from the previous grid
+    if (a.pdl_trigger) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const long long total = a.xsegs[1 + a.x_which];
     const long long it0 = total * blockIdx.x / gridDim.x;
     const long long it1 = total * (blockIdx.x + 1) / gridDim.x;
@@ -556,6 +567,7 @@ decode_reg_kernel(const DecodeKArgs a) {
         uint32_t rb = 0, rph = 0;    // partial-sum buffer and the parity of its current use
         bool dead = false;
         int cur_key = -1;
+        if (a.pdl_wait) asm volatile("griddepcontrol.wait;" ::: "memory");   // the activations come from the previous grid
         while (!dead && next_run_x<GU>(a, it, it1, cur, NKB * 4, run)) {
             if (run.seg != cur_key) {   // this group's activation fragments and sums, into registers
                 cur_key = run.seg;
@@ -802,6 +814,7 @@ route_fused_kernel(const RouteFusedArgs a) {
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // gate/up may be scheduled; it waits for this grid
     if (rank == 0 && threadIdx.x < 4) a.status[threadIdx.x] = 0;
     // top-k: a warp per token over the whole cluster (one block alone spends 15 us on 64 tokens)
     for (int t = rank + kRouteCluster * warp; t < a.n; t += kRouteCluster * 32)   // tokens dealt round-robin to the CTAs
@@ -833,7 +846,8 @@ xprep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ xp, int64
 __global__ void __launch_bounds__(256)
 combine_kernel(const float* __restrict__ ybuf, const int* __restrict__ slot_pos,
                const float* __restrict__ topk_w, int n, int topk, int H, int P, int has_shared,
-               float* __restrict__ out) {
+               float* __restrict__ out, int pdl_wait) {
+    if (pdl_wait) asm volatile("griddepcontrol.wait;" ::: "memory");   // launched under the down kernel's tail
     const int t = blockIdx.y;
     const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
     if (c4 >= (H >> 2)) return;
@@ -902,7 +916,18 @@ static int launch_reg(const DecodeKArgs& k, int nkb, int grid, cudaStream_t s) {
         if (cudaFuncSetAttribute(decode_reg_kernel<GU, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                  (int)smem) != cudaSuccess)                                            \
             return GSB_ERR_CUDA;                                                                       \
-        decode_reg_kernel<GU, N><<<grid, RCfg<GU>::kThreads, smem, s>>>(a);                                    \
+        if (a.pdl_wait || a.pdl_wait_all) {                                                            \
+            cudaLaunchConfig_t cfg = {};                                                               \
+            cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(RCfg<GU>::kThreads);               \
+            cfg.dynamicSmemBytes = smem; cfg.stream = s;                                               \
+            cudaLaunchAttribute at[1];                                                                 \
+            at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                             \
+            at[0].val.programmaticStreamSerializationAllowed = 1;                                      \
+            cfg.attrs = at; cfg.numAttrs = 1;                                                          \
+            if (cudaLaunchKernelEx(&cfg, decode_reg_kernel<GU, N>, a) != cudaSuccess) return GSB_ERR_LAUNCH; \
+        } else {                                                                                       \
+            decode_reg_kernel<GU, N><<<grid, RCfg<GU>::kThreads, smem, s>>>(a);                        \
+        }                                                                                              \
         return GSB_OK;
     switch (nkb) {
         GSB_LAUNCH_REG(1)
@@ -951,6 +976,10 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     g.xsegs = xsegs; g.x_which = 0;
     // register-resident variant when the input dim is a multiple of 2048 (at most 3 x 2048)
     const bool gu_reg = !d.force_smem_variant && d.H % 2048 == 0 && d.H / 2048 <= 3;
+    const bool dn_reg_ok = !d.force_smem_variant && d.I % 2048 == 0 && d.I / 2048 <= 3 && (!shared || d.Is == d.I);
+    const bool pdl = gu_reg && dn_reg_ok;   // both register-resident: the down kernel starts under gate/up's tail
+    g.pdl_trigger = pdl ? 1 : 0;
+    g.pdl_wait_all = (pdl && d.fused_route) ? 1 : 0;   // the fused routing kernel is the one that triggers
     if (gu_reg) {
         const int st = launch_reg<true>(g, d.H / 2048, d.sm_count, s);
         if (st) return st;
@@ -971,6 +1000,7 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     w.bsrc = d.hbuf; w.ldb = imax; w.K = d.I; w.Ks = shared ? d.Is : d.I;
     w.units = d.H / 32; w.units_s = d.H / 32;
     w.hbuf = nullptr; w.ybuf = d.ybuf; w.x_which = 1;
+    w.pdl_trigger = pdl ? 1 : 0; w.pdl_wait = pdl ? 1 : 0; w.pdl_wait_all = 0;
     const bool dn_reg = !d.force_smem_variant && d.I % 2048 == 0 && d.I / 2048 <= 3 && w.Ks == w.K;
     if (dn_reg) {
         const int st = launch_reg<false>(w, d.I / 2048, d.sm_count, s);
@@ -987,8 +1017,20 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     if (d.ev_down) cudaEventRecord(d.ev_down, s);
 
     dim3 cgrid((unsigned)(((d.H >> 2) + 255) / 256), (unsigned)d.n);
-    combine_kernel<<<cgrid, 256, 0, s>>>(d.ybuf, d.slot_pos, d.topk_w, d.n, d.topk, d.H, P,
-                                         shared ? 1 : 0, d.out);
+    if (pdl && dn_reg) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = cgrid; cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = s;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, combine_kernel, (const float*)d.ybuf, (const int*)d.slot_pos,
+                               (const float*)d.topk_w, d.n, d.topk, d.H, P, shared ? 1 : 0, d.out, 1) != cudaSuccess)
+            return GSB_ERR_LAUNCH;
+    } else {
+        combine_kernel<<<cgrid, 256, 0, s>>>(d.ybuf, d.slot_pos, d.topk_w, d.n, d.topk, d.H, P,
+                                             shared ? 1 : 0, d.out, 0);
+    }
     return launch_status();
 }
 
