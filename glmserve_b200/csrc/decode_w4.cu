@@ -117,28 +117,6 @@ struct SegRun {
     int seg, ubeg, uend, expert, slot_begin, ntok;
     const uint8_t* chunks;  // first chunk of unit ubeg
 };
-__device__ __forceinline__ bool next_run(const DecodeKArgs& a, long long& it, long long it1, int nshared,
-                                         int nchunk_routed, int nchunk_shared, SegRun& r) {
-    if (it >= it1) return false;
-    const long long shared_items = (long long)nshared * a.units_s;
-    const bool sh = it < shared_items;
-    const int U = sh ? a.units_s : a.units;
-    const long long l = sh ? it : it - shared_items;
-    const int sg = (int)(l / U);
-    r.ubeg = (int)(l - (long long)sg * U);
-    r.seg = sg + (sh ? 0 : nshared);
-    const long long left = it1 - it;
-    r.uend = (int)((long long)(U - r.ubeg) < left ? U : r.ubeg + left);
-    const int4 rec = reinterpret_cast<const int4*>(a.segs + kSegHeader)[r.seg];
-    r.expert = rec.x; r.slot_begin = rec.y; r.ntok = rec.z;
-    const int nchunk = sh ? nchunk_shared : nchunk_routed;
-    const uint8_t* base = sh ? a.shared_packed : a.packed;
-    const long long e_local = sh ? 0 : rec.x;
-    r.chunks = base + ((e_local * U + r.ubeg) * (long long)nchunk) * kChunkBytes;
-    it += r.uend - r.ubeg;
-    return true;
-}
-
 // ---- expert list (register-resident variant) ----------------------------------------------
 // One entry per expert that has tokens (the shared expert first, then the routed experts in order):
 //   xsegs[0] = entries, [1] / [2] = total items of the gate/up / down kernel, [3] = grid size,
