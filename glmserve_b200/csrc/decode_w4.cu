@@ -792,6 +792,7 @@ route_fused_kernel(const RouteFusedArgs a) {
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    asm volatile("griddepcontrol.wait;" ::: "memory");                // launched under the logits kernel's tail
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // gate/up may be scheduled; it waits for this grid
     if (rank == 0 && threadIdx.x < 4) a.status[threadIdx.x] = 0;
     // top-k: a warp per token over the whole cluster (one block alone spends 15 us on 64 tokens)
@@ -936,7 +937,13 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
         r.units_gu = d.I / 16; r.units_gu_s = shared ? d.Is / 16 : 1; r.units_dn = d.H / 32; r.grid = d.sm_count;
         r.status = d.status;
         const size_t smem = (size_t)(kDispWarps * d.E + 1024) * sizeof(int);   // 36 KiB at 256 experts
-        route_fused_kernel<<<kRouteCluster, 1024, smem, s>>>(r);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(kRouteCluster); cfg.blockDim = dim3(1024); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the logits kernel triggers at its start
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, route_fused_kernel, r) != cudaSuccess) return GSB_ERR_LAUNCH;
     } else {
         if (cudaMemsetAsync(d.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
         seg_build_kernel<<<1, 1024, 0, s>>>(d.expert_offsets, d.E, d.n, P, shared ? 1 : 0, d.segs, xsegs, d.I / 16,

@@ -142,6 +142,9 @@ router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
                          int n, int H, int E, float* __restrict__ logits, float* __restrict__ scores,
                          __half* __restrict__ xp) {
     extern __shared__ float red[];   // KSPLIT > 1: [8 warps][MT][NT][4][32] partial tiles
+    // the routing kernel that follows may be scheduled now; it waits for this grid before it reads
+    // (a no-op unless that launch asks for programmatic serialization)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (xp && (int)blockIdx.x * (16 * MT) >= E) {
         // one column of blocks beyond the experts: this block's token rows as fp16 in the decode
         // kernels' fragment order (saves a launch; the logits blocks read the same rows anyway)
