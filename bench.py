@@ -454,7 +454,7 @@ def run_ours(args) -> None:
                                                      min(T, args.cpu_tokens))
         # DRAM bytes per launch of the dominant kernel from the ncu launch lists summarised under
         # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum at these exact workloads)
-        measured_traffic = {("decode", 64, 256): 3032.5e6 + 5.0e6, ("prefill", 8192, 256): 4244.3e6 + 285.4e6}
+        measured_traffic = {("decode", 64, 256): 3031.7e6 + 5.3e6, ("prefill", 8192, 256): 4270.5e6 + 285.4e6}
         line["roofline"]["traffic"] = measured_traffic.get((shape, T, GLM["E"]))
         print(json.dumps(line))
     if world > 1:
