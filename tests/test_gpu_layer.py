@@ -224,6 +224,30 @@ def test_glm_scale_prefill(dev, glm_layer):
     assert_layer_close(out.cpu().numpy(), r["out"], "glm prefill n=512")
 
 
+def test_glm_scale_prefill_full_size_token_sample(dev, glm_layer):
+    """The benchmark's own prefill size (8192 tokens, 65536 routed slots, many-block dispatch,
+    several token tiles per expert) against the oracle on a sample of its tokens: tokens are
+    independent, so the oracle run on 12 of them alone gives their true rows.  Plus the run-twice
+    bit identity of the whole output."""
+    from glmserve_b200 import ops
+    layer, Lnp = glm_layer
+    n = 8192
+    x = make_x_torch(n, 6144, seed=808, device=dev)
+    out, logits, ids, w = layer.forward(x, path=ops.PATH_PREFILL, return_routing=True)
+    out = out.clone()
+    assert layer.status() == 0
+    pick = np.array([0, 1, 63, 64, 255, 256, 1000, 4095, 4096, 6000, 8190, 8191])
+    x_np = x[torch.from_numpy(pick).to(dev)].float().cpu().numpy()
+    r = oracle.moe_layer_w4(x_np, Lnp, logits_in=logits[torch.from_numpy(pick).to(dev)].cpu().numpy())
+    assert np.array_equal(ids.cpu().numpy()[pick], r["ids"])
+    assert_layer_close(out.cpu().numpy()[pick], r["out"], "glm prefill n=8192, sampled tokens")
+    again = layer.forward(x, path=ops.PATH_PREFILL)
+    assert torch.equal(again, out)
+    # every expert segment is complete: the permutation covers each routed slot exactly once
+    ids_np = ids.cpu().numpy()
+    assert np.bincount(ids_np.ravel(), minlength=256).sum() == n * 8
+
+
 def test_block_of_layers_with_prenorm_and_residual(dev):
     """Two chained layers h <- h + moe(rmsnorm(h)) (the speculative-verify block's shape,
     scaled down)."""
