@@ -1,6 +1,6 @@
 """Regenerates the golden fixtures in this folder from the reference itself.
 
-Run in a container that holds the reference tree (REF_ROOT, default /root/reference):
+Run in a container that holds the reference tree (environment variable REF_ROOT points at it):
     python tests/golden/make_golden.py
 It builds oracle/_ref/libglmref.so (the reference's own CPU float32 MoE, compiled from the
 reference sources in place) and imports the reference's numpy twin

@@ -1,6 +1,6 @@
 """Regenerates tests/golden/tiny_w4_ckpt/ from the reference's own tools.
 
-Run in a container that holds the reference tree (REF_ROOT, default /root/reference):
+Run in a container that holds the reference tree (environment variable REF_ROOT points at it):
     python tests/golden/make_w4_checkpoint_fixture.py
 It runs tools/make_tiny_checkpoint.py (fp32 checkpoint, seed 1234) and
 tools/convert_hf_to_glmserve.py --quantize-int4 --group 16 (the W4 checkpoint) into a temporary
