@@ -48,3 +48,32 @@ def test_shim_header_names_match_reference_surface():
                  "gemm_q", "gemm_q_i8", "quantize_act_q8", "qtype_has_i8", "moe_expert_ffn_q",
                  "moe_expert_ffn_q_i8"):
         assert re.search(r"inline\s+\w+\s+%s\s*\(" % name, text), name
+
+
+def test_shim_compiles_and_links_against_the_library(tmp_path):
+    """A translation unit written the way src/model_gpu.cpp calls the operators (namespace
+    glmserve::cuda, default stream argument) compiles against the shim and links with the
+    library - no GPU needed, nothing is run."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc not found")
+    src = tmp_path / "caller.cu"
+    src.write_text(
+        '#include <cuda_runtime.h>\n'
+        '#include "glmserve_b200.h"\n'
+        '#include "glmserve_cuda_shim.cuh"\n'
+        'int main() {\n'
+        '    float* f = nullptr; int* i = nullptr; unsigned char* q = nullptr;\n'
+        '    glmserve::cuda::moe_router(f, f, 0, 8, 2, true, 2.5f, i, f);\n'
+        '    glmserve::cuda::moe_dispatch(i, 0, 2, 8, i, i, i);\n'
+        '    glmserve::cuda::moe_expert_ffn_w4a16(f, i, f, q, f, q, f, q, f, 0, 2, 64, 64, 8, 32, f);\n'
+        '    glmserve::cuda::gemm_w4a16(f, q, f, nullptr, f, 0, 64, 64, 32);\n'
+        '    return glmserve::cuda::b200_last_status();\n'
+        '}\n')
+    exe = tmp_path / "caller"
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-I", os.path.join(ROOT, "include"),
+           str(src), "-o", str(exe), "-L", os.path.join(ROOT, "glmserve_b200"), "-lglmserve_b200"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
