@@ -312,7 +312,13 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
         ev = layer->prof_ev + (size_t)(layer->prof_used++) * (GSB_N_STAGES + 1);
     auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], s); };
     mark(0);
-    if (path == GSB_PATH_AUTO) path = layer->tiles_ok ? GSB_PATH_DECODE : GSB_PATH_DIRECT;
+    if (path == GSB_PATH_AUTO) {
+        // the grouped tcgen05 GEMM wins from about 32 rows per routed expert on (measured crossover at
+        // GLM scale: 1024 tokens x top-8 over 256 experts; below it the split-K kernels stream each expert
+        // once per 8 rows and are still ahead)
+        if (!layer->tiles_ok) path = GSB_PATH_DIRECT;
+        else path = (int64_t)n * c.topk >= 32LL * c.n_experts ? GSB_PATH_PREFILL : GSB_PATH_DECODE;
+    }
     if ((path == GSB_PATH_DECODE || path == GSB_PATH_PREFILL || path == GSB_PATH_DECODE_SMEM) && !layer->tiles_ok)
         return GSB_ERR_UNSUPPORTED;
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);

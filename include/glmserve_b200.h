@@ -228,7 +228,9 @@ GSB_API size_t gsb_moe_workspace_bytes(const gsb_moe_layer* layer, int n_tokens)
 /* Path selection for gsb_moe_layer_forward. */
 enum {
     GSB_PATH_AUTO = 0,    /* by shape: direct-layout kernels for shapes the tile kernels do
-                             not cover, else decode-shaped or prefill-shaped tile kernels */
+                             not cover; else the split-K kernels below an average of 32 rows per
+                             routed expert (n * topk < 32 * n_experts) and the tcgen05 grouped
+                             GEMM from there on */
     GSB_PATH_DIRECT = 1,  /* direct-layout SIMT kernels (any shape) */
     GSB_PATH_DECODE = 2,  /* bandwidth-bound split-K tile-stream kernels */
     GSB_PATH_PREFILL = 3, /* tcgen05 grouped GEMM */

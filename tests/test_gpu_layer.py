@@ -119,6 +119,17 @@ def test_wide_config_repeated_forwards_with_weights_in_l2(dev, n, reps):
     assert int(differing) == 0, f"{int(differing)} of {reps} forwards differ from the first"
 
 
+@pytest.mark.parametrize("n", [16, 127, 128, 640])
+def test_mid_config_automatic_path(dev, n):
+    """PATH_AUTO: the split-K kernels below about 32 rows per expert (n * top-k < 32 * E, here
+    n < 128), the tcgen05 grouped GEMM from there on; either way the oracle's result."""
+    from glmserve_b200 import ops
+    L = make_layer_np(CONFIGS["mid"], seed=5)
+    layer = ops.MoELayer(layer_to_torch(L, dev))
+    x = make_x_np(n, L["H"], seed=90 + n)
+    _check_layer(layer, L, x, dev, ops.PATH_AUTO, f"mid auto n={n}")
+
+
 def test_mid_config_without_shared_expert_and_skew(dev):
     from glmserve_b200 import ops
     L = make_layer_np(CONFIGS["mid"], seed=22, shared=False, zipf_amplitude=0.1)
