@@ -98,23 +98,25 @@ def test_wide_config_register_resident_decode(dev, n):
     assert torch.equal(layer.forward(bf16_tensor(x, dev), path=ops.PATH_DECODE), a["out"])
 
 
-@pytest.mark.parametrize("n,reps", [(200, 300), (500, 400)])
-def test_wide_config_repeated_forwards_with_weights_in_l2(dev, n, reps):
+@pytest.mark.parametrize("n,reps,path_name", [(200, 300, "PATH_DECODE"), (500, 400, "PATH_DECODE"),
+                                              (300, 300, "PATH_PREFILL")])
+def test_wide_config_repeated_forwards_with_weights_in_l2(dev, n, reps, path_name):
     """A layer small enough to stay in L2 makes the weight ring turn over as fast as the
     consumers can release it; a stage released before every load from it is ordered ahead of
     the refill (the refill writes through the async proxy) showed up as wrong sums in up to 40%
     of these forwards.  No atomics, fixed summation order: every forward returns the same bits
     as the first one, which is checked against the oracle."""
     from glmserve_b200 import ops
+    path = getattr(ops, path_name)
     cfg = CONFIGS["wide"]
     L = make_layer_np(cfg, seed=11)
     layer = ops.MoELayer(layer_to_torch(L, dev))
     x_np = make_x_np(n, cfg["H"], seed=40 + n)
     x = bf16_tensor(x_np, dev)
-    first = _check_layer(layer, L, x_np, dev, ops.PATH_DECODE, f"wide decode n={n}")["out"].clone()
+    first = _check_layer(layer, L, x_np, dev, path, f"wide {path_name} n={n}")["out"].clone()
     differing = torch.zeros((), dtype=torch.int32, device=dev)
     for _ in range(reps):
-        differing += (layer.forward(x, path=ops.PATH_DECODE) != first).any().int()
+        differing += (layer.forward(x, path=path) != first).any().int()
     assert layer.status() == 0
     assert int(differing) == 0, f"{int(differing)} of {reps} forwards differ from the first"
 
