@@ -29,14 +29,11 @@ struct Workspace {
     int* slot_pos;            // [P]
     int* disp_scratch;        // many-block dispatch: per-block expert counts
     int* segs;                // decode segments: int4 per segment, [kMaxSegHeader + nseg_max]
-    __half* xp;               // [n, H] fp16 activations in fragment order
+    __half* xp;               // [n, H] fp16 activations in token order (decode: fragment order; tcgen05: natural)
     __half* hbuf;             // [P + n, Imax] fp16 SwiGLU output in fragment order
     float* ybuf;              // [P + n, H] per-slot down-projection rows
     __half* xs;               // prefill: [P + n, H] fp16 activations in expert order
-    int* tiles_gu;            // prefill tile lists
-    int* tiles_dn;
-    __nv_bfloat16* xnorm;     // [n, H] bf16 (block layer: rmsnorm output)
-    float* mlp;               // [n, H] (block layer: layer output before the residual add)
+    int* tiles;               // prefill token-tile list
     size_t total;
 };
 
@@ -65,10 +62,7 @@ Workspace carve(const gsb_moe_config& c, int n, void* base) {
     ws.hbuf = reinterpret_cast<__half*>(take((P + n) * imax * sizeof(__half)));
     ws.ybuf = reinterpret_cast<float*>(take((P + n) * (size_t)c.hidden * sizeof(float)));
     ws.xs = reinterpret_cast<__half*>(take((P + n) * (size_t)c.hidden * sizeof(__half)));
-    ws.tiles_gu = reinterpret_cast<int*>(take(prefill_tile_bytes(n, c.topk, c.n_experts, c.hidden, (int)imax)));
-    ws.tiles_dn = reinterpret_cast<int*>(take(prefill_tile_bytes(n, c.topk, c.n_experts, c.hidden, (int)imax)));
-    ws.xnorm = reinterpret_cast<__nv_bfloat16*>(take((size_t)n * c.hidden * sizeof(__nv_bfloat16)));
-    ws.mlp = reinterpret_cast<float*>(take((size_t)n * c.hidden * sizeof(float)));
+    ws.tiles = reinterpret_cast<int*>(take(prefill_tile_bytes(n, c.topk, c.n_experts)));
     ws.total = off;
     return ws;
 }
@@ -295,18 +289,18 @@ int gsb_router_logits(const void* x_bf16, const void* router_w_bf16, int n, int 
                                 logits, nullptr, as_stream(stream));
 }
 
-int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float* out,
-                          void* workspace, size_t workspace_bytes, int path, float* logits_out,
-                          int* ids_out, float* weights_out, void* stream) {
-    if (!layer || n < 0) return GSB_ERR_INVALID_ARG;
-    if (layer->cfg.ep_size > 1) return GSB_ERR_UNSUPPORTED;  // expert-parallel layers: gsb_moe_layer_forward_ep
-    if (n == 0) return GSB_OK;
-    if (!x_bf16 || !out || !workspace || !aligned(workspace, 256) || !aligned(x_bf16, 16))
-        return GSB_ERR_INVALID_ARG;
+}  // extern "C"
+
+namespace {
+
+// The layer on x (bf16 rows) or, when `hidden` is given, on bf16(rmsnorm(hidden, norm_w, eps)) with the
+// norm folded into the router-logits launch; `residual` (nullable) is added in the combine pass.
+int forward_impl(gsb_moe_layer* layer, const __nv_bfloat16* x, const float* hidden, const float* norm_w, float eps,
+                 int n, float* out, const float* residual, void* workspace, size_t workspace_bytes, int path,
+                 float* logits_out, int* ids_out, float* weights_out, cudaStream_t s) {
     const gsb_moe_config& c = layer->cfg;
     Workspace ws = carve(c, n, workspace);
     if (workspace_bytes < ws.total) return GSB_ERR_WORKSPACE;
-    cudaStream_t s = as_stream(stream);
     cudaEvent_t* ev = nullptr;
     if (layer->prof_ev && layer->prof_used < layer->prof_sets)
         ev = layer->prof_ev + (size_t)(layer->prof_used++) * (GSB_N_STAGES + 1);
@@ -319,47 +313,40 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
         if (!layer->tiles_ok) path = GSB_PATH_DIRECT;
         else path = (int64_t)n * c.topk >= 32LL * c.n_experts ? GSB_PATH_PREFILL : GSB_PATH_DECODE;
     }
-    if ((path == GSB_PATH_DECODE || path == GSB_PATH_PREFILL || path == GSB_PATH_DECODE_SMEM) && !layer->tiles_ok)
-        return GSB_ERR_UNSUPPORTED;
-    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
-
-    int st;
-    // decode-sized batches on the tile-stream decode path: the logits launch also converts the
-    // activations, and one block does top-k + dispatch + work lists (inside launch_decode_layer)
     const bool decode_path = path == GSB_PATH_DECODE || path == GSB_PATH_DECODE_SMEM;
-    const bool fused = decode_path && !c.fixed_routing && c.hidden % 256 == 0 &&
-                       decode_route_fusable(n, c.topk, c.n_experts);
+    if ((decode_path || path == GSB_PATH_PREFILL) && !layer->tiles_ok) return GSB_ERR_UNSUPPORTED;
+    if (path != GSB_PATH_DIRECT && !decode_path && path != GSB_PATH_PREFILL) return GSB_ERR_INVALID_ARG;
+
+    int st = GSB_OK;
+    // the logits launch can leave the activations behind as fp16 rows for the expert GEMMs (an extra
+    // column of blocks): fragment order for the decode kernels, natural order for the tcgen05 path
+    const bool can_fuse_x = !c.fixed_routing && c.hidden % 256 == 0;
+    const bool x_fused = can_fuse_x && path != GSB_PATH_DIRECT;
+    // decode-sized batches: one cluster does top-k + dispatch + work lists (inside launch_decode_layer)
+    const bool fused_route = decode_path && x_fused && decode_route_fusable(n, c.topk, c.n_experts);
+    if (hidden && !x_fused) {
+        // shapes or paths whose logits launch cannot take the norm: a separate pass into the (otherwise
+        // unused here) expert-order buffer, then the plain bf16 path
+        __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(ws.xs);
+        st = launch_rmsnorm_bf16(hidden, norm_w, xn, n, c.hidden, eps, s);
+        if (st) return st;
+        x = xn; hidden = nullptr;
+    }
     if (c.fixed_routing) {
         if (logits_out) return GSB_ERR_INVALID_ARG;   // there are no logits
         st = launch_fixed_routing(n, c.topk, ws.ids, ws.w, s);
     } else {
         st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden,
-                                  c.n_experts, ws.logits, ws.scores, s, fused ? ws.xp : nullptr);
+                                  c.n_experts, ws.logits, ws.scores, s, x_fused ? ws.xp : nullptr,
+                                  path == GSB_PATH_PREFILL ? 1 : 0, hidden, norm_w, eps);
         if (st) return st;
-        if (!fused)
+        if (!fused_route)
             st = launch_router_topk(ws.scores, c.e_bias, n, c.n_experts, c.topk, c.norm_topk,
                                     c.routed_scale, ws.ids, ws.w, s, true);
     }
     if (st) return st;
     mark(1);
-    if (fused) {
-        DecodeArgs d{};
-        d.force_smem_variant = path == GSB_PATH_DECODE_SMEM ? 1 : 0;
-        d.x = x; d.n = n; d.topk = c.topk; d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter;
-        d.E = c.n_experts;
-        d.gate_up_packed = c.gate_up_packed; d.down_packed = c.down_packed;
-        d.shared_gate_up_packed = c.shared_gate_up_packed; d.shared_down_packed = c.shared_down_packed;
-        d.expert_offsets = ws.expert_offsets; d.sorted_tok = ws.sorted_tok; d.slot_pos = ws.slot_pos;
-        d.topk_w = ws.w; d.segs = ws.segs; d.xp = ws.xp; d.hbuf = ws.hbuf; d.ybuf = ws.ybuf;
-        d.status = ws.status; d.out = out; d.sm_count = layer->sm_count;
-        d.fused_route = 1; d.xp_ready = 1;
-        d.scores = ws.scores; d.e_bias = c.e_bias; d.norm_topk = c.norm_topk; d.routed_scale = c.routed_scale;
-        d.ids = ws.ids; d.w_out = ws.w; d.sorted_row = ws.sorted_row;
-        if (ev) { d.ev_prep = ev[2]; d.ev_gate_up = ev[3]; d.ev_down = ev[4]; }
-        st = launch_decode_layer(d, s);
-        mark(5);
-        if (st) return st;
-        // routing outputs exist only after the fused block has run
+    auto copy_routing = [&]() -> int {
         if (logits_out && cudaMemcpyAsync(logits_out, ws.logits, (size_t)n * c.n_experts * sizeof(float),
                                           cudaMemcpyDeviceToDevice, s) != cudaSuccess)
             return GSB_ERR_CUDA;
@@ -370,20 +357,13 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
                                            cudaMemcpyDeviceToDevice, s) != cudaSuccess)
             return GSB_ERR_CUDA;
         return GSB_OK;
-    }
-    if (logits_out && cudaMemcpyAsync(logits_out, ws.logits, (size_t)n * c.n_experts * sizeof(float),
-                                      cudaMemcpyDeviceToDevice, s) != cudaSuccess)
-        return GSB_ERR_CUDA;
-    if (ids_out && cudaMemcpyAsync(ids_out, ws.ids, (size_t)n * c.topk * sizeof(int),
-                                   cudaMemcpyDeviceToDevice, s) != cudaSuccess)
-        return GSB_ERR_CUDA;
-    if (weights_out && cudaMemcpyAsync(weights_out, ws.w, (size_t)n * c.topk * sizeof(float),
-                                       cudaMemcpyDeviceToDevice, s) != cudaSuccess)
-        return GSB_ERR_CUDA;
+    };
+    if (!fused_route) { st = copy_routing(); if (st) return st; }
 
     if (path == GSB_PATH_DIRECT) {
         if (!(c.gate_q && c.gate_sc && c.up_q && c.up_sc && c.down_q && c.down_sc))
             return GSB_ERR_UNSUPPORTED;
+        if (cudaMemsetAsync(ws.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
         GenericExpertArgs a{};
         a.x = x; a.ids = ws.ids; a.w = ws.w;
         a.gate = c.gate_q; a.gate_sc = c.gate_sc; a.up = c.up_q; a.up_sc = c.up_sc;
@@ -394,17 +374,19 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
             a.sd = c.sd_q; a.sd_sc = c.sd_sc;
         }
         a.n = n; a.topk = c.topk; a.H = c.hidden; a.I = c.moe_inter; a.Is = c.shared_inter;
-        a.E = c.n_experts; a.group = c.group; a.out = out;
+        a.E = c.n_experts; a.group = c.group; a.out = out; a.residual = residual;
         mark(2);
         st = launch_generic_expert(a, 1, 1, true, s);
         mark(3); mark(4); mark(5);
         return st;
     }
 
-    st = launch_dispatch(ws.ids, n, c.topk, c.n_experts, ws.expert_offsets, ws.sorted_tok,
-                         ws.sorted_row, ws.slot_pos, s, ws.disp_scratch);
-    if (st) return st;
-    if (path == GSB_PATH_DECODE || path == GSB_PATH_DECODE_SMEM) {
+    if (!fused_route) {
+        st = launch_dispatch(ws.ids, n, c.topk, c.n_experts, ws.expert_offsets, ws.sorted_tok,
+                             ws.sorted_row, ws.slot_pos, s, ws.disp_scratch);
+        if (st) return st;
+    }
+    if (decode_path) {
         DecodeArgs d{};
         d.force_smem_variant = path == GSB_PATH_DECODE_SMEM ? 1 : 0;
         d.x = x; d.n = n; d.topk = c.topk; d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter;
@@ -413,46 +395,64 @@ int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float
         d.shared_gate_up_packed = c.shared_gate_up_packed; d.shared_down_packed = c.shared_down_packed;
         d.expert_offsets = ws.expert_offsets; d.sorted_tok = ws.sorted_tok; d.slot_pos = ws.slot_pos;
         d.topk_w = ws.w; d.segs = ws.segs; d.xp = ws.xp; d.hbuf = ws.hbuf; d.ybuf = ws.ybuf;
-        d.status = ws.status; d.out = out; d.sm_count = layer->sm_count;
+        d.status = ws.status; d.out = out; d.residual = residual; d.sm_count = layer->sm_count;
+        d.xp_ready = x_fused ? 1 : 0;
+        if (fused_route) {
+            d.fused_route = 1;
+            d.scores = ws.scores; d.e_bias = c.e_bias; d.norm_topk = c.norm_topk; d.routed_scale = c.routed_scale;
+            d.ids = ws.ids; d.w_out = ws.w; d.sorted_row = ws.sorted_row;
+        }
         if (ev) { d.ev_prep = ev[2]; d.ev_gate_up = ev[3]; d.ev_down = ev[4]; }
         st = launch_decode_layer(d, s);
         mark(5);
-        return st;
+        if (st) return st;
+        // with fused routing the routing outputs exist only after that cluster has run
+        return fused_route ? copy_routing() : GSB_OK;
     }
-    if (path == GSB_PATH_PREFILL) {
-        PrefillArgs d{};
-        d.x = x; d.n = n; d.topk = c.topk; d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter;
-        d.E = c.n_experts;
-        d.gate_up_packed = c.gate_up_packed; d.down_packed = c.down_packed;
-        d.shared_gate_up_packed = c.shared_gate_up_packed; d.shared_down_packed = c.shared_down_packed;
-        d.expert_offsets = ws.expert_offsets; d.sorted_tok = ws.sorted_tok; d.slot_pos = ws.slot_pos;
-        d.topk_w = ws.w; d.tiles_gu = ws.tiles_gu; d.tiles_dn = ws.tiles_dn; d.xs = ws.xs;
-        d.hbuf = ws.hbuf; d.ybuf = reinterpret_cast<__half*>(ws.ybuf);
-        d.status = ws.status; d.out = out; d.sm_count = layer->sm_count;
-        if (ev) { d.ev_prep = ev[2]; d.ev_gate_up = ev[3]; d.ev_down = ev[4]; }
-        st = launch_prefill_layer(d, s);
-        mark(5);
-        return st;
-    }
-    return GSB_ERR_UNSUPPORTED;
+    PrefillArgs d{};
+    d.x = x; d.n = n; d.topk = c.topk; d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter;
+    d.E = c.n_experts;
+    d.gate_up_packed = c.gate_up_packed; d.down_packed = c.down_packed;
+    d.shared_gate_up_packed = c.shared_gate_up_packed; d.shared_down_packed = c.shared_down_packed;
+    d.expert_offsets = ws.expert_offsets; d.sorted_tok = ws.sorted_tok; d.slot_pos = ws.slot_pos;
+    d.topk_w = ws.w; d.tiles = ws.tiles; d.xh = ws.xp; d.xh_ready = x_fused ? 1 : 0; d.xs = ws.xs;
+    d.hbuf = ws.hbuf; d.ybuf = reinterpret_cast<__half*>(ws.ybuf);
+    d.status = ws.status; d.out = out; d.residual = residual; d.sm_count = layer->sm_count;
+    if (ev) { d.ev_prep = ev[2]; d.ev_gate_up = ev[3]; d.ev_down = ev[4]; }
+    st = launch_prefill_layer(d, s);
+    mark(5);
+    return st;
+}
+
+}  // namespace
+
+extern "C" {
+
+int gsb_moe_layer_forward(gsb_moe_layer* layer, const void* x_bf16, int n, float* out,
+                          void* workspace, size_t workspace_bytes, int path, float* logits_out,
+                          int* ids_out, float* weights_out, void* stream) {
+    if (!layer || n < 0) return GSB_ERR_INVALID_ARG;
+    if (layer->cfg.ep_size > 1) return GSB_ERR_UNSUPPORTED;  // expert-parallel layers: gsb_moe_layer_forward_ep
+    if (n == 0) return GSB_OK;
+    if (!x_bf16 || !out || !workspace || !aligned(workspace, 256) || !aligned(x_bf16, 16))
+        return GSB_ERR_INVALID_ARG;
+    return forward_impl(layer, reinterpret_cast<const __nv_bfloat16*>(x_bf16), nullptr, nullptr, 0.f, n, out, nullptr,
+                        workspace, workspace_bytes, path, logits_out, ids_out, weights_out, as_stream(stream));
 }
 
 int gsb_moe_block_layer_forward(gsb_moe_layer* layer, float* hidden, const float* norm_w, float eps,
                                 int n, void* workspace, size_t workspace_bytes, int path,
                                 int* ids_out, void* stream) {
     if (!layer || n < 0) return GSB_ERR_INVALID_ARG;
+    if (layer->cfg.ep_size > 1) return GSB_ERR_UNSUPPORTED;
     if (n == 0) return GSB_OK;
-    if (!hidden || !norm_w || !workspace || !aligned(workspace, 256)) return GSB_ERR_INVALID_ARG;
-    const gsb_moe_config& c = layer->cfg;
-    Workspace ws = carve(c, n, workspace);
-    if (workspace_bytes < ws.total) return GSB_ERR_WORKSPACE;
-    cudaStream_t s = as_stream(stream);
-    int st = launch_rmsnorm_bf16(hidden, norm_w, ws.xnorm, n, c.hidden, eps, s);
-    if (st) return st;
-    st = gsb_moe_layer_forward(layer, ws.xnorm, n, ws.mlp, workspace, workspace_bytes, path, nullptr,
-                               ids_out, nullptr, stream);
-    if (st) return st;
-    return launch_add_inplace(hidden, ws.mlp, (int64_t)n * c.hidden, s);
+    if (!hidden || !norm_w || !workspace || !aligned(workspace, 256) || !aligned(hidden, 16) || !aligned(norm_w, 16))
+        return GSB_ERR_INVALID_ARG;
+    // the norm rides the router-logits launch and the residual add rides the combine: the block costs the
+    // layer's own launches, and neither the normalised activations nor the layer output make a round trip
+    // of their own through memory
+    return forward_impl(layer, nullptr, hidden, norm_w, eps, n, hidden, hidden, workspace, workspace_bytes, path,
+                        nullptr, ids_out, nullptr, as_stream(stream));
 }
 
 int gsb_moe_layer_profile_enable(gsb_moe_layer* layer, int max_forwards) {
@@ -498,7 +498,7 @@ int gsb_moe_layer_status(gsb_moe_layer* layer, void* workspace) {
         return GSB_ERR_CUDA;
     if (host[0] != 0) {
         cudaMemset(workspace, 0, 64 * sizeof(int));
-        return GSB_ERR_TIMEOUT;
+        return (host[0] > 0 && host[0] <= GSB_ERR_TOO_LARGE) ? host[0] : GSB_ERR_CUDA;
     }
     return GSB_OK;
 }

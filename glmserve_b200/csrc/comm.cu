@@ -3,15 +3,19 @@
 //
 // Replaces, for the MoE path, the reference's one-shot CUDA-IPC all-reduce
 // (cuda/custom_ar.cu:49-93, cuda/custom_ar.h:26-43) and supplies what the reference does not
-// have: the expert-parallel token exchange.  Differences from the reference's kernel: data is
-// PULLED from the peers' staging areas (one staging copy per rank instead of world slots),
-// large messages take a two-shot reduce-scatter + all-gather, flags use release/acquire at
-// system scope, and every wait is bounded (about a second of SM clocks) and reports
-// GSB_ERR_TIMEOUT through a status word instead of spinning forever
+// have: the expert-parallel token exchange.  Like the reference's kernel the all-reduce PUSHES:
+// a rank stores its data straight into a slot of its own on every peer, then a flag, and each
+// rank sums slots that sit in its own memory - one NVLink traversal on the critical path.
+// Unlike it, flags are per thread block (block b of a rank waits only for block b of its
+// peers, which wrote the same element range: no grid-wide arrival counter), large messages take
+// a two-shot reduce-scatter + all-gather (also pushed), flags use release/acquire at system
+// scope, and every wait is bounded (gsb_comm_set_wait_cycles, about two seconds of SM clocks by
+// default) and reports GSB_ERR_TIMEOUT through a status word instead of spinning forever
 // (cuda/custom_ar.cu:77-79 spins without limit).
 // Sums are taken in rank order 0..world-1 for every element, independent of the message
-// size or grid, so a row reduces to the same bits whether it travels alone or in a batch
-// (the property the reference's all_reduce_sum_rows exists for, include/nccl_comm.hpp:53-59).
+// size, the algorithm or the grid, so a row reduces to the same bits whether it travels alone or
+// in a batch (the property the reference's all_reduce_sum_rows exists for,
+// include/nccl_comm.hpp:53-59).
 #include <new>
 
 #include "internal.cuh"
@@ -27,11 +31,11 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
     return v;
 }
 // Bounded wait until *p >= seq (sequence numbers only grow).  Returns false on timeout.
-__device__ __forceinline__ bool wait_flag(const int* p, int seq, int* status) {
+__device__ __forceinline__ bool wait_flag(const int* p, int seq, int* status, long long limit) {
     if (ld_acquire_sys(p) - seq >= 0) return true;
     const long long start = clock64();
     while (ld_acquire_sys(p) - seq < 0) {
-        if (clock64() - start > kCommWaitCycles) {
+        if (clock64() - start > limit) {
             atomicCAS(status, 0, GSB_ERR_TIMEOUT);
             return false;
         }
@@ -46,103 +50,140 @@ __global__ void signal_kernel(CommPeers pr, int rank, int world, int ch, int seq
     if (threadIdx.x < world && threadIdx.x != rank)
         st_release_sys(ctrl_of(pr, threadIdx.x) + kFlagBase + ch * kMaxWorld + rank, seq);
 }
-// Waits until every peer posted `seq` on channel ch.
-__global__ void wait_kernel(CommPeers pr, int rank, int world, int ch, int seq) {
+// Waits until every peer posted `seq` on channel ch (a timeout is recorded in the status word; what
+// runs afterwards must be safe on stale data, see ep_plan_kernel).
+__global__ void wait_kernel(CommPeers pr, int rank, int world, int ch, int seq, long long limit) {
     int* ctrl = ctrl_of(pr, rank);
     if (threadIdx.x < world && threadIdx.x != rank)
-        wait_flag(ctrl + kFlagBase + ch * kMaxWorld + threadIdx.x, seq, ctrl + kStatusWord);
+        wait_flag(ctrl + kFlagBase + ch * kMaxWorld + threadIdx.x, seq, ctrl + kStatusWord, limit);
 }
 
 // ---- all-reduce ---------------------------------------------------------------------------
-// Phase 1: copy `data` into the local staging area, then (last block) post the flag.
-// Phase 2: wait for every peer's flag.
-// Phase 3 (one-shot): out[i] = sum over ranks in rank order of staging_r[i], read over NVLink.
-// Two-shot: phase 3 reduces only this rank's slice into a second staging area, posts a second
-// flag, and phase 4 gathers every owner's reduced slice.
-// Element i of every rank's staging, added in rank order.  The loads of up to eight ranks are issued
-// before the first add: a loop that adds as it loads waits one NVLink round trip per rank.
-__device__ __forceinline__ float4 sum_over_ranks(const CommPeers& pr, int world, size_t stage_off, int64_t i) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int r0 = 0; r0 < world; r0 += 8) {
-        float4 v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (r0 + j < world) v[j] = reinterpret_cast<const float4*>(pr.base[r0 + j] + stage_off)[i];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (r0 + j < world) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
-    }
-    return acc;
+// Staging of one parity: two areas of `area` floats.
+//   one-shot  slot[src] = area 0 + src * count floats (both areas together; needs world * count <= 2 * area).
+//             Block b owns elements [b * chunk, (b + 1) * chunk): it stores them into its slot on every peer,
+//             posts flag(0, rank, b) to every peer, waits for flag(0, s, b) of every peer s, then sums the
+//             slots (its own contribution straight from `data`) in rank order into `data`.
+//   two-shot  rank j owns slice j of `per` elements.  Area 0 holds world scatter slots of `per` elements,
+//             area 1 the gathered result.  Block b takes sub-range b of EVERY slice: it pushes its part of
+//             slice j to rank j, flags, waits, sums its part of the own slice in rank order, pushes the sums
+//             to every peer's gather area, flags (phase 1), waits, and copies the other slices' sums home.
+// Every rank launches the same grid for the same count, so "block b" means the same elements everywhere.
+struct ArArgs {
+    CommPeers pr;
+    int rank, world;
+    float* data;
+    int64_t count4;          // float4 elements
+    size_t stage_off;        // byte offset (from the heap base pointer) of this parity's staging
+    size_t area_bytes;       // bytes of one area
+    int seq;
+    int two_shot;
+    long long wait_cycles;
+};
+
+__device__ __forceinline__ int* blk_flag(const CommPeers& pr, int owner, int phase, int src) {
+    return ctrl_of(pr, owner) + kBlkFlagBase + (phase * kMaxWorld + src) * kMaxArBlocks + (int)blockIdx.x;
 }
 
-__global__ void __launch_bounds__(512)
-allreduce_kernel(CommPeers pr, int rank, int world, float* __restrict__ data, int64_t count4,
-                 size_t stage_off, size_t stage2_off, int seq, int two_shot) {
-    int* ctrl = ctrl_of(pr, rank);
-    __shared__ int last_block, ok;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    const int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    float4* stage = reinterpret_cast<float4*>(pr.base[rank] + stage_off);
-    const float4* src = reinterpret_cast<const float4*>(data);
-    for (int64_t i = i0; i < count4; i += stride) stage[i] = src[i];
+// All peers' block-b flags of `phase`: post ours, then wait for theirs.  Returns false on a timeout (all threads).
+__device__ __forceinline__ bool ar_exchange_flags(const ArArgs& a, int phase, int* ok_s) {
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0) {
-        last_block = atomicAdd(ctrl + kArriveCounter, 1) == (int)gridDim.x - 1;
-        ok = 1;
+    if (threadIdx.x == 0) *ok_s = 1;
+    __syncthreads();
+    if (threadIdx.x < a.world && threadIdx.x != a.rank) {
+        st_release_sys(blk_flag(a.pr, threadIdx.x, phase, a.rank), a.seq);
+        if (!wait_flag(blk_flag(a.pr, a.rank, phase, threadIdx.x), a.seq, ctrl_of(a.pr, a.rank) + kStatusWord, a.wait_cycles))
+            *ok_s = 0;
     }
     __syncthreads();
-    if (last_block && threadIdx.x < world) {
-        if (threadIdx.x == 0) ctrl[kArriveCounter] = 0;
-        if (threadIdx.x != rank)
-            st_release_sys(ctrl_of(pr, threadIdx.x) + kFlagBase + kChAllReduce * kMaxWorld + rank, seq);
-    }
-    if (threadIdx.x < world && threadIdx.x != rank)
-        if (!wait_flag(ctrl + kFlagBase + kChAllReduce * kMaxWorld + threadIdx.x, seq, ctrl + kStatusWord)) ok = 0;
-    __syncthreads();
-    if (!ok) return;
-    float4* out = reinterpret_cast<float4*>(data);
-    if (!two_shot) {
-        for (int64_t i = i0; i < count4; i += stride) out[i] = sum_over_ranks(pr, world, stage_off, i);
+    return *ok_s != 0;
+}
+
+__device__ __forceinline__ float4 ld_cg4(const float4* p) { return __ldcg(p); }
+
+__global__ void __launch_bounds__(256)
+allreduce_kernel(const ArArgs a) {
+    __shared__ int ok_s;
+    const int B = (int)gridDim.x, b = (int)blockIdx.x;
+    float4* data = reinterpret_cast<float4*>(a.data);
+    if (!a.two_shot) {
+        const int64_t chunk = (a.count4 + B - 1) / B;
+        const int64_t lo = min(a.count4, chunk * b), hi = min(a.count4, lo + chunk);
+        const size_t slot_bytes = (size_t)a.count4 * sizeof(float4);
+        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            const float4 v = data[i];
+            for (int p = 0; p < a.world; ++p)
+                if (p != a.rank) reinterpret_cast<float4*>(a.pr.base[p] + a.stage_off + a.rank * slot_bytes)[i] = v;
+        }
+        if (!ar_exchange_flags(a, 0, &ok_s)) return;
+        const uint8_t* mine = a.pr.base[a.rank] + a.stage_off;
+        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            float4 v[kMaxWorld];
+#pragma unroll
+            for (int r = 0; r < kMaxWorld; ++r)
+                if (r < a.world) v[r] = r == a.rank ? data[i] : ld_cg4(reinterpret_cast<const float4*>(mine + r * slot_bytes) + i);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int r = 0; r < kMaxWorld; ++r)
+                if (r < a.world) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
+            data[i] = acc;
+        }
         return;
     }
-    // two-shot: this rank owns slice [lo, hi)
-    const int64_t per = (count4 + world - 1) / world;
-    const int64_t lo = min(count4, per * rank), hi = min(count4, lo + per);
-    float4* stage2 = reinterpret_cast<float4*>(pr.base[rank] + stage2_off);
-    for (int64_t i = lo + i0; i < hi; i += stride) {
-        const float4 acc = sum_over_ranks(pr, world, stage_off, i);
-        stage2[i] = acc;
-        out[i] = acc;
+    const int64_t per = (a.count4 + a.world - 1) / a.world;   // slice length
+    const int64_t sub = (per + B - 1) / B;                     // this block's part of a slice
+    const size_t slot_bytes = (size_t)per * sizeof(float4);
+    // scatter: my part of slice j goes to rank j's slot for me
+    for (int j = 0; j < a.world; ++j) {
+        if (j == a.rank) continue;
+        const int64_t slo = min(a.count4, per * j), shi = min(a.count4, slo + per);
+        const int64_t lo = min(shi, slo + sub * b), hi = min(shi, lo + sub);
+        float4* dst = reinterpret_cast<float4*>(a.pr.base[j] + a.stage_off + a.rank * slot_bytes);
+        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) dst[i - slo] = data[i];
     }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) last_block = atomicAdd(ctrl + kArriveCounter + 1, 1) == (int)gridDim.x - 1;
-    __syncthreads();
-    if (last_block && threadIdx.x < world) {
-        if (threadIdx.x == 0) ctrl[kArriveCounter + 1] = 0;
-        if (threadIdx.x != rank)
-            st_release_sys(ctrl_of(pr, threadIdx.x) + kFlagBase + kChAllReduce2 * kMaxWorld + rank, seq);
+    if (!ar_exchange_flags(a, 0, &ok_s)) return;
+    {   // reduce my part of my slice in rank order, write it home and into every peer's gather area
+        const int64_t slo = min(a.count4, per * a.rank), shi = min(a.count4, slo + per);
+        const int64_t lo = min(shi, slo + sub * b), hi = min(shi, lo + sub);
+        const uint8_t* mine = a.pr.base[a.rank] + a.stage_off;
+        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            float4 v[kMaxWorld];
+#pragma unroll
+            for (int r = 0; r < kMaxWorld; ++r)
+                if (r < a.world) v[r] = r == a.rank ? data[i] : ld_cg4(reinterpret_cast<const float4*>(mine + r * slot_bytes) + (i - slo));
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int r = 0; r < kMaxWorld; ++r)
+                if (r < a.world) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
+            data[i] = acc;
+            for (int p = 0; p < a.world; ++p)
+                if (p != a.rank) reinterpret_cast<float4*>(a.pr.base[p] + a.stage_off + a.area_bytes)[i] = acc;
+        }
     }
-    if (threadIdx.x < world && threadIdx.x != rank)
-        if (!wait_flag(ctrl + kFlagBase + kChAllReduce2 * kMaxWorld + threadIdx.x, seq, ctrl + kStatusWord)) ok = 0;
-    __syncthreads();
-    if (!ok) return;
-    for (int r = 0; r < world; ++r) {
-        if (r == rank) continue;
-        const int64_t rlo = min(count4, per * r), rhi = min(count4, rlo + per);
-        const float4* rs = reinterpret_cast<const float4*>(pr.base[r] + stage2_off);
-        for (int64_t i = rlo + i0; i < rhi; i += stride) out[i] = rs[i];
+    if (!ar_exchange_flags(a, 1, &ok_s)) return;
+    const float4* gathered = reinterpret_cast<const float4*>(a.pr.base[a.rank] + a.stage_off + a.area_bytes);
+    for (int j = 0; j < a.world; ++j) {
+        if (j == a.rank) continue;
+        const int64_t slo = min(a.count4, per * j), shi = min(a.count4, slo + per);
+        const int64_t lo = min(shi, slo + sub * b), hi = min(shi, lo + sub);
+        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) data[i] = ld_cg4(gathered + i);
     }
 }
 
 // ---- expert-parallel exchange ---------------------------------------------------------------
-// Counts: rank posts its per-expert row counts (from its local dispatch offsets) to every peer.
+// Counts: rank posts its per-expert row counts (from its local dispatch offsets) and the layout of its
+// own buffers {receive buffer offset, receive capacity, per-slot row buffer offset} to every peer, so a
+// peer never derives an address on this rank from its own arguments.
 __global__ void ep_post_counts_kernel(CommPeers pr, int rank, int world, const int* __restrict__ expert_offsets,
-                                      int E, int seq) {
+                                      int E, int seq, int recv_off_kib, int recv_cap, int ybuf_off_kib) {
     for (int p = 0; p < world; ++p) {
         int* dst = ctrl_of(pr, p) + kCntBase + rank * kMaxExperts;
         for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = expert_offsets[e + 1] - expert_offsets[e];
+        if (threadIdx.x == 0) {
+            int* m = ctrl_of(pr, p) + kMetaBase + rank * 8;
+            m[0] = recv_off_kib; m[1] = recv_cap; m[2] = ybuf_off_kib;
+        }
     }
     __threadfence_system();
     __syncthreads();
@@ -152,23 +193,37 @@ __global__ void ep_post_counts_kernel(CommPeers pr, int rank, int world, const i
 
 // After every rank's counts arrived: the layout of the rows this rank RECEIVES (local expert
 // major, then source rank, then the source's order) and where the rows it SENDS land.
-//   recv_offsets[El + 1]      first received row of each local expert (El = E / world)
+//   recv_offsets[El + 1]      first received row of each local expert (El = E / world), clamped to recv_cap
 //   send_base[E]              row index on the owner's receive buffer of this rank's first row for expert e
-//   ydst[row]                 for each received row: where its output row goes (peer ybuf row pointer)
+//   ydst[row]                 for each received row: where its output row goes (the source's row buffer)
+//   plan[0] = 1 when every peer's counts arrived (0: nothing is pushed and nothing is computed),
+//   plan[1] = rows received, plan[4 + 4r ..] = rank r's posted {receive offset KiB, capacity, row buffer KiB}
+// More rows than recv_cap: GSB_ERR_TOO_LARGE is recorded, the offsets are clamped so that no tile, row of
+// the intermediate buffer or ydst entry lies beyond recv_cap, and the senders drop the rows that do not fit.
 // One block; E <= 1024.
 __global__ void __launch_bounds__(1024)
 ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restrict__ recv_offsets,
-               int* __restrict__ send_base, float** __restrict__ ydst, size_t ybuf_off, int H, int y_elem_bytes,
-               int recv_cap, int* __restrict__ recv_total) {
+               int* __restrict__ send_base, void** __restrict__ ydst, int H, int y_elem_bytes,
+               int recv_cap, int* __restrict__ plan, long long wait_cycles) {
     int* ctrl = ctrl_of(pr, rank);
     __shared__ int tot_s[kMaxExperts];             // rows of expert e over all sources
     __shared__ int base_s[kMaxExperts];            // first receive row of expert e on its owner
     __shared__ int spos_s[kMaxWorld][kMaxExperts]; // position of expert e's rows in source s's sorted order
-    if (threadIdx.x < world && threadIdx.x != rank)
-        wait_flag(ctrl + kFlagBase + kChCounts * kMaxWorld + threadIdx.x, seq, ctrl + kStatusWord);
+    __shared__ int ok_s;
+    if (threadIdx.x == 0) ok_s = 1;
     __syncthreads();
-    const int* cnt = ctrl + kCntBase;              // [src][e]
+    if (threadIdx.x < world && threadIdx.x != rank)
+        if (!wait_flag(ctrl + kFlagBase + kChCounts * kMaxWorld + threadIdx.x, seq, ctrl + kStatusWord, wait_cycles)) ok_s = 0;
+    __syncthreads();
     const int El = E / world;
+    if (!ok_s) {   // a peer never posted: plan nothing (stale counts must not steer any address)
+        for (int e = threadIdx.x; e < E; e += blockDim.x) send_base[e] = 0;
+        for (int e = threadIdx.x; e <= El; e += blockDim.x) recv_offsets[e] = 0;
+        if (threadIdx.x == 0) { plan[0] = 0; plan[1] = 0; }
+        return;
+    }
+    const int* cnt = ctrl + kCntBase;              // [src][e]
+    const int* meta = ctrl + kMetaBase;            // [src][8]
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         int t = 0;
         for (int s = 0; s < world; ++s) t += cnt[s * kMaxExperts + e];
@@ -177,14 +232,17 @@ ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restric
     if (threadIdx.x < world) {                     // one thread per source: running prefix over experts
         int run = 0;
         for (int e = 0; e < E; ++e) { spos_s[threadIdx.x][e] = run; run += cnt[threadIdx.x * kMaxExperts + e]; }
+        plan[4 + 4 * threadIdx.x + 0] = threadIdx.x == rank ? 0 : meta[threadIdx.x * 8 + 0];
+        plan[4 + 4 * threadIdx.x + 1] = threadIdx.x == rank ? recv_cap : meta[threadIdx.x * 8 + 1];
+        plan[4 + 4 * threadIdx.x + 2] = threadIdx.x == rank ? 0 : meta[threadIdx.x * 8 + 2];
     }
     __syncthreads();
     if (threadIdx.x < world) {                     // one thread per owner: running prefix over its experts
         int run = 0;
         for (int e = threadIdx.x * El; e < (threadIdx.x + 1) * El; ++e) { base_s[e] = run; run += tot_s[e]; }
         if (threadIdx.x == rank) {
-            recv_offsets[El] = run;
-            *recv_total = run;
+            recv_offsets[El] = min(run, recv_cap);
+            plan[0] = 1; plan[1] = min(run, recv_cap);
             if (run > recv_cap) atomicCAS(ctrl + kStatusWord, 0, GSB_ERR_TOO_LARGE);
         }
     }
@@ -193,7 +251,7 @@ ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restric
         int before = 0;
         for (int s = 0; s < rank; ++s) before += cnt[s * kMaxExperts + e];
         send_base[e] = base_s[e] + before;
-        if (e / El == rank) recv_offsets[e - rank * El] = base_s[e];
+        if (e / El == rank) recv_offsets[e - rank * El] = min(base_s[e], recv_cap);
     }
     // output destinations of the rows this rank will compute: one warp per (local expert, source)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
@@ -204,41 +262,33 @@ ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restric
         for (int s2 = 0; s2 < sidx; ++s2) row += cnt[s2 * kMaxExperts + e];
         const int c = cnt[sidx * kMaxExperts + e];
         const int src_pos = spos_s[sidx][e];
+        // the source's own row buffer, at the offset the source posted (this rank's own: its argument)
+        const size_t yoff = kCtrlBytes + ((size_t)(sidx == rank ? plan[4 + 4 * rank + 3] : meta[sidx * 8 + 2]) << 10);
         for (int i = lane; i < c; i += 32)
             if (row + i < recv_cap)
-                ydst[row + i] = reinterpret_cast<float*>(pr.base[sidx] + ybuf_off + (size_t)(src_pos + i) * H * y_elem_bytes);
+                ydst[row + i] = pr.base[sidx] + yoff + (size_t)(src_pos + i) * H * y_elem_bytes;
     }
 }
 
 // Dispatch: every local (token, slot) row, in sorted order, is stored as fp16 into the owner's
-// receive buffer over NVLink (16-byte stores); one block per row.
+// receive buffer over NVLink (16-byte stores), at the offset and within the capacity the OWNER
+// posted; one block per row.  frag_order: the decode kernels' fragment order instead of natural order.
 __global__ void __launch_bounds__(256)
-ep_dispatch_push_kernel(CommPeers pr, int world, int E, const __nv_bfloat16* __restrict__ x,
+ep_dispatch_push_kernel(CommPeers pr, int rank, int world, int E, const __nv_bfloat16* __restrict__ x,
                         const int* __restrict__ expert_offsets, const int* __restrict__ sorted_tok,
                         const int* __restrict__ send_base, const int* __restrict__ sorted_expert, int H,
-                        size_t recv_off, int recv_cap) {
+                        const int* __restrict__ plan, size_t own_recv_off, int frag_order) {
+    if (!plan[0]) return;
     const int r = blockIdx.x;
     const int e = sorted_expert[r];
     const int owner = e / (E / world);
     const int dst_row = send_base[e] + (r - expert_offsets[e]);
-    if (dst_row >= recv_cap) return;
+    if (dst_row >= plan[4 + 4 * owner + 1]) return;     // beyond what the owner can receive
+    const size_t recv_off = owner == rank ? own_recv_off : ((size_t)plan[4 + 4 * owner + 0] << 10);
     const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)sorted_tok[r] * H);
-    uint4* dst = reinterpret_cast<uint4*>(pr.base[owner] + recv_off + (size_t)dst_row * H * 2);
-    for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x) {
-        const uint4 in = __ldg(src + v);
-        const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&in);
-        uint4 o;
-        uint32_t* op = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            float2 f = __bfloat1622float2(bp[q]);
-            f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
-            f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
-            const __half2 hh = __floats2half2_rn(f.x, f.y);
-            op[q] = *reinterpret_cast<const uint32_t*>(&hh);
-        }
-        dst[v] = o;
-    }
+    __half* dst = reinterpret_cast<__half*>(pr.base[owner] + kCtrlBytes + recv_off) + (size_t)dst_row * H;
+    for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x)
+        *reinterpret_cast<uint4*>(dst + (frag_order ? frag_pos(v << 3) : (v << 3))) = bf16x8_to_half8(__ldg(src + v));
 }
 
 // expert id of every sorted row (inverse of the offsets), for the push kernel
@@ -252,26 +302,30 @@ int comm_launch_signal(gsb_comm* c, int ch, cudaStream_t s) {
     return launch_status();
 }
 int comm_launch_wait(gsb_comm* c, int ch, cudaStream_t s) {
-    wait_kernel<<<1, 32, 0, s>>>(c->peers, c->rank, c->world, ch, (int)c->seq[ch]);
+    wait_kernel<<<1, 32, 0, s>>>(c->peers, c->rank, c->world, ch, (int)c->seq[ch], c->wait_cycles);
     return launch_status();
 }
 
-// Count exchange, plan, dispatch push and its signal - everything up to (not including) the wait
-// for the peers' rows.  The caller waits on kChDispatch before reading its receive buffer.
-int comm_ep_exchange(gsb_comm* c, const __nv_bfloat16* x, const int* expert_offsets, const int* sorted_tok,
-                     int P, int E, int H, int* sorted_expert, int* recv_offsets, int* send_base, void** ydst,
-                     size_t ybuf_off, int y_elem_bytes, size_t recv_off, int recv_cap, int* recv_total,
-                     cudaStream_t s) {
-    if (E > kMaxExperts || E % c->world) return GSB_ERR_UNSUPPORTED;
-    rows_to_expert_kernel<<<E, 128, 0, s>>>(expert_offsets, E, sorted_expert);
+// Count exchange and plan on s_plan; dispatch push and its signal on s_push (which the caller has made
+// wait for s_plan's work so far; the same stream is fine).  Everything up to (not including) the wait for
+// the peers' rows: the caller waits on kChDispatch before reading its receive buffer.
+int comm_ep_exchange(gsb_comm* c, const EpExchange& e, cudaStream_t s) {
+    if (e.E > kMaxExperts || e.E % c->world) return GSB_ERR_UNSUPPORTED;
+    if ((e.recv_off & 1023) || (e.ybuf_off & 1023) || (e.recv_off >> 10) > 0x7fffffff || (e.ybuf_off >> 10) > 0x7fffffff)
+        return GSB_ERR_INVALID_ARG;
+    rows_to_expert_kernel<<<e.E, 128, 0, s>>>(e.expert_offsets, e.E, e.sorted_expert);
     const int seq_c = (int)++c->seq[kChCounts];
-    ep_post_counts_kernel<<<1, 256, 0, s>>>(c->peers, c->rank, c->world, expert_offsets, E, seq_c);
-    ep_plan_kernel<<<1, 1024, 0, s>>>(c->peers, c->rank, c->world, E, seq_c, recv_offsets, send_base,
-                                      reinterpret_cast<float**>(ydst), kCtrlBytes + ybuf_off, H, y_elem_bytes,
-                                      recv_cap, recv_total);
-    if (P > 0)
-        ep_dispatch_push_kernel<<<P, 256, 0, s>>>(c->peers, c->world, E, x, expert_offsets, sorted_tok, send_base,
-                                                  sorted_expert, H, kCtrlBytes + recv_off, recv_cap);
+    ep_post_counts_kernel<<<1, 256, 0, s>>>(c->peers, c->rank, c->world, e.expert_offsets, e.E, seq_c,
+                                            (int)(e.recv_off >> 10), e.recv_cap, (int)(e.ybuf_off >> 10));
+    // this rank's own row-buffer offset travels to the plan kernel in plan[4 + 4 * rank + 3]
+    const int own_y = (int)(e.ybuf_off >> 10);
+    if (cudaMemcpyAsync(e.plan + 4 + 4 * c->rank + 3, &own_y, sizeof(int), cudaMemcpyHostToDevice, s) != cudaSuccess)
+        return GSB_ERR_CUDA;
+    ep_plan_kernel<<<1, 1024, 0, s>>>(c->peers, c->rank, c->world, e.E, seq_c, e.recv_offsets, e.send_base, e.ydst,
+                                      e.H, e.y_elem_bytes, e.recv_cap, e.plan, c->wait_cycles);
+    if (e.P > 0)
+        ep_dispatch_push_kernel<<<e.P, 256, 0, s>>>(c->peers, c->rank, c->world, e.E, e.x, e.expert_offsets, e.sorted_tok,
+                                                    e.send_base, e.sorted_expert, e.H, e.plan, e.recv_off, e.frag_order);
     ++c->seq[kChDispatch];
     return comm_launch_signal(c, kChDispatch, s);
 }
@@ -291,6 +345,9 @@ int gsb_comm_create(int rank, int world, size_t heap_bytes, void* out_handle, gs
     if (!c) return GSB_ERR_CUDA;
     c->rank = rank; c->world = world;
     c->heap_bytes = (heap_bytes + 255) / 256 * 256;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    c->sm_count = sms > 0 ? sms : 148;
     if (cudaMalloc(reinterpret_cast<void**>(&c->local), kCtrlBytes + c->heap_bytes) != cudaSuccess) { delete c; return GSB_ERR_CUDA; }
     if (cudaMemset(c->local, 0, kCtrlBytes) != cudaSuccess) { cudaFree(c->local); delete c; return GSB_ERR_CUDA; }
     cudaIpcMemHandle_t h;
@@ -302,7 +359,7 @@ int gsb_comm_create(int rank, int world, size_t heap_bytes, void* out_handle, gs
 }
 
 int gsb_comm_open(gsb_comm* c, const void* handles) {
-    if (!c || !handles) return GSB_ERR_INVALID_ARG;
+    if (!c || !handles || c->loopback) return GSB_ERR_INVALID_ARG;
     for (int r = 0; r < c->world; ++r) {
         if (r == c->rank) continue;
         cudaIpcMemHandle_t h;
@@ -312,6 +369,21 @@ int gsb_comm_open(gsb_comm* c, const void* handles) {
         c->peers.base[r] = static_cast<uint8_t*>(p);
         c->opened[r] = true;
     }
+    return GSB_OK;
+}
+
+int gsb_comm_open_loopback(gsb_comm* c) {
+    if (!c) return GSB_ERR_INVALID_ARG;
+    for (int r = 0; r < c->world; ++r)
+        if (c->opened[r]) return GSB_ERR_INVALID_ARG;
+    for (int r = 0; r < c->world; ++r) c->peers.base[r] = c->local;
+    c->loopback = true;
+    return GSB_OK;
+}
+
+int gsb_comm_set_wait_cycles(gsb_comm* c, long long cycles) {
+    if (!c || cycles < 0) return GSB_ERR_INVALID_ARG;
+    c->wait_cycles = cycles ? cycles : kCommWaitCycles;
     return GSB_OK;
 }
 
@@ -346,19 +418,19 @@ int gsb_comm_barrier(gsb_comm* c, void* stream) {
     return comm_launch_wait(c, kChBarrier, s);
 }
 
-// The first `2 * 2 * stage_floats` floats of the heap are the all-reduce staging (two parities,
-// two areas); callers that also use the heap for expert parallelism place their buffers after
-// gsb_comm_allreduce_reserve() bytes.
+// The first bytes of the heap are the all-reduce staging: two parities of two areas of
+// (max_count + kArPad) floats; callers that also use the heap for expert parallelism place their
+// buffers after gsb_comm_allreduce_reserve() bytes.
 size_t gsb_comm_allreduce_reserve(gsb_comm* c, int64_t max_count) {
     if (!c || max_count < 0) return 0;
     const size_t fl = ((size_t)max_count + 3) / 4 * 4;
     c->ar_stage_floats = fl;
-    return 4 * fl * sizeof(float);
+    return 4 * (fl + kArPad) * sizeof(float);
 }
 
 int gsb_comm_allreduce_one_shot_limit(gsb_comm* c, int64_t total_floats) {
     if (!c || total_floats < 0) return GSB_ERR_INVALID_ARG;
-    c->ar_one_shot_limit = total_floats ? total_floats : (int64_t)(1 << 21);
+    c->ar_one_shot_limit = total_floats ? total_floats : (int64_t)(1 << 18);
     return GSB_OK;
 }
 
@@ -367,21 +439,23 @@ int gsb_comm_allreduce_sum(gsb_comm* c, float* data, int64_t count, void* stream
     if (c->world == 1 || count == 0) return GSB_OK;
     if (count % 4 || (reinterpret_cast<uintptr_t>(data) & 15)) return GSB_ERR_INVALID_ARG;
     if ((size_t)count > c->ar_stage_floats) return GSB_ERR_TOO_LARGE;
-    if (4 * c->ar_stage_floats * sizeof(float) > c->heap_bytes) return GSB_ERR_WORKSPACE;
+    const size_t area = c->ar_stage_floats + kArPad;
+    if (4 * area * sizeof(float) > c->heap_bytes) return GSB_ERR_WORKSPACE;
     const unsigned seq = ++c->seq[kChAllReduce];
-    c->seq[kChAllReduce2] = seq;
-    const int parity = seq & 1;
-    const size_t stage_off = kCtrlBytes + (size_t)parity * 2 * c->ar_stage_floats * sizeof(float);
-    const size_t stage2_off = stage_off + c->ar_stage_floats * sizeof(float);
-    const int64_t count4 = count / 4;
-    const int two_shot = count * c->world > c->ar_one_shot_limit ? 1 : 0;
-    int sms = 148;
-    int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int64_t blocks = (count4 + 511) / 512;
-    if (blocks > sms) blocks = sms;   // every block must be resident: they wait on one another's flags
-    allreduce_kernel<<<(unsigned)blocks, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        c->peers, c->rank, c->world, data, count4, stage_off, stage2_off, (int)seq, two_shot);
+    ArArgs a{};
+    a.pr = c->peers; a.rank = c->rank; a.world = c->world; a.data = data; a.count4 = count / 4;
+    a.area_bytes = area * sizeof(float);
+    a.stage_off = kCtrlBytes + (size_t)(seq & 1u) * 2 * a.area_bytes;
+    a.seq = (int)seq; a.wait_cycles = c->wait_cycles;
+    // one-shot while it is allowed and the world slots of `count` floats fit the two areas
+    a.two_shot = (count * c->world > c->ar_one_shot_limit || (size_t)count * c->world > 2 * c->ar_stage_floats) ? 1 : 0;
+    int64_t blocks = (a.count4 + 255) / 256;
+    if (a.two_shot) blocks = ((a.count4 + c->world - 1) / c->world + 255) / 256 * 1;   // one 256-thread pass over a slice part
+    if (a.two_shot) blocks = blocks * 2;                                                // two parts per slice pass: more stores in flight
+    const int64_t cap = c->sm_count < kMaxArBlocks ? c->sm_count : kMaxArBlocks;       // every block resident: blocks wait on peers
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    allreduce_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
     return launch_status();
 }
 

@@ -29,6 +29,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 // silu exactly as the CPU reference writes it (src/model_glm52.cpp:95): x / (1 + exp(-x)).
 __device__ __forceinline__ float silu_ref(float x) { return __fdiv_rn(x, 1.0f + expf(-x)); }
 
+// largest finite fp16 instead of infinity: an intermediate beyond +-65504 must not turn into
+// inf and then NaN (inf * 0) further down; the fp32 reference has no such cliff
+__device__ __forceinline__ __half sat_half(float v) {
+    return __float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f));
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -55,6 +61,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
     return ok != 0;
+}
+// Non-blocking test of a phase (try_wait may suspend the thread for a while before it answers).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok;
 }
 // Bounded wait: gives up after `limit_cycles` SM clock cycles and returns false (the caller
 // records the error and leaves); a wait that would otherwise hang the GPU ends in about a
@@ -93,11 +111,9 @@ __device__ __host__ __forceinline__ int frag_pos(int f) {
     return (kb << 7) + (((j << 2) + t) << 3) + el;
 }
 
-// One 8-feature group of a bf16 row -> fp16 at its fragment-order position (exact for |x| in
-// the fp16 normal range; values beyond +-65504 saturate to the largest finite fp16).
-__device__ __forceinline__ void xprep_group(const __nv_bfloat16* __restrict__ x, __half* __restrict__ xp,
-                                            int64_t row, int grp, int H) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + row * H) + grp);
+// Four bf16 pairs -> fp16 (exact for |x| in the fp16 normal range; values beyond +-65504
+// saturate to the largest finite fp16).
+__device__ __forceinline__ uint4 bf16x8_to_half8(const uint4& v) {
     const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&v);
     uint4 o;
     uint32_t* op = reinterpret_cast<uint32_t*>(&o);
@@ -109,7 +125,41 @@ __device__ __forceinline__ void xprep_group(const __nv_bfloat16* __restrict__ x,
         const __half2 h = __floats2half2_rn(f.x, f.y);
         op[q] = *reinterpret_cast<const uint32_t*>(&h);
     }
-    *reinterpret_cast<uint4*>(xp + row * H + frag_pos(grp << 3)) = o;
+    return o;
+}
+
+// Eight fp32 values (a0, a1) normalised as the CPU reference does (src/model_glm52.cpp:61-71:
+// x * inv * w, each product rounded) and rounded to bf16, as four packed pairs.
+__device__ __forceinline__ uint4 norm8_bf16(const uint4& a0, const uint4& a1, const uint4& w0, const uint4& w1, float inv) {
+    const float xv[8] = {__uint_as_float(a0.x), __uint_as_float(a0.y), __uint_as_float(a0.z), __uint_as_float(a0.w),
+                         __uint_as_float(a1.x), __uint_as_float(a1.y), __uint_as_float(a1.z), __uint_as_float(a1.w)};
+    const float wv[8] = {__uint_as_float(w0.x), __uint_as_float(w0.y), __uint_as_float(w0.z), __uint_as_float(w0.w),
+                         __uint_as_float(w1.x), __uint_as_float(w1.y), __uint_as_float(w1.z), __uint_as_float(w1.w)};
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(__fmul_rn(__fmul_rn(xv[2 * q], inv), wv[2 * q]),
+                                                       __fmul_rn(__fmul_rn(xv[2 * q + 1], inv), wv[2 * q + 1]));
+        op[q] = *reinterpret_cast<const uint32_t*>(&b);
+    }
+    return o;
+}
+
+// One 8-feature group of a bf16 row -> fp16, at its fragment-order position or (natural != 0) in place.
+__device__ __forceinline__ void xprep_group(const __nv_bfloat16* __restrict__ x, __half* __restrict__ xp,
+                                            int64_t row, int grp, int H, int natural = 0) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + row * H) + grp);
+    *reinterpret_cast<uint4*>(xp + row * H + (natural ? (grp << 3) : frag_pos(grp << 3))) = bf16x8_to_half8(v);
+}
+// The same from an fp32 hidden state through the pre-norm: fp16(bf16(x * inv * w)).
+__device__ __forceinline__ void xprep_group_norm(const float* __restrict__ hidden, const float* __restrict__ norm_w,
+                                                 float inv, __half* __restrict__ xp, int64_t row, int grp, int H,
+                                                 int natural) {
+    const uint4* hp = reinterpret_cast<const uint4*>(hidden + row * H) + 2 * grp;
+    const uint4* wp = reinterpret_cast<const uint4*>(norm_w) + 2 * grp;
+    const uint4 v = norm8_bf16(__ldg(hp), __ldg(hp + 1), __ldg(wp), __ldg(wp + 1), inv);
+    *reinterpret_cast<uint4*>(xp + row * H + (natural ? (grp << 3) : frag_pos(grp << 3))) = bf16x8_to_half8(v);
 }
 
 }  // namespace gsb

@@ -393,7 +393,7 @@ decode_gemm_kernel(const DecodeKArgs a) {
                 const long long slot = im.slot_begin + n;
                 if (GU) {
                     const float h = __fmul_rn(silu_ref(s0), s1);
-                    a.hbuf[slot * a.ldh + frag_pos(im.unit * 16 + r)] = __float2half_rn(h);
+                    a.hbuf[slot * a.ldh + frag_pos(im.unit * 16 + r)] = sat_half(h);
                 } else {
                     float* y = a.ybuf + slot * a.H + im.unit * 32 + r;
                     y[0] = s0;
@@ -468,7 +468,7 @@ __device__ __forceinline__ void reduce_item(const DecodeKArgs& a, const float* _
         const int n = n0 + 2 * v;
         if (n >= ntok) continue;
         const long long slot = slot_begin + n;
-        if (GU) a.hbuf[slot * a.ldh + frag_pos(unit * 16 + r)] = __float2half_rn(__fmul_rn(silu_ref(s0[v]), s1[v & 1]));
+        if (GU) a.hbuf[slot * a.ldh + frag_pos(unit * 16 + r)] = sat_half(__fmul_rn(silu_ref(s0[v]), s1[v & 1]));
         else a.ybuf[slot * a.H + unit * 32 + m * 16 + r] = s0[v];
     }
 }
@@ -807,15 +807,15 @@ route_fused_kernel(const RouteFusedArgs a) {
                     a.units_gu_s, a.units_dn, a.grid);
 }
 
-// bf16 activations -> fp16 in fragment order (exact for |x| in the fp16 normal range; values
-// beyond +-65504 saturate to the largest finite fp16).
+// bf16 activations -> fp16 in fragment order or natural order (exact for |x| in the fp16 normal
+// range; values beyond +-65504 saturate to the largest finite fp16).
 __global__ void __launch_bounds__(256)
-xprep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ xp, int64_t n, int H) {
+xprep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ xp, int64_t n, int H, int natural) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one 8-feature group each
     const int gpr = H >> 3;
     if (i >= n * gpr) return;
     const int64_t row = i / gpr;
-    xprep_group(x, xp, row, (int)(i - row * gpr), H);
+    xprep_group(x, xp, row, (int)(i - row * gpr), H, natural);
 }
 
 // Deterministic weighted combine (replaces the in-kernel slot sum of
@@ -825,7 +825,7 @@ xprep_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ xp, int64
 __global__ void __launch_bounds__(256)
 combine_kernel(const float* __restrict__ ybuf, const int* __restrict__ slot_pos,
                const float* __restrict__ topk_w, int n, int topk, int H, int P, int has_shared,
-               float* __restrict__ out, int pdl_wait) {
+               const float* residual, float* out, int pdl_wait) {
     if (pdl_wait) asm volatile("griddepcontrol.wait;" ::: "memory");   // launched under the down kernel's tail
     const int t = blockIdx.y;
     const int c4 = blockIdx.x * blockDim.x + threadIdx.x;
@@ -847,6 +847,11 @@ combine_kernel(const float* __restrict__ ybuf, const int* __restrict__ slot_pos,
         acc.z = __fadd_rn(acc.z, y.z);
         acc.w = __fadd_rn(acc.w, y.w);
     }
+    if (residual) {   // hidden + mlp with the layer's sum complete before the add (src/model_gpu.cpp:1502);
+                      // out may be the residual itself: each thread reads its element before it writes it
+        const float4 r = reinterpret_cast<const float4*>(residual + (int64_t)t * H)[c4];
+        acc = make_float4(__fadd_rn(r.x, acc.x), __fadd_rn(r.y, acc.y), __fadd_rn(r.z, acc.z), __fadd_rn(r.w, acc.w));
+    }
     reinterpret_cast<float4*>(out + (int64_t)t * H)[c4] = acc;
 }
 
@@ -864,6 +869,12 @@ int pick_stages(int Kmax) {
 }
 
 }  // namespace
+
+int launch_xprep(const __nv_bfloat16* x, __half* xp, int64_t n, int H, int natural, cudaStream_t s) {
+    if (n == 0) return GSB_OK;
+    xprep_kernel<<<(unsigned)((n * (H >> 3) + 255) / 256), 256, 0, s>>>(x, xp, n, H, natural);
+    return launch_status();
+}
 
 size_t decode_seg_bytes(int n, int topk, int E) {
     const size_t P = (size_t)n * topk;
@@ -923,8 +934,10 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     const int imax = d.I > d.Is ? d.I : d.Is;
     if (d.E > 1024) return GSB_ERR_UNSUPPORTED;
     if (d.sm_count > 1024) return GSB_ERR_UNSUPPORTED;
-    if (!d.xp_ready)
-        xprep_kernel<<<(unsigned)(((int64_t)d.n * (d.H >> 3) + 255) / 256), 256, 0, s>>>(d.x, d.xp, d.n, d.H);
+    if (!d.xp_ready) {
+        const int st0 = launch_xprep(d.x, d.xp, d.n, d.H, 0, s);
+        if (st0) return st0;
+    }
     int* xsegs = d.segs + xsegs_offset_ints(d.n, d.topk, d.E);
     if (d.fused_route) {
         if (!decode_route_fusable(d.n, d.topk, d.E)) return GSB_ERR_INVALID_ARG;
@@ -1010,11 +1023,12 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
         at[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
         if (cudaLaunchKernelEx(&cfg, combine_kernel, (const float*)d.ybuf, (const int*)d.slot_pos,
-                               (const float*)d.topk_w, d.n, d.topk, d.H, P, shared ? 1 : 0, d.out, 1) != cudaSuccess)
+                               (const float*)d.topk_w, d.n, d.topk, d.H, P, shared ? 1 : 0, (const float*)d.residual,
+                               d.out, 1) != cudaSuccess)
             return GSB_ERR_LAUNCH;
     } else {
         combine_kernel<<<cgrid, 256, 0, s>>>(d.ybuf, d.slot_pos, d.topk_w, d.n, d.topk, d.H, P,
-                                             shared ? 1 : 0, d.out, 0);
+                                             shared ? 1 : 0, d.residual, d.out, 0);
     }
     return launch_status();
 }

@@ -21,7 +21,7 @@ EpHeap ep_heap(const gsb_moe_config& c, int n, int recv_cap) {
 struct EpWs {
     int* status; float* logits; float* scores; int* ids; float* w; int* expert_offsets; int* sorted_tok;
     int* sorted_row; int* slot_pos; int* sorted_expert; int* disp_scratch; int* recv_offsets; int* send_base; void** ydst;
-    int* recv_total; int* tiles_gu; int* tiles_dn; int* tiles_sh_gu; int* tiles_sh_dn;
+    int* plan; int* tiles; int* tiles_sh;
     __half* hbuf; __half* xs_local; __half* hbuf_sh;
     size_t total;
 };
@@ -49,14 +49,9 @@ EpWs ep_carve(const gsb_moe_config& c, int n, int recv_cap, void* base) {
     ws.recv_offsets = reinterpret_cast<int*>(take((size_t)(El + 1) * sizeof(int)));
     ws.send_base = reinterpret_cast<int*>(take((size_t)c.n_experts * sizeof(int)));
     ws.ydst = reinterpret_cast<void**>(take((size_t)recv_cap * sizeof(void*)));
-    ws.recv_total = reinterpret_cast<int*>(take(sizeof(int)));
-    const size_t tb = prefill_tile_bytes(recv_cap / (c.topk > 0 ? c.topk : 1) + 1, c.topk, El, c.hidden,
-                                         c.moe_inter > c.shared_inter ? c.moe_inter : c.shared_inter);
-    ws.tiles_gu = reinterpret_cast<int*>(take(tb));
-    ws.tiles_dn = reinterpret_cast<int*>(take(tb));
-    const size_t tbs = prefill_tile_bytes(n, 1, 1, c.hidden, c.shared_inter > 0 ? c.shared_inter : 64);
-    ws.tiles_sh_gu = reinterpret_cast<int*>(take(tbs));
-    ws.tiles_sh_dn = reinterpret_cast<int*>(take(tbs));
+    ws.plan = reinterpret_cast<int*>(take((4 + 4 * kMaxWorld) * sizeof(int)));
+    ws.tiles = reinterpret_cast<int*>(take(prefill_tile_bytes(recv_cap / (c.topk > 0 ? c.topk : 1) + 1, c.topk, El)));
+    ws.tiles_sh = reinterpret_cast<int*>(take(prefill_tile_bytes(n, 1, 1)));
     ws.hbuf = reinterpret_cast<__half*>(take((size_t)recv_cap * c.moe_inter * sizeof(__half)));
     ws.xs_local = reinterpret_cast<__half*>(take((size_t)n * c.hidden * sizeof(__half)));
     ws.hbuf_sh = reinterpret_cast<__half*>(take((size_t)n * (c.shared_inter > 0 ? c.shared_inter : 1) * sizeof(__half)));
@@ -112,9 +107,12 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
                          ws.disp_scratch);
     if (st) return st;
     // counts -> plan -> push rows to their owners -> signal
-    st = comm_ep_exchange(comm, x, ws.expert_offsets, ws.sorted_tok, P, E, c.hidden, ws.sorted_expert,
-                          ws.recv_offsets, ws.send_base, ws.ydst, heap_offset + hp.ybuf, (int)sizeof(__half),
-                          heap_offset + hp.recv_x, recv_cap, ws.recv_total, s);
+    EpExchange ex{};
+    ex.x = x; ex.expert_offsets = ws.expert_offsets; ex.sorted_tok = ws.sorted_tok; ex.P = P; ex.E = E; ex.H = c.hidden;
+    ex.sorted_expert = ws.sorted_expert; ex.recv_offsets = ws.recv_offsets; ex.send_base = ws.send_base; ex.ydst = ws.ydst;
+    ex.plan = ws.plan; ex.recv_off = heap_offset + hp.recv_x; ex.ybuf_off = heap_offset + hp.ybuf;
+    ex.y_elem_bytes = (int)sizeof(__half); ex.recv_cap = recv_cap; ex.frag_order = 0;
+    st = comm_ep_exchange(comm, ex, s);
     if (st) return st;
 
     PrefillEpArgs a{};
@@ -122,9 +120,9 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
     a.shared_gate_up_packed = c.shared_gate_up_packed; a.shared_down_packed = c.shared_down_packed;
     a.H = c.hidden; a.I = c.moe_inter; a.Is = c.shared_inter; a.El = El;
     a.recv_offsets = ws.recv_offsets; a.recv_x = recv_x; a.recv_cap = recv_cap; a.hbuf = ws.hbuf;
-    a.ydst = reinterpret_cast<__half* const*>(ws.ydst); a.tiles_gu = ws.tiles_gu; a.tiles_dn = ws.tiles_dn;
+    a.ydst = reinterpret_cast<__half* const*>(ws.ydst); a.tiles = ws.tiles;
     a.x = x; a.n = n; a.xs_local = ws.xs_local; a.hbuf_sh = ws.hbuf_sh; a.y_shared = ybuf + (size_t)P * c.hidden;
-    a.tiles_sh_gu = ws.tiles_sh_gu; a.tiles_sh_dn = ws.tiles_sh_dn; a.status = ws.status; a.sm_count = layer->sm_count;
+    a.tiles_sh = ws.tiles_sh; a.status = ws.status; a.sm_count = layer->sm_count;
 
     // the shared expert needs only local tokens: it runs while the peers' rows are in flight
     if (n > 0) { st = launch_prefill_ep_shared(a, s); if (st) return st; }
@@ -137,7 +135,7 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
     if (st) return st;
     st = comm_launch_wait(comm, kChCombine, s);
     if (st) return st;
-    return launch_combine_h(ybuf, ws.slot_pos, ws.w, n, c.topk, c.hidden, P, c.shared_inter > 0 ? 1 : 0, out, s);
+    return launch_combine_h(ybuf, ws.slot_pos, ws.w, n, c.topk, c.hidden, P, c.shared_inter > 0 ? 1 : 0, nullptr, out, s);
 }
 
 }  // extern "C"

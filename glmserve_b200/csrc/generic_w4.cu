@@ -104,7 +104,8 @@ generic_expert_kernel(GenericExpertArgs a) {
         __syncthreads();
     }
     float* orow = a.out + (size_t)t * a.H;
-    for (int i = tid; i < a.H; i += blockDim.x) orow[i] = acc[i];
+    const float* rrow = a.residual ? a.residual + (size_t)t * a.H : nullptr;
+    for (int i = tid; i < a.H; i += blockDim.x) orow[i] = rrow ? __fadd_rn(rrow[i], acc[i]) : acc[i];
 }
 
 template <typename XT, typename ST, bool W4>

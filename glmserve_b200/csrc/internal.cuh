@@ -17,7 +17,15 @@ constexpr int kFlagBase = 64;
 constexpr int kMaxExperts = 1024;
 constexpr int kCntBase = 1024;
 constexpr int kStatusWord = 0;                  // ctrl[0]: sticky GSB_ERR_TIMEOUT
-constexpr int kArriveCounter = 8;               // ctrl[8..]: block arrival counters (local use)
+//   [kMetaBase + src*8 + i]            expert-parallel layout posted by rank src: {receive buffer offset and
+//                                      per-slot row buffer offset in KiB from the heap start, receive capacity}
+//   [kBlkFlagBase + (phase*kMaxWorld + src)*kMaxArBlocks + b]   all-reduce: block b of rank src finished `phase`
+constexpr int kMetaBase = 12288;
+constexpr int kMaxArBlocks = 256;
+constexpr int kBlkFlagBase = 16384;
+static_assert(kCntBase + kMaxWorld * kMaxExperts <= kMetaBase && kMetaBase + kMaxWorld * 8 <= kBlkFlagBase &&
+              (kBlkFlagBase + 2 * kMaxWorld * kMaxArBlocks) * sizeof(int) <= kCtrlBytes, "control area layout");
+constexpr size_t kArPad = 64;                   // floats of slack per staging area (slices are rounded up)
 
 struct CommPeers { uint8_t* base[kMaxWorld]; };
 
@@ -30,8 +38,11 @@ struct gsb_comm {
     gsb::CommPeers peers{};
     bool opened[gsb::kMaxWorld] = {};
     unsigned seq[gsb::kNumCh] = {};
-    size_t ar_stage_floats = 0;                 // capacity of the all-reduce staging (per parity)
-    int64_t ar_one_shot_limit = 1 << 21;        // count * world up to which every rank pulls everything
+    size_t ar_stage_floats = 0;                 // largest message the all-reduce staging was reserved for
+    int64_t ar_one_shot_limit = 1 << 18;        // count * world up to which the one-shot form is used
+    long long wait_cycles = gsb::kCommWaitCycles;  // budget of every device-side wait (SM clocks)
+    bool loopback = false;                      // every peer slot maps this rank's own heap (single-process tests)
+    int sm_count = 148;
 };
 
 
@@ -48,8 +59,20 @@ struct gsb_moe_layer {
 namespace gsb {
 int comm_launch_signal(gsb_comm* c, int ch, cudaStream_t s);
 int comm_launch_wait(gsb_comm* c, int ch, cudaStream_t s);
-int comm_ep_exchange(gsb_comm* c, const __nv_bfloat16* x, const int* expert_offsets, const int* sorted_tok,
-                     int P, int E, int H, int* sorted_expert, int* recv_offsets, int* send_base, void** ydst,
-                     size_t ybuf_off, int y_elem_bytes, size_t recv_off, int recv_cap, int* recv_total,
-                     cudaStream_t s);
+struct EpExchange {
+    const __nv_bfloat16* x;        // this rank's tokens [n, H]
+    const int* expert_offsets;     // local dispatch [E + 1]
+    const int* sorted_tok;         // [P]
+    int P, E, H;
+    int* sorted_expert;            // scratch [P]
+    int* recv_offsets;             // out [El + 1]
+    int* send_base;                // out [E]
+    void** ydst;                   // out [recv_cap]
+    int* plan;                     // out [4 + 4 * kMaxWorld]: {ok, rows received, 0, 0} then every rank's posted layout
+    size_t recv_off, ybuf_off;     // byte offsets from the heap start (multiples of 1 KiB) of this rank's buffers
+    int y_elem_bytes;              // element size of the per-slot output rows (2 = fp16, 4 = fp32)
+    int recv_cap;
+    int frag_order;                // 1: rows are pushed in the decode kernels' fragment order
+};
+int comm_ep_exchange(gsb_comm* c, const EpExchange& e, cudaStream_t s);
 }  // namespace gsb

@@ -23,9 +23,12 @@ int launch_fixed_routing(int n, int topk, int* ids, float* w, cudaStream_t s);
 int launch_router_topk(const float* logits, const float* e_bias, int n, int E, int topk,
                        int norm_topk, float routed_scale, int* ids, float* w, cudaStream_t s,
                        bool from_scores = false);
-// scores (nullable): also store sigmoid(logit)
+// scores (nullable): also store sigmoid(logit).  xp (nullable): also write the activations as fp16 rows
+// (fragment order, or natural order when xp_natural).  hidden (nullable): the activations are
+// bf16(rmsnorm(hidden, norm_w, eps)) instead of x.
 int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n, int H, int E,
-                         float* logits, float* scores, cudaStream_t s, __half* xp = nullptr);
+                         float* logits, float* scores, cudaStream_t s, __half* xp = nullptr, int xp_natural = 0,
+                         const float* hidden = nullptr, const float* norm_w = nullptr, float eps = 0.f);
 // scratch: dispatch_scratch_bytes() of device memory, or null (then one block does everything)
 int launch_dispatch(const int* topk_ids, int n, int topk, int E, int* expert_offsets,
                     int* sorted_token_ids, int* sorted_row, int* slot_pos, cudaStream_t s, int* scratch = nullptr);
@@ -45,6 +48,7 @@ struct GenericExpertArgs {
     const uint8_t* sd; const void* sd_sc;
     int n, topk, H, I, Is, E, group;
     float* out;
+    const float* residual;   // nullable: out = residual + layer (out may be the residual itself)
 };
 int launch_generic_expert(const GenericExpertArgs& a, int xt, int st, bool w4, cudaStream_t s);
 int launch_generic_gemm_w4(const float* x, const uint8_t* qW, const float* scales,
@@ -84,6 +88,7 @@ struct DecodeArgs {
     float* ybuf;
     int* status;
     float* out;
+    const float* residual;   // nullable: out = residual + layer (out may be the residual itself)
     int sm_count;
     int force_smem_variant;  // 1: always use the shared-memory-activation variant (testing)
     cudaEvent_t ev_prep, ev_gate_up, ev_down;  // optional stage marks (null = none)
@@ -96,10 +101,12 @@ struct DecodeArgs {
     int xp_ready;            // 1: xp already holds the converted activations (logits launch did it)
 };
 int launch_decode_layer(const DecodeArgs& a, cudaStream_t s);
+// bf16 rows -> fp16 rows in fragment order (natural = 0) or natural feature order (1)
+int launch_xprep(const __nv_bfloat16* x, __half* xp, int64_t n, int H, int natural, cudaStream_t s);
 // whether the single-block routing kernel covers this shape
 inline bool decode_route_fusable(int n, int topk, int E) { return n <= 128 && E <= 256 && topk <= 32 && n * topk <= 4096; }
 
-size_t prefill_tile_bytes(int n, int topk, int E, int H, int I);
+size_t prefill_tile_bytes(int n, int topk, int E);
 
 struct PrefillArgs {
     const __nv_bfloat16* x;
@@ -112,13 +119,15 @@ struct PrefillArgs {
     const int* sorted_tok;
     const int* slot_pos;
     const float* topk_w;
-    int* tiles_gu;
-    int* tiles_dn;
+    int* tiles;     // token-tile list (prefill_tile_bytes), read by both GEMM kernels
+    __half* xh;     // [n, H] fp16 activations in token order, natural feature order
+    int xh_ready;   // 1: the router-logits launch already wrote xh
     __half* xs;     // [P + n, H] fp16 activations in expert order
     __half* hbuf;   // [P + n, max(I, Is)] fp16
     __half* ybuf;   // [P + n, H] fp16 per-slot output rows
     int* status;
     float* out;
+    const float* residual;  // nullable: out = residual + layer (out may be the residual itself)
     int sm_count;
     cudaEvent_t ev_prep, ev_gate_up, ev_down;
 };
@@ -136,18 +145,18 @@ struct PrefillEpArgs {
     int recv_cap;
     __half* hbuf;                       // [recv_cap, I]
     __half* const* ydst;                // [recv_cap] where each received row's output goes
-    int* tiles_gu; int* tiles_dn;
+    int* tiles;                         // token-tile list over the received rows
     const __nv_bfloat16* x; int n;      // this GPU's own tokens (shared expert)
     __half* xs_local;                   // [n, H]
     __half* hbuf_sh;                    // [n, Is]
     __half* y_shared;                   // [n, H]
-    int* tiles_sh_gu; int* tiles_sh_dn;
+    int* tiles_sh;                      // token-tile list of the shared expert over the local tokens
     int* status;
     int sm_count;
 };
 int launch_prefill_ep_shared(const PrefillEpArgs& a, cudaStream_t s);
 int launch_prefill_ep_routed(const PrefillEpArgs& a, cudaStream_t s);
 int launch_combine_h(const __half* ybuf, const int* slot_pos, const float* topk_w, int n, int topk, int H,
-                     int P, int has_shared, float* out, cudaStream_t s);
+                     int P, int has_shared, const float* residual, float* out, cudaStream_t s);
 
 }  // namespace gsb

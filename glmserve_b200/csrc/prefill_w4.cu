@@ -1,19 +1,23 @@
 // Prefill-shaped W4A16 grouped GEMM on the 5th-generation tensor cores (tcgen05 / TMEM).
 //
-// D[weight row, token] = sum_k W[row, k] * X[token, k] for one tile = (expert segment of up
-// to 256 token rows) x (128 weight rows = four 32-row units of the tile stream).
+// D[weight row, token] = sum_k W[row, k] * X[token, k] for one tile = (up to 192 token rows of
+// one expert) x (128 weight rows = four 32-row units of the tile stream).
 //   A operand (M = 128 weight rows): int4 chunks arrive by 1-D bulk copies; eight dequant
-//     warps unpack them to fp16 (q - 8) * scale and store them into shared memory in the
-//     K-major 128-byte-swizzled layout the tensor core reads.
-//   B operand (N = 16..256 token rows): fp16 activations, gathered into expert order
-//     beforehand, loaded by TMA (2-D tiled, 128-byte swizzle, no multicast).
-//   D: fp32 in tensor memory, two buffers of 256 columns so the epilogue of one tile overlaps
-//     the main loop of the next.
-// One thread issues tcgen05.mma (cta_group::1, kind::f16, 128 x N x 16); tcgen05.commit
-// releases shared-memory stages and publishes finished accumulators through mbarriers.
+//     warps unpack them to fp16 (q - 8) * scale and store them with tcgen05.st straight into
+//     TENSOR MEMORY (lane = weight row, one 32-bit column per pair of input columns), a ring of
+//     four 64-column k-blocks.  The tensor core reads A from there, so the dequantised weights
+//     never touch shared memory: its bandwidth is left to the activation tiles, and a k-block is
+//     handed over with one tcgen05.st per thread instead of eight swizzled shared-memory stores
+//     and a proxy fence.
+//   B operand (N = 16..192 token rows): fp16 activations, gathered into expert order
+//     beforehand, loaded by TMA (2-D tiled, 128-byte swizzle, no multicast), five stages.
+//   D: fp32 in tensor memory, two buffers of 192 columns so the epilogue of one tile overlaps
+//     the main loop of the next.  TMEM columns: [0,192) and [192,384) accumulators, [384,512) A.
+// One thread issues tcgen05.mma (cta_group::1, kind::f16, 128 x N x 16, A from TMEM);
+// tcgen05.commit releases stages and publishes finished accumulators through mbarriers.
 // Epilogue warps read the accumulator with tcgen05.ld: the gate/up kernel pairs gate and up
 // rows (lanes l and l^16 of a warp) to fuse SwiGLU and stores fp16 h; the down kernel stores
-// the slot's fp16 output row.  Persistent CTAs walk a tile list built on the device.
+// the slot's fp16 output row.  Persistent CTAs walk a list of token tiles built on the device.
 // All waits are bounded (see mbar_wait); a timeout is recorded in the status word.
 #include <cuda.h>
 
@@ -24,20 +28,27 @@ namespace gsb {
 
 namespace {
 
-constexpr int kPfThreads = 512;        // 16 warps
-// A (dequantised weights, 16 KiB) and B (activations, 32 KiB) stages are template parameters
-// AS / BS of the kernel; one stage = one 64-column k-block.
-constexpr int kBN = 256;               // token rows per tile (TMA box rows)
-constexpr int kABytes = 128 * 128;     // 128 weight rows x 64 fp16
-constexpr int kBBytes = kBN * 128;     // 256 token rows x 64 fp16
-constexpr int kQBytes = 4 * kChunkBytes;  // four units x one 512-column chunk
+constexpr int kDqGroups = 4;           // groups of four unpack warps; group g owns ring stage g
+constexpr int kPfThreads = 256 + kDqGroups * 128;   // 4 service warps, 4 epilogue warps, the unpack warps
+constexpr int kBN = 192;               // token rows per tile at most (TMA box rows, accumulator columns)
+constexpr int kBBytes = kBN * 128;     // one activation stage: 192 token rows x 64 fp16
+constexpr int kQBytes = 4 * kChunkBytes;  // one int4 stage: four units x one 512-column chunk
+constexpr int kAStages = 4;            // TMEM ring of dequantised k-blocks (32 columns each)
+constexpr int kBStages = 6;            // shared-memory ring of activation tiles (deeper: a TMA load takes longer to land
+                                       // than three k-blocks take to multiply)
+constexpr int kACol0 = 2 * kBN;        // first TMEM column of that ring
 constexpr long long kPfWaitLimit = 2000000000LL;
 constexpr int kTileHeader = 4;
+constexpr int kEpiWarpBytes = 2048;     // per epilogue warp: 32 tokens x 32 features fp16
+static_assert(kDqGroups == kAStages && kAStages % 2 == 0 && kBStages % 2 == 0, "an unpack group per ring stage; stages are handed over in pairs");
+static_assert(kACol0 + kAStages * 32 <= 512, "accumulators and the A ring must fit the 512 TMEM columns");
 
 struct PrefillKArgs {
     const uint8_t* packed;
     const uint8_t* shared_packed;
-    const int* tiles;        // [0] = ntiles; then int4 {expert, first slot, tokens, row block}
+    const int* tiles;        // [0] = routed token tiles, [1] = shared-expert token tiles; then int4
+                             // {expert, first slot, tokens, 0} per token tile, routed ones first
+    int RB, RBs;             // 128-row blocks per routed / shared token tile (tile = token tile x row block)
     int K, Ks;               // input dims (routed / shared)
     int units, units_s;      // 32-row units per expert
     int E;
@@ -46,7 +57,20 @@ struct PrefillKArgs {
     __half* const* ydst;     // optional per-row output pointers (expert parallel: rows live on the
                              // token's home GPU and are stored there over NVLink); overrides ybuf
     int* status;
+    long long* prof;         // optional [grid][8] wait cycles per role (gsb_prefill_wait_profile)
 };
+
+// mbar_wait that also adds the cycles spent waiting to `acc` (try_wait may itself block for a while
+// before it answers, so the first call is timed as well)
+__device__ __forceinline__ bool mbar_wait_acc(uint64_t* bar, uint32_t parity, long long limit_cycles, long long& acc) {
+    const long long start = clock64();
+    bool ok = true;
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - start > limit_cycles) { ok = false; break; }
+    }
+    acc += clock64() - start;
+    return ok;
+}
 
 __device__ __forceinline__ void pf_timeout(const PrefillKArgs& a, volatile int* abort_flag, int where) {
     *abort_flag = 1;
@@ -71,11 +95,12 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem descriptor]
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -88,6 +113,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// One lane of the (converged) warp, the same one every time.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+// This thread's 32 registers -> its TMEM lane, columns taddr .. taddr + 31.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint4 (&v)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr),
+          "r"(v[0].x), "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y), "r"(v[1].z), "r"(v[1].w),
+          "r"(v[2].x), "r"(v[2].y), "r"(v[2].z), "r"(v[2].w), "r"(v[3].x), "r"(v[3].y), "r"(v[3].z), "r"(v[3].w),
+          "r"(v[4].x), "r"(v[4].y), "r"(v[4].z), "r"(v[4].w), "r"(v[5].x), "r"(v[5].y), "r"(v[5].z), "r"(v[5].w),
+          "r"(v[6].x), "r"(v[6].y), "r"(v[6].z), "r"(v[6].w), "r"(v[7].x), "r"(v[7].y), "r"(v[7].z), "r"(v[7].w)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 bytes apart, groups of
 // eight rows 1024 bytes apart (stride byte offset); descriptor version 1 (sm_100).
@@ -135,10 +179,16 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __half2 s2) {
 
 struct PfTile { int expert, slot0, ntok, rb, K, nkb, nround; const uint8_t* chunks; int unit_stride; };
 
+// tile idx -> (token tile, row block); row block varies fastest so CTAs running together share
+// the token tile through L2
 __device__ __forceinline__ PfTile pf_tile(const PrefillKArgs& a, int idx) {
-    const int4 t = reinterpret_cast<const int4*>(a.tiles + kTileHeader)[idx];
+    const int routed = a.tiles[0] * a.RB;
+    int tt, rb;
+    if (idx < routed) { tt = idx / a.RB; rb = idx - tt * a.RB; }
+    else { const int j = idx - routed; const int q = j / a.RBs; tt = a.tiles[0] + q; rb = j - q * a.RBs; }
+    const int4 t = reinterpret_cast<const int4*>(a.tiles + kTileHeader)[tt];
     PfTile r;
-    r.expert = t.x; r.slot0 = t.y; r.ntok = t.z; r.rb = t.w;
+    r.expert = t.x; r.slot0 = t.y; r.ntok = t.z; r.rb = rb;
     const bool sh = t.x >= a.E;
     r.K = sh ? a.Ks : a.K;
     r.nkb = r.K >> 6;
@@ -152,25 +202,28 @@ __device__ __forceinline__ PfTile pf_tile(const PrefillKArgs& a, int idx) {
     return r;
 }
 
-template <bool GU, int AS, int BS>
+template <bool GU, int QS>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tmap_b64,
-                    const __grid_constant__ CUtensorMap tmap_b128, const __grid_constant__ CUtensorMap tmap_b256) {
+                    const __grid_constant__ CUtensorMap tmap_b128, const __grid_constant__ CUtensorMap tmap_b192) {
     extern __shared__ uint8_t smem_raw[];
     // the kernel has no static shared memory, so the dynamic window starts 1024-byte aligned (the
     // swizzled tiles need that); checked below, a misaligned base is reported instead of used
     uint8_t* smem = smem_raw;
-    uint8_t* sA = smem;                                   // [AS][16 KiB]
-    uint8_t* sB = sA + AS * kABytes;                      // [BS][32 KiB]
-    uint8_t* sQ = sB + BS * kBBytes;                      // [2][4 chunks]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + 2 * kQBytes);
-    uint64_t* full_a = bars;                   // [AS] dequant warps -> MMA
-    uint64_t* empty = full_a + AS;             // [AS] MMA commit -> dequant
-    uint64_t* full_b = empty + AS;             // [BS] TMA -> MMA
-    uint64_t* empty_b = full_b + BS;           // [BS] MMA commit -> producer
-    uint64_t* q_full = empty_b + BS;           // [2] bulk copy -> dequant
-    uint64_t* q_empty = q_full + 2;            // [2] dequant -> producer
-    uint64_t* acc_full = q_empty + 2;          // [2] MMA commit -> epilogue
+    constexpr int BS = kBStages;
+    uint8_t* sB = smem;                                   // [BS][24 KiB]
+    uint8_t* sQ = sB + BS * kBBytes;                      // [QS][4 chunks]
+    uint8_t* sE = sQ + QS * kQBytes;                      // [4 epilogue warps][2 KiB] transposition staging
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sE + 4 * kEpiWarpBytes);
+    // Stages are handed over in PAIRS of k-blocks: the tensor pipe drains and idles while the MMA warp
+    // waits, fences and commits, so it does that once per eight MMAs, not once per four.
+    uint64_t* full = bars;                     // [kAStages / 2] the pair's 8 unpack warps -> MMA
+    uint64_t* empty = full + kAStages / 2;     // [kAStages / 2] MMA commit -> unpack warps
+    uint64_t* full_b = empty + kAStages / 2;   // [BS / 2] activation TMA (two loads) -> MMA
+    uint64_t* empty_b = full_b + BS / 2;       // [BS / 2] MMA commit -> producer
+    uint64_t* q_full = empty_b + BS / 2;       // [QS] bulk copy -> dequant
+    uint64_t* q_empty = q_full + QS;           // [QS] dequant -> producer
+    uint64_t* acc_full = q_empty + QS;         // [2] MMA commit -> epilogue
     uint64_t* acc_empty = acc_full + 2;        // [2] epilogue -> MMA
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -181,9 +234,10 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
         return;
     }
     if (tid == 0) {
-        for (int i = 0; i < AS; ++i) { mbar_init(&full_a[i], 4); mbar_init(&empty[i], 1); }
-        for (int i = 0; i < BS; ++i) { mbar_init(&full_b[i], 1); mbar_init(&empty_b[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 8); mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+        for (int i = 0; i < kAStages / 2; ++i) { mbar_init(&full[i], 8); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < BS / 2; ++i) { mbar_init(&full_b[i], 1); mbar_init(&empty_b[i], 1); }
+        for (int i = 0; i < QS; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 4 * kDqGroups); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -192,87 +246,128 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const int ntiles = a.tiles[0];
+    const int ntiles = a.tiles[0] * a.RB + a.tiles[1] * a.RBs;
 
     if (warp == 0) {
-        // ------------- producer: int4 chunks (bulk copies) and activation tiles (TMA) -------------
+        // ------------- producer of the activation tiles (TMA) -------------
         if (lane == 0) {
-            uint32_t kc = 0, qc = 0;
-            for (int ti = blockIdx.x; ti < ntiles && !*abort_flag; ti += gridDim.x) {
+            uint32_t sb = 0, phb = 0;      // ring position and the parity of its current use
+            bool dead = false;
+            long long w_b = 0;
+            const long long t_begin = clock64();
+            for (int ti = blockIdx.x; ti < ntiles && !dead && !*abort_flag; ti += gridDim.x) {
                 const PfTile t = pf_tile(a, ti);
-                for (int kb = 0; kb < t.nkb; ++kb, ++kc) {
-                    if ((kb & 7) == 0) {
-                        const uint32_t qs = qc & 1u, qph = (qc >> 1) & 1u;
-                        if (!mbar_wait(&q_empty[qs], qph ^ 1u, kPfWaitLimit)) { pf_timeout(a, abort_flag, 1); break; }
-                        mbar_arrive_expect_tx(&q_full[qs], kQBytes);
-                        const int c = kb >> 3;
+                // the smallest box that covers the tile's rows: a ragged tile does not pull 192 rows
+                const CUtensorMap* tm = t.nround <= 64 ? &tmap_b64 : (t.nround <= 128 ? &tmap_b128 : &tmap_b192);
+                const uint32_t rows = t.nround <= 64 ? 64u : (t.nround <= 128 ? 128u : 192u);
+                for (int kb = 0; kb < t.nkb; kb += 2) {   // sb counts pairs of stages
+                    if (!mbar_wait_acc(&empty_b[sb], phb ^ 1u, kPfWaitLimit, w_b)) { pf_timeout(a, abort_flag, 2); dead = true; break; }
+                    mbar_arrive_expect_tx(&full_b[sb], 2u * rows * 128u);
+                    tma_load_2d(sB + (2 * sb) * kBBytes, tm, kb * 64, t.slot0, &full_b[sb]);
+                    tma_load_2d(sB + (2 * sb + 1) * kBBytes, tm, kb * 64 + 64, t.slot0, &full_b[sb]);
+                    if (++sb == (uint32_t)(BS / 2)) { sb = 0; phb ^= 1u; }
+                }
+            }
+            if (a.prof) { long long* p = a.prof + (size_t)blockIdx.x * 16; p[0] = clock64() - t_begin; p[2] = w_b; }
+        }
+    } else if (warp == 2) {
+        // ------------- producer of the int4 chunks (bulk copies), a thread of its own: it runs ahead by
+        // the depth of the int4 ring whatever the state of the activation ring -------------
+        if (lane == 0) {
+            uint32_t qs = 0, qph = 0;
+            bool dead = false;
+            long long w_q = 0;
+            for (int ti = blockIdx.x; ti < ntiles && !dead && !*abort_flag; ti += gridDim.x) {
+                const PfTile t = pf_tile(a, ti);
+                for (int c = 0; c < (t.nkb >> 3); ++c) {
+                    if (!mbar_wait_acc(&q_empty[qs], qph ^ 1u, kPfWaitLimit, w_q)) { pf_timeout(a, abort_flag, 1); dead = true; break; }
+                    mbar_arrive_expect_tx(&q_full[qs], kQBytes);
 #pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            bulk_g2s(sQ + qs * kQBytes + u * kChunkBytes,
-                                     t.chunks + (int64_t)u * t.unit_stride + (int64_t)c * kChunkBytes, kChunkBytes, &q_full[qs]);
-                        ++qc;
-                    }
-                    const uint32_t s = kc % BS, ph = (kc / BS) & 1u;
-                    if (!mbar_wait(&empty_b[s], ph ^ 1u, kPfWaitLimit)) { pf_timeout(a, abort_flag, 2); break; }
-                    // the smallest box that covers the tile's rows: a ragged tile does not pull 256 rows
-                    const CUtensorMap* tm = t.nround <= 64 ? &tmap_b64 : (t.nround <= 128 ? &tmap_b128 : &tmap_b256);
-                    const uint32_t rows = t.nround <= 64 ? 64u : (t.nround <= 128 ? 128u : 256u);
-                    mbar_arrive_expect_tx(&full_b[s], rows * 128u);
-                    tma_load_2d(sB + s * kBBytes, tm, kb * 64, t.slot0, &full_b[s]);
+                    for (int u = 0; u < 4; ++u)
+                        bulk_g2s(sQ + qs * kQBytes + u * kChunkBytes,
+                                 t.chunks + (int64_t)u * t.unit_stride + (int64_t)c * kChunkBytes, kChunkBytes, &q_full[qs]);
+                    if (++qs == (uint32_t)QS) { qs = 0; qph ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------- MMA issuer -------------
-        if (lane == 0) {
-            uint32_t kc = 0, tl = 0;
-            for (int ti = blockIdx.x; ti < ntiles && !*abort_flag; ti += gridDim.x, ++tl) {
-                const PfTile t = pf_tile(a, ti);
-                const uint32_t buf = tl & 1u;
-                if (!mbar_wait(&acc_empty[buf], ((tl >> 1) & 1u) ^ 1u, kPfWaitLimit)) { pf_timeout(a, abort_flag, 3); break; }
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * 256u;
-                const uint32_t idesc = make_idesc((uint32_t)t.nround);
-                bool dead = false;
-                for (int kb = 0; kb < t.nkb; ++kb, ++kc) {
-                    const uint32_t s = kc % AS, ph = (kc / AS) & 1u;
-                    const uint32_t sb = kc % BS, phb = (kc / BS) & 1u;
-                    if (!mbar_wait(&full_a[s], ph, kPfWaitLimit) || !mbar_wait(&full_b[sb], phb, kPfWaitLimit)) {
-                        pf_timeout(a, abort_flag, 4); dead = true; break;
-                    }
-                    tc_fence_after();
-                    const uint64_t ad = make_desc_sw128(smem_u32(sA + s * kABytes));
-                    const uint64_t bd = make_desc_sw128(smem_u32(sB + sb * kBBytes));
+        // The tensor pipe idles whenever this warp's instruction stream is not at a tcgen05.mma, so the
+        // loop is kept short: all 32 lanes run it (warp-uniform values stay in uniform registers; one
+        // elected lane issues the tcgen05 instructions), the four ring stages are unrolled (a tile has a
+        // multiple of eight k-blocks, so every tile starts at stage 0 and stage numbers are constants),
+        // and whether the NEXT stage is full is asked (non-blocking) before this stage's MMAs are issued
+        // and looked at after them.
+        const bool leader = elect_one();
+        uint32_t pha = 0, tl = 0, sb = 0, phb = 0;
+        bool dead = false;
+        long long w_acc = 0, w_a = 0, w_bf = 0;
+        const long long t_begin = clock64();
+        const uint32_t a_tmem0 = tmem_base + (uint32_t)kACol0;
+        const uint64_t bd0 = make_desc_sw128(smem_u32(sB));
+        uint32_t ready_a = mbar_test_wait(&full[0], 0), ready_b = mbar_test_wait(&full_b[0], 0);
+        for (int ti = blockIdx.x; ti < ntiles && !dead && !*abort_flag; ti += gridDim.x, ++tl) {
+            const PfTile t = pf_tile(a, ti);
+            const uint32_t buf = tl & 1u;
+            if (!mbar_wait_acc(&acc_empty[buf], ((tl >> 1) & 1u) ^ 1u, kPfWaitLimit, w_acc)) { pf_timeout(a, abort_flag, 3); break; }
+            const uint32_t d_tmem = tmem_base + buf * (uint32_t)kBN;
+            const uint32_t idesc = make_idesc((uint32_t)t.nround);
+            uint32_t acc = 0;    // the tile's first MMA overwrites the accumulator
+            for (int kb = 0; kb < t.nkb && !dead; kb += kAStages) {
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4)
-                        tc_mma_f16(d_tmem, ad + (uint64_t)(k4 * 2), bd + (uint64_t)(k4 * 2), idesc, (kb | k4) ? 1u : 0u);
-                    tc_commit(&empty[s]);
-                    tc_commit(&empty_b[sb]);
+                for (int pr = 0; pr < kAStages / 2; ++pr) {   // pair of ring stages 2 pr, 2 pr + 1; sb counts activation pairs
+                    if (!ready_a && !mbar_wait_acc(&full[pr], pha, kPfWaitLimit, w_a)) { pf_timeout(a, abort_flag, 4); dead = true; break; }
+                    if (!ready_b && !mbar_wait_acc(&full_b[sb], phb, kPfWaitLimit, w_bf)) { pf_timeout(a, abort_flag, 8); dead = true; break; }
+                    tc_fence_after();
+                    const uint32_t sbn = sb + 1 == (uint32_t)(BS / 2) ? 0u : sb + 1, phn = sb + 1 == (uint32_t)(BS / 2) ? phb ^ 1u : phb;
+                    ready_a = mbar_test_wait(&full[(pr + 1) % (kAStages / 2)], pr + 1 == kAStages / 2 ? pha ^ 1u : pha);
+                    ready_b = mbar_test_wait(&full_b[sbn], phn);
+                    if (leader) {
+                        const uint64_t bd = bd0 + (uint64_t)(sb * (uint32_t)(2 * (kBBytes >> 4)));
+#pragma unroll
+                        for (int k8 = 0; k8 < 8; ++k8)
+                            tc_mma_f16_ts(d_tmem, a_tmem0 + (uint32_t)(pr * 64 + k8 * 8),
+                                          bd + (uint64_t)((k8 >> 2) * (kBBytes >> 4) + (k8 & 3) * 2), idesc, k8 ? 1u : acc);
+                        tc_commit(&empty[pr]);
+                        tc_commit(&empty_b[sb]);
+                    }
+                    acc = 1u;
+                    sb = sbn; phb = phn;
                 }
-                if (dead) break;
-                tc_commit(&acc_full[buf]);
+                pha ^= 1u;
             }
+            if (dead) break;
+            if (leader) tc_commit(&acc_full[buf]);
         }
+        if (a.prof && lane == 0) { long long* p = a.prof + (size_t)blockIdx.x * 16; p[3] = w_acc; p[4] = w_a; p[1] = w_bf; p[9] = clock64() - t_begin; }
     } else if (warp >= 4 && warp < 8) {
         // ------------- epilogue (warp % 4 selects the TMEM lane quarter) -------------
         const int q = warp & 3;
         uint32_t tl = 0;
+        long long w_full = 0, w_ld = 0;
+        const long long t_begin = clock64();
         for (int ti = blockIdx.x; ti < ntiles; ti += gridDim.x, ++tl) {
             const PfTile t = pf_tile(a, ti);
             const uint32_t buf = tl & 1u;
-            if (*abort_flag || !mbar_wait(&acc_full[buf], (tl >> 1) & 1u, kPfWaitLimit)) {
+            if (*abort_flag || !mbar_wait_acc(&acc_full[buf], (tl >> 1) & 1u, kPfWaitLimit, w_full)) {
                 if (!*abort_flag) pf_timeout(a, abort_flag, 5);
                 break;
             }
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256u;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)kBN;
+            // A lane holds ONE weight row (feature) for 32 tokens, but memory wants a token's features side
+            // by side: the chunk goes through this warp's 2 KiB of shared memory as [token][feature], and
+            // comes back as 16-byte vectors - eight features of one token per lane, so a store instruction
+            // writes 512 bytes instead of 32 two-byte pieces.
+            __half* stg = reinterpret_cast<__half*>(sE + q * kEpiWarpBytes);
             for (int c0 = 0; c0 < t.nround; c0 += 32) {
                 uint32_t r[32];
+                const long long t_l = a.prof ? clock64() : 0;
                 tmem_ld32(taddr + (uint32_t)c0, r);
                 tmem_ld_wait();
+                if (a.prof) w_ld += clock64() - t_l;
                 if (GU) {
-                    // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows
-                    const int feat = t.rb * 64 + q * 16 + (lane & 15);
+                    // lanes 0..15 hold gate rows, lanes 16..31 the matching up rows: 16 features per token
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
                         const float v0 = __uint_as_float(r[j]), v1 = __uint_as_float(r[j + 1]);
@@ -280,93 +375,121 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
                         const float recv = __shfl_xor_sync(0xffffffffu, send, 16);
                         const float g = (lane < 16) ? v0 : recv;
                         const float u = (lane < 16) ? recv : v1;
-                        const int n = c0 + j + ((lane < 16) ? 0 : 1);
-                        if (n < t.ntok)
-                            a.hbuf[(int64_t)(t.slot0 + n) * a.ldh + feat] = __float2half_rn(__fmul_rn(silu_ref(g), u));
+                        // token j (lanes 0..15) and token j + 1 (lanes 16..31), 32 bytes each, back to back
+                        stg[j * 16 + lane] = sat_half(__fmul_rn(silu_ref(g), u));
+                    }
+                    __syncwarp();
+                    const int feat = t.rb * 64 + q * 16 + (lane & 1) * 8;
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const int n = c0 + k * 16 + (lane >> 1);
+                        const uint4 v = *reinterpret_cast<const uint4*>(stg + (k * 16 + (lane >> 1)) * 16 + (lane & 1) * 8);
+                        if (n < t.ntok) *reinterpret_cast<uint4*>(a.hbuf + (int64_t)(t.slot0 + n) * a.ldh + feat) = v;
                     }
                 } else {
-                    const int feat = t.rb * 128 + q * 32 + lane;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int n = c0 + j;
+                    for (int j = 0; j < 32; ++j) stg[j * 32 + lane] = sat_half(__uint_as_float(r[j]));
+                    __syncwarp();
+                    const int feat = t.rb * 128 + q * 32 + (lane & 3) * 8;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int n = c0 + k * 8 + (lane >> 2);
+                        const uint4 v = *reinterpret_cast<const uint4*>(stg + (k * 8 + (lane >> 2)) * 32 + (lane & 3) * 8);
                         if (n < t.ntok) {
                             __half* yrow = a.ydst ? a.ydst[t.slot0 + n] : a.ybuf + (int64_t)(t.slot0 + n) * a.H;
-                            yrow[feat] = __float2half_rn(__uint_as_float(r[j]));
+                            *reinterpret_cast<uint4*>(yrow + feat) = v;
                         }
                     }
                 }
+                __syncwarp();   // the staging area is rewritten by the next chunk
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
+        if (a.prof && q == 0 && lane == 0) { long long* p = a.prof + (size_t)blockIdx.x * 16; p[10] = w_full; p[11] = w_ld; p[12] = clock64() - t_begin; }
     } else if (warp >= 8) {
-        // ------------- dequant: int4 chunk pieces -> swizzled fp16 A tile -------------
-        // Two groups of four warps take alternate k-blocks, so each group has two MMA periods
-        // per k-block; a thread owns one row of the 128-row tile (both 32-column halves).
-        const int d = tid - 256;                       // 0..255
-        const int grp = d >> 7;                        // 0: even k-blocks, 1: odd
+        // ------------- dequant: int4 chunk pieces -> fp16 rows of the A ring in TMEM -------------
+        // Four groups of four warps; group g unpacks the k-blocks kb with kb % 4 == g into ring stage g
+        // (a tile has a multiple of eight k-blocks, so that holds across tiles).  A thread owns one row
+        // of the 128-row tile = one TMEM lane (warp % 4 is the lane quarter it may access).  The work of a
+        // k-block is a latency chain (shared-memory loads, ~100 ALU operations, the TMEM store), so it
+        // takes this many warps in flight to produce a k-block as fast as the tensor core consumes one.
+        const int d = tid - 256;
+        const int grp = d >> 7;                        // ring stage and k-block residue of this group
         const int R = d & 127;                         // row of the tile (= TMEM lane)
         const int uu = R >> 5, m = (R >> 4) & 1, h = (R >> 3) & 1, g = R & 7;
-        uint32_t kc = grp, qc = 0;
+        const uint32_t a_st = tmem_base + ((uint32_t)(R & ~31) << 16) + (uint32_t)kACol0 + (uint32_t)grp * 32u;
+        uint32_t pha = 0;                              // parity of the stage's current use
+        uint32_t qs = 0, qph = 0;
         bool dead = false;
+        long long w_qf = 0, w_ea = 0, w_alu = 0, w_pub = 0, w_st = 0;
+        const long long t_begin = clock64();
         for (int ti = blockIdx.x; ti < ntiles && !dead; ti += gridDim.x) {
             const PfTile t = pf_tile(a, ti);
-            uint32_t qs = 0;
-            for (int kb = grp; kb < t.nkb; kb += 2, kc += 2) {
+            for (int kb = grp; kb < t.nkb; kb += kDqGroups) {
                 const int kb8 = kb & 7;
                 if (kb8 == grp) {
-                    qs = qc & 1u;
-                    if (*abort_flag || !mbar_wait(&q_full[qs], (qc >> 1) & 1u, kPfWaitLimit)) {
+                    if (*abort_flag || !mbar_wait_acc(&q_full[qs], qph, kPfWaitLimit, w_qf)) {
                         if (!*abort_flag) pf_timeout(a, abort_flag, 6);
                         dead = true; break;
                     }
-                    ++qc;
                 }
-                const int ks = kb8 >> 1, tq0 = grp << 1;
+                const long long t0 = a.prof ? clock64() : 0;
+                const int ks = kb8 >> 1, tq0 = (kb8 & 1) << 1;
                 const uint8_t* chunk = sQ + qs * kQBytes + uu * kChunkBytes;
                 const uint4* piece = reinterpret_cast<const uint4*>(chunk + (ks * 2 + m) * 1024 + h * 512 + (g * 4 + tq0) * 16);
-                // A row's two 16-byte pieces sit 64 bytes from the next row's, so eight lanes reading
-                // "their first piece" fall on two bank groups (4-way conflict).  Rows 2,3,6,7 read
-                // their second piece first: four bank groups per load, 2-way - the best this layout
-                // allows, since one k-block touches only half of the bank groups.
-                const int swp = (g >> 1) & 1;
-                const uint4 wa = piece[swp], wb = piece[swp ^ 1];
-                const uint4 wv0 = swp ? wb : wa, wv1 = swp ? wa : wb;
+                const uint4 wv0 = piece[0], wv1 = piece[1];
                 const __half sc = reinterpret_cast<const __half*>(chunk + kChunkWeightBytes)[(ks * 2 + m) * 16 + g + 8 * h];
                 const __half2 s2 = __half2half2(sc);
                 const uint32_t wq[8] = {wv0.x, wv0.y, wv0.z, wv0.w, wv1.x, wv1.y, wv1.z, wv1.w};
-                uint4 dq[8];   // unpacked in registers first: only the stores need the stage to be free
+                uint4 dq[8];   // unpacked in registers first: only the store needs the stage to be free
 #pragma unroll
                 for (int c = 0; c < 8; ++c) dq[c] = dequant8(wq[c], s2);
-                const uint32_t s = kc % AS, ph = (kc / AS) & 1u;
-                if (!mbar_wait(&empty[s], ph ^ 1u, kPfWaitLimit)) { pf_timeout(a, abort_flag, 7); dead = true; break; }
-                uint8_t* arow = sA + s * kABytes + (R >> 3) * 1024 + g * 128;
-#pragma unroll
-                for (int c = 0; c < 8; ++c)             // c = 16-byte piece of the 128-byte row
-                    *reinterpret_cast<uint4*>(arow + ((c ^ g) << 4)) = dq[c];
-                fence_proxy_async();   // this thread's stores, visible to the tensor core's reads
+                long long t1 = 0;
+                if (a.prof) { t1 = clock64(); w_alu += t1 - t0 + (long long)(dq[0].x & 0u); }
+                // unpacked in registers before the wait: only the store needs the stage to be free
+                if (!mbar_wait_acc(&empty[grp >> 1], pha ^ 1u, kPfWaitLimit, w_ea)) { pf_timeout(a, abort_flag, 7); dead = true; break; }
+                const long long t3 = a.prof ? clock64() : 0;
+                tc_fence_after();      // the MMAs that read this stage (their commit released it) before the store
+                tmem_st32(a_st, dq);
+                tmem_st_wait();
+                tc_fence_before();     // the store before the MMA thread's reads, across the arrive below
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&full_a[s]);
-                if (kb8 >= 6) {        // this group's last k-block of the int4 super-stage
+                if (lane == 0) mbar_arrive(&full[grp >> 1]);
+                if (a.prof) w_st += clock64() - t3;
+                pha ^= 1u;
+                if (kb8 >= 4) {        // this group's last k-block of the int4 stage; the store above took the
+                                       // unpacked words, so every load from the stage has returned
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&q_empty[qs]);
+                    if (++qs == (uint32_t)QS) { qs = 0; qph ^= 1u; }
                 }
             }
         }
+        if (a.prof && d == 0) { long long* p = a.prof + (size_t)blockIdx.x * 16; p[6] = w_qf; p[7] = w_ea; p[5] = w_alu; p[8] = w_pub; p[13] = w_st; p[14] = clock64() - t_begin; }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
-// ---- tile list ------------------------------------------------------------------------
-// tiles[0] = count; then int4 {expert (E = shared), first slot, tokens (<= 256), row block}.
-// Row block varies fastest so CTAs running together share the token tile through L2.
+// ---- token-tile list ------------------------------------------------------------------
+// tiles[0] = routed token tiles, tiles[1] = shared-expert token tiles, then int4 {expert
+// (shared_marker = shared), first slot, tokens (<= 192), 0} per token tile, routed ones first.  Both GEMM kernels
+// read the one list (they differ in the row blocks per token tile).  An expert's rows are cut into
+// the fewest tiles of at most 192 rows, of equal size up to one row: a 200-row expert becomes
+// 100 + 100, not 192 + 8 (a tile pays a full pass of weight unpacking however few rows it has).
+__device__ __forceinline__ int4 token_tile(int expert, int beg, int cnt, int nt, int j) {
+    const int base = cnt / nt, rem = cnt - base * nt;
+    return make_int4(expert, beg + j * base + min(j, rem), base + (j < rem ? 1 : 0), 0);
+}
+
 __global__ void __launch_bounds__(1024)
-tile_build_kernel(const int* __restrict__ expert_offsets, int E, int n, int P, int has_shared,
-                  int row_blocks, int row_blocks_s, int* __restrict__ tiles) {
+tile_list_kernel(const int* __restrict__ expert_offsets, int E, int shared_marker, int n_shared, int shared_slot0,
+                 int* __restrict__ tiles) {
     __shared__ int wsum[32];
+    __shared__ int routed_total;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     int cnt = 0, beg = 0;
     if (tid < E) { beg = expert_offsets[tid]; cnt = expert_offsets[tid + 1] - beg; }
@@ -379,7 +502,6 @@ tile_build_kernel(const int* __restrict__ expert_offsets, int E, int n, int P, i
     }
     if (lane == 31) wsum[w] = incl;
     __syncthreads();
-    int total_routed = 0;
     if (w == 0) {
         const int s = wsum[lane];
         int si = s;
@@ -389,41 +511,21 @@ tile_build_kernel(const int* __restrict__ expert_offsets, int E, int n, int P, i
             if (lane >= o) si += u;
         }
         wsum[lane] = si - s;
-        total_routed = __shfl_sync(0xffffffffu, si, 31);
-        const int nsh = has_shared ? (n + kBN - 1) / kBN : 0;
-        if (lane == 0) { tiles[0] = total_routed * row_blocks + nsh * row_blocks_s; tiles[1] = tiles[2] = tiles[3] = 0; }
+        if (lane == 31) routed_total = si;
     }
     __syncthreads();
+    const int nsh = (n_shared + kBN - 1) / kBN;
+    if (tid == 0) { tiles[0] = routed_total; tiles[1] = nsh; tiles[2] = tiles[3] = 0; }
     const int base = incl - ng + wsum[w];
     int4* out = reinterpret_cast<int4*>(tiles + kTileHeader);
-    for (int j = 0; j < ng; ++j)
-        for (int rb = 0; rb < row_blocks; ++rb)
-            out[(int64_t)(base + j) * row_blocks + rb] = make_int4(tid, beg + j * kBN, min(kBN, cnt - j * kBN), rb);
+    for (int j = 0; j < ng; ++j) out[base + j] = token_tile(tid, beg, cnt, ng, j);
+    for (int j = tid; j < nsh; j += 1024) out[routed_total + j] = token_tile(shared_marker, shared_slot0, n_shared, nsh, j);
 }
 
-// Shared-expert tiles appended after the routed tiles (separate tiny kernel keeps the scan simple).
-__global__ void tile_append_shared_kernel(const int* __restrict__ expert_offsets, int E, int n, int P,
-                                          int row_blocks, int row_blocks_s, int* __restrict__ tiles) {
-    // number of routed token tiles
-    __shared__ int routed_tiles;
-    if (threadIdx.x == 0) {
-        int tot = 0;
-        for (int e = 0; e < E; ++e) tot += (expert_offsets[e + 1] - expert_offsets[e] + kBN - 1) / kBN;
-        routed_tiles = tot;
-    }
-    __syncthreads();
-    const int nsh = (n + kBN - 1) / kBN;
-    int4* out = reinterpret_cast<int4*>(tiles + kTileHeader) + (int64_t)routed_tiles * row_blocks;
-    for (int i = threadIdx.x; i < nsh * row_blocks_s; i += blockDim.x) {
-        const int j = i / row_blocks_s, rb = i - j * row_blocks_s;
-        out[i] = make_int4(E, P + j * kBN, min(kBN, n - j * kBN), rb);
-    }
-}
-
-// Activations into expert order, bf16 -> fp16 (natural feature order for TMA):
-// xs[r] = x[sorted_tok[r]] for r < P, xs[P + t] = x[t].
+// Activations into expert order (natural feature order for TMA), from the fp16 copy the
+// router-logits launch left behind: xs[r] = xh[sorted_tok[r]] for r < P, xs[P + t] = xh[t].
 __global__ void __launch_bounds__(256)
-gather_x_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sorted_tok, int P,
+gather_x_kernel(const __half* __restrict__ xh, const int* __restrict__ sorted_tok, int P,
                 int n, int H, int with_shared, __half* __restrict__ xs) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int gpr = H >> 3;
@@ -432,27 +534,16 @@ gather_x_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ sor
     const int64_t r = i / gpr;
     const int grp = (int)(i - r * gpr);
     const int64_t src = r < P ? sorted_tok[r] : r - P;
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + src * H) + grp);
-    const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&v);
-    uint4 o;
-    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        float2 f = __bfloat1622float2(bp[q]);
-        f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
-        f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
-        const __half2 hh = __floats2half2_rn(f.x, f.y);
-        op[q] = *reinterpret_cast<const uint32_t*>(&hh);
-    }
-    reinterpret_cast<uint4*>(xs + r * H)[grp] = o;
+    reinterpret_cast<uint4*>(xs + r * H)[grp] = __ldg(reinterpret_cast<const uint4*>(xh + src * H) + grp);
 }
 
 // Deterministic combine over fp16 per-slot rows (same order as combine_kernel of the decode
-// path: slots k = 0..topk-1, then the shared expert).
+// path: slots k = 0..topk-1, then the shared expert); with `residual` the layer's pre-norm
+// residual add rides the same pass (out = residual + sum).
 __global__ void __launch_bounds__(256)
 combine_h_kernel(const __half* __restrict__ ybuf, const int* __restrict__ slot_pos,
                  const float* __restrict__ topk_w, int n, int topk, int H, int P, int has_shared,
-                 float* __restrict__ out) {
+                 const float* residual, float* out) {
     const int t = blockIdx.y;
     const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
     if (c8 >= (H >> 3)) return;
@@ -473,6 +564,13 @@ combine_h_kernel(const __half* __restrict__ ybuf, const int* __restrict__ slot_p
         }
     }
     float4* o = reinterpret_cast<float4*>(out + (int64_t)t * H + (c8 << 3));
+    if (residual) {   // hidden + mlp, the layer's sum complete before the add (src/model_gpu.cpp:1502 of the reference)
+        const float4* rp = reinterpret_cast<const float4*>(residual + (int64_t)t * H + (c8 << 3));
+        const float4 r0 = rp[0], r1 = rp[1];   // out may be the residual itself: read before the stores
+        o[0] = make_float4(__fadd_rn(r0.x, acc[0]), __fadd_rn(r0.y, acc[1]), __fadd_rn(r0.z, acc[2]), __fadd_rn(r0.w, acc[3]));
+        o[1] = make_float4(__fadd_rn(r1.x, acc[4]), __fadd_rn(r1.y, acc[5]), __fadd_rn(r1.z, acc[6]), __fadd_rn(r1.w, acc[7]));
+        return;
+    }
     o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
@@ -494,7 +592,7 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// fp16 [rows, cols] row-major; box = 64 columns x kBN rows, 128-byte swizzle.
+// fp16 [rows, cols] row-major; box = 64 columns x box_rows rows, 128-byte swizzle.
 int make_tmap(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return GSB_ERR_CUDA;
@@ -508,71 +606,60 @@ int make_tmap(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int6
     return r == CUDA_SUCCESS ? GSB_OK : GSB_ERR_CUDA;
 }
 
-// Tile list holding only shared-expert tiles over n token rows starting at row 0.
-__global__ void tile_shared_only_kernel(int E_marker, int n, int row_blocks, int* __restrict__ tiles) {
-    const int nsh = (n + kBN - 1) / kBN;
-    if (threadIdx.x == 0) { tiles[0] = nsh * row_blocks; tiles[1] = tiles[2] = tiles[3] = 0; }
-    int4* out = reinterpret_cast<int4*>(tiles + kTileHeader);
-    for (int i = threadIdx.x; i < nsh * row_blocks; i += blockDim.x) {
-        const int j = i / row_blocks, rb = i - j * row_blocks;
-        out[i] = make_int4(E_marker, j * kBN, min(kBN, n - j * kBN), rb);
-    }
-}
-
-constexpr size_t pf_smem(int as, int bs) { return (size_t)as * kABytes + (size_t)bs * kBBytes + 2 * kQBytes + 256; }
+constexpr size_t pf_smem(int qs) { return (size_t)kBStages * kBBytes + (size_t)qs * kQBytes + 4 * kEpiWarpBytes + 256; }
+constexpr int kPfQStages = 2;
+static_assert(pf_smem(kPfQStages) <= 227 * 1024, "stages exceed the shared memory of an SM");
 
 }  // namespace
 
-size_t prefill_tile_bytes(int n, int topk, int E, int H, int I) {
+size_t prefill_tile_bytes(int n, int topk, int E) {
     const size_t P = (size_t)n * topk;
     const size_t tok_tiles = (size_t)E + P / kBN + (size_t)n / kBN + 2;
-    const size_t rbmax = (size_t)((H / 128 > I / 64) ? H / 128 : I / 64);
-    return (kTileHeader + 4 * tok_tiles * rbmax) * sizeof(int);
+    return (kTileHeader + 4 * tok_tiles) * sizeof(int);
 }
 
-template <int AS, int BS>
-static int launch_pair(const PrefillKArgs& g, const PrefillKArgs& w, const CUtensorMap* tm_x, const CUtensorMap* tm_h,
-                       int sm_count, cudaStream_t s, cudaEvent_t ev_mid) {
-    const size_t smem = pf_smem(AS, BS);
-    if (smem > 227 * 1024) return GSB_ERR_UNSUPPORTED;
-    if (cudaFuncSetAttribute(prefill_gemm_kernel<true, AS, BS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-        cudaFuncSetAttribute(prefill_gemm_kernel<false, AS, BS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return GSB_ERR_CUDA;
-    prefill_gemm_kernel<true, AS, BS><<<sm_count, kPfThreads, smem, s>>>(g, tm_x[0], tm_x[1], tm_x[2]);
-    if (ev_mid) cudaEventRecord(ev_mid, s);
-    prefill_gemm_kernel<false, AS, BS><<<sm_count, kPfThreads, smem, s>>>(w, tm_h[0], tm_h[1], tm_h[2]);
-    return launch_status();
-}
+// optional wait-cycle profile of the two GEMM kernels (see gsb_prefill_wait_profile)
+static long long* g_pf_prof = nullptr;
 
 static int run_gemm_pair(const PrefillKArgs& g_in, const PrefillKArgs& w_in, const void* xbase, int64_t xrows,
                          int H, const void* hbase, int64_t hrows, int ldh, int sm_count, cudaStream_t s,
                          cudaEvent_t ev_mid) {
     CUtensorMap tm_x[3], tm_h[3];
-    const int boxes[3] = {64, 128, 256};
+    const int boxes[3] = {64, 128, kBN};
     for (int i = 0; i < 3; ++i) {
         int st = make_tmap(&tm_x[i], xbase, xrows, H, H, boxes[i]);
         if (st) return st;
         st = make_tmap(&tm_h[i], hbase, hrows, ldh, ldh, boxes[i]);
         if (st) return st;
     }
-    // two weight stages and four activation stages measured best on the skewed GLM-scale layer
-    return launch_pair<2, 4>(g_in, w_in, tm_x, tm_h, sm_count, s, ev_mid);
+    PrefillKArgs g = g_in, w = w_in;
+    g.prof = g_pf_prof;
+    w.prof = g_pf_prof ? g_pf_prof + 16 * 1024 : nullptr;
+    constexpr size_t smem = pf_smem(kPfQStages);
+    if (cudaFuncSetAttribute(prefill_gemm_kernel<true, kPfQStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_gemm_kernel<false, kPfQStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return GSB_ERR_CUDA;
+    prefill_gemm_kernel<true, kPfQStages><<<sm_count, kPfThreads, smem, s>>>(g, tm_x[0], tm_x[1], tm_x[2]);
+    if (ev_mid) cudaEventRecord(ev_mid, s);
+    prefill_gemm_kernel<false, kPfQStages><<<sm_count, kPfThreads, smem, s>>>(w, tm_h[0], tm_h[1], tm_h[2]);
+    return launch_status();
 }
 
 // Expert parallel, shared expert: this GPU's own tokens through the shared expert, output rows
 // into y_shared [n, H] (the tail of the local per-slot row buffer).
 int launch_prefill_ep_shared(const PrefillEpArgs& d, cudaStream_t s) {
     if (d.Is <= 0) return GSB_OK;
-    gather_x_kernel<<<(unsigned)(((int64_t)d.n * (d.H >> 3) + 255) / 256), 256, 0, s>>>(d.x, nullptr, 0, d.n, d.H, 1, d.xs_local);
-    tile_shared_only_kernel<<<1, 256, 0, s>>>(d.El, d.n, d.Is / 64, d.tiles_sh_gu);
-    tile_shared_only_kernel<<<1, 256, 0, s>>>(d.El, d.n, d.H / 128, d.tiles_sh_dn);
+    int st0 = launch_xprep(d.x, d.xs_local, d.n, d.H, 1, s);   // this GPU's own rows, already in order
+    if (st0) return st0;
+    tile_list_kernel<<<1, 1024, 0, s>>>(nullptr, 0, d.El, d.n, 0, d.tiles_sh);
     PrefillKArgs g{};
     g.packed = nullptr; g.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_gate_up_packed);
-    g.tiles = d.tiles_sh_gu; g.K = d.H; g.Ks = d.H; g.units = d.I / 16; g.units_s = d.Is / 16; g.E = d.El;
+    g.tiles = d.tiles_sh; g.RB = 1; g.RBs = d.Is / 64;
+    g.K = d.H; g.Ks = d.H; g.units = d.I / 16; g.units_s = d.Is / 16; g.E = d.El;
     g.hbuf = d.hbuf_sh; g.ldh = d.Is; g.ybuf = nullptr; g.H = d.H; g.ydst = nullptr; g.status = d.status;
     PrefillKArgs w = g;
     w.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_down_packed);
-    w.tiles = d.tiles_sh_dn; w.K = d.I; w.Ks = d.Is; w.units = d.H / 32; w.units_s = d.H / 32;
+    w.RBs = d.H / 128; w.K = d.I; w.Ks = d.Is; w.units = d.H / 32; w.units_s = d.H / 32;
     w.hbuf = nullptr; w.ybuf = d.y_shared;
     return run_gemm_pair(g, w, d.xs_local, d.n, d.H, d.hbuf_sh, d.n, d.Is, d.sm_count, s, nullptr);
 }
@@ -581,24 +668,24 @@ int launch_prefill_ep_shared(const PrefillEpArgs& d, cudaStream_t s) {
 // recv_x) through its resident experts; the down kernel's epilogue stores every output row
 // straight to the GPU that owns the token (ydst) - compute and the return all-to-all in one kernel.
 int launch_prefill_ep_routed(const PrefillEpArgs& d, cudaStream_t s) {
-    tile_build_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, 0, 0, 0, d.I / 64, 1, d.tiles_gu);
-    tile_build_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, 0, 0, 0, d.H / 128, 1, d.tiles_dn);
+    tile_list_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, d.El, 0, 0, d.tiles);
     PrefillKArgs g{};
     g.packed = reinterpret_cast<const uint8_t*>(d.gate_up_packed); g.shared_packed = nullptr;
-    g.tiles = d.tiles_gu; g.K = d.H; g.Ks = d.H; g.units = d.I / 16; g.units_s = 1; g.E = d.El;
+    g.tiles = d.tiles; g.RB = d.I / 64; g.RBs = 1;
+    g.K = d.H; g.Ks = d.H; g.units = d.I / 16; g.units_s = 1; g.E = d.El;
     g.hbuf = d.hbuf; g.ldh = d.I; g.ybuf = nullptr; g.H = d.H; g.ydst = nullptr; g.status = d.status;
     PrefillKArgs w = g;
     w.packed = reinterpret_cast<const uint8_t*>(d.down_packed);
-    w.tiles = d.tiles_dn; w.K = d.I; w.Ks = d.I; w.units = d.H / 32; w.units_s = 1;
+    w.RB = d.H / 128; w.K = d.I; w.Ks = d.I; w.units = d.H / 32; w.units_s = 1;
     w.hbuf = nullptr; w.ybuf = nullptr; w.ydst = d.ydst;
     return run_gemm_pair(g, w, d.recv_x, d.recv_cap, d.H, d.hbuf, d.recv_cap, d.I, d.sm_count, s, nullptr);
 }
 
 int launch_combine_h(const __half* ybuf, const int* slot_pos, const float* topk_w, int n, int topk, int H,
-                     int P, int has_shared, float* out, cudaStream_t s) {
+                     int P, int has_shared, const float* residual, float* out, cudaStream_t s) {
     if (n == 0) return GSB_OK;
     dim3 cgrid((unsigned)(((H >> 3) + 255) / 256), (unsigned)n);
-    combine_h_kernel<<<cgrid, 256, 0, s>>>(ybuf, slot_pos, topk_w, n, topk, H, P, has_shared, out);
+    combine_h_kernel<<<cgrid, 256, 0, s>>>(ybuf, slot_pos, topk_w, n, topk, H, P, has_shared, residual, out);
     return launch_status();
 }
 
@@ -610,32 +697,37 @@ int launch_prefill_layer(const PrefillArgs& d, cudaStream_t s) {
     if (cudaMemsetAsync(d.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
     const int64_t rows = (int64_t)P + (shared ? d.n : 0);
 
-    gather_x_kernel<<<(unsigned)((rows * (d.H >> 3) + 255) / 256), 256, 0, s>>>(d.x, d.sorted_tok, P, d.n, d.H,
+    if (!d.xh_ready) {
+        const int st0 = launch_xprep(d.x, d.xh, d.n, d.H, 1, s);
+        if (st0) return st0;
+    }
+    gather_x_kernel<<<(unsigned)((rows * (d.H >> 3) + 255) / 256), 256, 0, s>>>(d.xh, d.sorted_tok, P, d.n, d.H,
                                                                               shared ? 1 : 0, d.xs);
-    // gate/up tiles: row block = 4 units of (16 gate + 16 up) rows = 64 features
-    tile_build_kernel<<<1, 1024, 0, s>>>(d.expert_offsets, d.E, d.n, P, shared ? 1 : 0, d.I / 64, d.Is / 64, d.tiles_gu);
-    if (shared) tile_append_shared_kernel<<<1, 256, 0, s>>>(d.expert_offsets, d.E, d.n, P, d.I / 64, d.Is / 64, d.tiles_gu);
-    tile_build_kernel<<<1, 1024, 0, s>>>(d.expert_offsets, d.E, d.n, P, shared ? 1 : 0, d.H / 128, d.H / 128, d.tiles_dn);
-    if (shared) tile_append_shared_kernel<<<1, 256, 0, s>>>(d.expert_offsets, d.E, d.n, P, d.H / 128, d.H / 128, d.tiles_dn);
+    tile_list_kernel<<<1, 1024, 0, s>>>(d.expert_offsets, d.E, d.E, shared ? d.n : 0, P, d.tiles);
     if (d.ev_prep) cudaEventRecord(d.ev_prep, s);
 
     PrefillKArgs g{};
     g.packed = reinterpret_cast<const uint8_t*>(d.gate_up_packed);
     g.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_gate_up_packed);
-    g.tiles = d.tiles_gu; g.K = d.H; g.Ks = d.H; g.units = d.I / 16; g.units_s = d.Is / 16; g.E = d.E;
+    // gate/up row block = 4 units of (16 gate + 16 up) rows = 64 features; down row block = 128 rows
+    g.tiles = d.tiles; g.RB = d.I / 64; g.RBs = shared ? d.Is / 64 : 1;
+    g.K = d.H; g.Ks = d.H; g.units = d.I / 16; g.units_s = d.Is / 16; g.E = d.E;
     g.hbuf = d.hbuf; g.ldh = imax; g.ybuf = nullptr; g.H = d.H; g.status = d.status;
     PrefillKArgs w = g;
     w.packed = reinterpret_cast<const uint8_t*>(d.down_packed);
     w.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_down_packed);
-    w.tiles = d.tiles_dn; w.K = d.I; w.Ks = shared ? d.Is : d.I; w.units = d.H / 32; w.units_s = d.H / 32;
+    w.RB = d.H / 128; w.RBs = d.H / 128;
+    w.K = d.I; w.Ks = shared ? d.Is : d.I; w.units = d.H / 32; w.units_s = d.H / 32;
     w.hbuf = nullptr; w.ybuf = d.ybuf;
     const int st = run_gemm_pair(g, w, d.xs, rows, d.H, d.hbuf, rows, imax, d.sm_count, s, d.ev_gate_up);
     if (st) return st;
     if (d.ev_down) cudaEventRecord(d.ev_down, s);
-
-    dim3 cgrid((unsigned)(((d.H >> 3) + 255) / 256), (unsigned)d.n);
-    combine_h_kernel<<<cgrid, 256, 0, s>>>(d.ybuf, d.slot_pos, d.topk_w, d.n, d.topk, d.H, P, shared ? 1 : 0, d.out);
-    return launch_status();
+    return launch_combine_h(d.ybuf, d.slot_pos, d.topk_w, d.n, d.topk, d.H, P, shared ? 1 : 0, d.residual, d.out, s);
 }
 
 }  // namespace gsb
+
+extern "C" int gsb_prefill_wait_profile(long long* device_buffer) {
+    gsb::g_pf_prof = device_buffer;
+    return GSB_OK;
+}

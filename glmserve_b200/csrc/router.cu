@@ -136,21 +136,52 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
             : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, int NT, int KSPLIT>
+// NORM: the activations are bf16(rmsnorm(hidden)) of an fp32 hidden state (the layer's pre-norm,
+// src/model_gpu.cpp:1430 of the reference, folded into this launch): every block first takes the
+// inverse RMS of its token rows - the same thread-strided double sums in the same order as
+// rmsnorm_kernel, so the normalised values are the bits a separate norm pass would produce - and
+// normalises and rounds to bf16 as it loads.
+template <int MT, int NT, int KSPLIT, bool NORM>
 __global__ void __launch_bounds__(256)
 router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr,
                          int n, int H, int E, float* __restrict__ logits, float* __restrict__ scores,
-                         __half* __restrict__ xp) {
+                         __half* __restrict__ xp, int xp_natural, const float* __restrict__ hidden,
+                         const float* __restrict__ norm_w, float eps) {
     extern __shared__ float red[];   // KSPLIT > 1: [8 warps][MT][NT][4][32] partial tiles
+    __shared__ double nred[8];
+    __shared__ float inv_s[8 * NT];
     // the routing kernel that follows may be scheduled now; it waits for this grid before it reads
     // (a no-op unless that launch asks for programmatic serialization)
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (NORM) {
+        const int rows = min(8 * NT, n - (int)blockIdx.y * (8 * NT));
+        for (int r = 0; r < rows; ++r) {
+            const float* xr = hidden + ((int64_t)blockIdx.y * (8 * NT) + r) * H;
+            double ss = 0.0;
+            for (int i = threadIdx.x; i < H; i += 256) ss += (double)xr[i] * (double)xr[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if ((threadIdx.x & 31) == 0) nred[threadIdx.x >> 5] = ss;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                double tot = 0.0;
+                for (int i = 0; i < 8; ++i) tot += nred[i];
+                inv_s[r] = (float)(1.0 / sqrt(tot / (double)H + (double)eps));
+            }
+            __syncthreads();
+        }
+    }
     if (xp && (int)blockIdx.x * (16 * MT) >= E) {
-        // one column of blocks beyond the experts: this block's token rows as fp16 in the decode
-        // kernels' fragment order (saves a launch; the logits blocks read the same rows anyway)
+        // one column of blocks beyond the experts: this block's token rows as fp16 for the expert
+        // GEMMs - in the decode kernels' fragment order or in natural order (tcgen05 path) - which
+        // saves a launch; the logits blocks read the same rows anyway
         const int gpr = H >> 3, rows = min(8 * NT, n - (int)blockIdx.y * (8 * NT));
-        for (int i = threadIdx.x; i < rows * gpr; i += 256)
-            xprep_group(x, xp, (int64_t)blockIdx.y * (8 * NT) + i / gpr, i % gpr, H);
+        for (int i = threadIdx.x; i < rows * gpr; i += 256) {
+            const int r = i / gpr;
+            const int64_t row = (int64_t)blockIdx.y * (8 * NT) + r;
+            if (NORM) xprep_group_norm(hidden, norm_w, inv_s[r], xp, row, i - r * gpr, H, xp_natural);
+            else xprep_group(x, xp, row, i - r * gpr, H, xp_natural);
+        }
         return;
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -173,12 +204,27 @@ router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
     }
     const uint4* px[NT];
     bool x_ok[NT];
+    float xinv[NT];
 #pragma unroll
     for (int i = 0; i < NT; ++i) {
         const int tok = t0 + i * 8 + g;
         x_ok[i] = tok < n;
-        px[i] = reinterpret_cast<const uint4*>(x + (size_t)(x_ok[i] ? tok : 0) * H + kbeg) + t;
+        if (NORM) {
+            px[i] = reinterpret_cast<const uint4*>(hidden + (size_t)(x_ok[i] ? tok : 0) * H + kbeg) + 2 * t;
+            xinv[i] = x_ok[i] ? inv_s[i * 8 + g] : 0.f;
+        } else {
+            px[i] = reinterpret_cast<const uint4*>(x + (size_t)(x_ok[i] ? tok : 0) * H + kbeg) + t;
+            xinv[i] = 0.f;
+        }
     }
+    const uint4* pnw = reinterpret_cast<const uint4*>(norm_w + (NORM ? kbeg : 0)) + 2 * t;
+    // eight activations of a 32-column block as bf16: loaded as such, or normalised from fp32
+    auto load_x = [&](int i, int it) -> uint4 {
+        if (!NORM) return __ldg(px[i] + it * 4);
+        const uint4 a0 = __ldg(px[i] + it * 8), a1 = __ldg(px[i] + it * 8 + 1);
+        const uint4 w0 = __ldg(pnw + it * 8), w1 = __ldg(pnw + it * 8 + 1);
+        return norm8_bf16(a0, a1, w0, w1, xinv[i]);
+    };
     float acc[MT][NT][4];
 #pragma unroll
     for (int j = 0; j < MT; ++j)
@@ -199,7 +245,7 @@ router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
                     vb[j] = rb_ok[j] ? __ldg(pb[j] + it * 4) : zero;
                 }
 #pragma unroll
-                for (int i = 0; i < NT; ++i) vx[i] = x_ok[i] ? __ldg(px[i] + it * 4) : zero;
+                for (int i = 0; i < NT; ++i) vx[i] = x_ok[i] ? load_x(i, it) : zero;
 #pragma unroll
                 for (int j = 0; j < MT; ++j)
 #pragma unroll
@@ -221,7 +267,7 @@ router_logits_mma_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
                     vb[u][j] = (in && rb_ok[j]) ? __ldg(pb[j] + it * 4) : zero;
                 }
 #pragma unroll
-                for (int i = 0; i < NT; ++i) vx[u][i] = (in && x_ok[i]) ? __ldg(px[i] + it * 4) : zero;
+                for (int i = 0; i < NT; ++i) vx[u][i] = (in && x_ok[i]) ? load_x(i, it) : zero;
             }
 #pragma unroll
             for (int u = 0; u < kBatch; ++u) {
@@ -276,26 +322,39 @@ __global__ void sigmoid_scores_kernel(const float* __restrict__ logits, float* _
     if (i < n) scores[i] = sigmoid_ref(logits[i]);
 }
 
+template <bool NORM>
+static int launch_logits_mma(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n, int H, int E, float* logits,
+                             float* scores, cudaStream_t s, __half* xp, int xp_natural, const float* hidden,
+                             const float* norm_w, float eps) {
+    if (n <= 128) {
+        dim3 grid((unsigned)((E + 15) / 16) + (xp ? 1u : 0u), (unsigned)((n + 7) / 8));
+        router_logits_mma_kernel<1, 1, 8, NORM><<<grid, 256, 8 * 512, s>>>(x, wr, n, H, E, logits, scores, xp, xp_natural,
+                                                                         hidden, norm_w, eps);
+    } else {
+        constexpr int smem = 8 * 4 * 4 * 512;   // 64 KiB of partial tiles
+        if (cudaFuncSetAttribute(router_logits_mma_kernel<4, 4, 8, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 smem) != cudaSuccess)
+            return GSB_ERR_CUDA;
+        dim3 grid((unsigned)((E + 63) / 64) + (xp ? 1u : 0u), (unsigned)((n + 31) / 32));
+        router_logits_mma_kernel<4, 4, 8, NORM><<<grid, 256, smem, s>>>(x, wr, n, H, E, logits, scores, xp, xp_natural,
+                                                                      hidden, norm_w, eps);
+    }
+    return launch_status();
+}
+
+// x (bf16) or, when `hidden` is given, bf16(rmsnorm(hidden, norm_w, eps)) computed on the fly.
+// xp (nullable, input dims that are multiples of 256 only): the same activations as fp16 rows for the
+// expert GEMMs, in fragment order (xp_natural = 0) or natural order (1).
 int launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wr, int n, int H, int E,
-                         float* logits, float* scores, cudaStream_t s, __half* xp) {
+                         float* logits, float* scores, cudaStream_t s, __half* xp, int xp_natural,
+                         const float* hidden, const float* norm_w, float eps) {
     if (n == 0) return GSB_OK;
     if (H % 8 != 0) return GSB_ERR_UNSUPPORTED;
     if (H % 256 == 0) {
-        if (n <= 128) {
-            dim3 grid((unsigned)((E + 15) / 16) + (xp ? 1u : 0u), (unsigned)((n + 7) / 8));
-            router_logits_mma_kernel<1, 1, 8><<<grid, 256, 8 * 512, s>>>(x, wr, n, H, E, logits, scores, xp);
-        } else {
-            constexpr int smem = 8 * 4 * 4 * 512;   // 64 KiB of partial tiles
-            if (cudaFuncSetAttribute(router_logits_mma_kernel<4, 4, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     smem) != cudaSuccess)
-                return GSB_ERR_CUDA;
-            dim3 grid((unsigned)((E + 63) / 64), (unsigned)((n + 31) / 32));
-            if (xp) return GSB_ERR_INVALID_ARG;   // the fused conversion exists for decode-sized batches only
-            router_logits_mma_kernel<4, 4, 8><<<grid, 256, smem, s>>>(x, wr, n, H, E, logits, scores, nullptr);
-        }
-        return launch_status();
+        if (hidden) return launch_logits_mma<true>(nullptr, wr, n, H, E, logits, scores, s, xp, xp_natural, hidden, norm_w, eps);
+        return launch_logits_mma<false>(x, wr, n, H, E, logits, scores, s, xp, xp_natural, nullptr, nullptr, 0.f);
     }
-    if (xp) return GSB_ERR_INVALID_ARG;
+    if (xp || hidden) return GSB_ERR_INVALID_ARG;
     constexpr int TT = 8;
     const size_t smem = (size_t)TT * H * 2;
     if (smem > 200 * 1024) return GSB_ERR_UNSUPPORTED;

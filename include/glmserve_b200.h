@@ -272,6 +272,14 @@ GSB_API int gsb_router_logits(const void* x_bf16, const void* router_w_bf16, int
 GSB_API int gsb_moe_layer_profile_enable(gsb_moe_layer* layer, int max_forwards);
 GSB_API int gsb_moe_layer_profile_read(gsb_moe_layer* layer, float* stage_ms, int* n_forwards);
 
+/* Diagnostic of the tcgen05 path: while device_buffer (2 x 1024 x 16 int64, device memory) is set, every
+ * CTA of the gate/up kernel (first 1024 x 16) and of the down kernel (second) stores the SM cycles its
+ * roles spent in bounded waits during the last forward: [0] producer loop total, [1] producer waiting
+ * for a free int4 stage, [2] for a free activation stage, [3] MMA thread waiting for a free accumulator,
+ * [4] for unpacked weights, [5] for an activation tile, [6] unpack warps waiting for int4 data, [7] for a
+ * free slot of the weight ring, [8] MMA thread issuing tcgen05.mma / commit, [9] MMA thread total.  NULL switches it off (the default).  Host call, not thread safe. */
+GSB_API int gsb_prefill_wait_profile(long long* device_buffer);
+
 /* Routing without any allocation: x bf16 [n,hidden] and the bf16 router weight [E,hidden]
  * in, topk_ids i32 [n,topk] and topk_weights f32 [n,topk] out - the same result as
  * gsb_router_logits followed by gsb_moe_router, but the [n,E] logits in between are kept in

@@ -261,25 +261,149 @@ def test_glm_scale_prefill_full_size_token_sample(dev, glm_layer):
     assert np.bincount(ids_np.ravel(), minlength=256).sum() == n * 8
 
 
+def test_glm_scale_prefill_zipf_skewed_benchmark_inputs(dev, glm_layer):
+    """The benchmark's own prefill configuration: 8192 tokens through the GLM-scale layer with the
+    Zipf(1.1)-ranked router bias (amplitude 0.04) that bench.py adds - experts with a handful of rows
+    next to experts with about 2000 rows and ten token tiles.  The oracle runs on a token sample
+    chosen to visit the heaviest and the lightest experts (tokens are independent); the whole
+    65,536-slot permutation is compared with the oracle's stable counting sort."""
+    from glmserve_b200 import ops
+    from glmserve_b200.synth import zipf_bias
+    layer, Lnp = glm_layer
+    E, n = 256, 8192
+    bias = (Lnp["e_bias"] + zipf_bias(E, np.random.default_rng(1), 0.04)).astype(np.float32)
+    Ls = dict(H=6144, E=E, topk=8, I=2048, Is=2048, group=128, norm_topk=True, routed_scale=2.5,
+              router_w=layer._keep["router_w"], e_bias=torch.from_numpy(bias).to(dev),
+              sg_q=torch.zeros(1, dtype=torch.uint8, device=dev))
+    skewed = ops.MoELayer(Ls, share_from=layer)
+    Lsk = dict(Lnp, e_bias=bias)
+    x = make_x_torch(n, 6144, seed=200, device=dev)
+    out, logits, ids, w = skewed.forward(x, path=ops.PATH_PREFILL, return_routing=True)
+    out = out.clone()
+    assert skewed.status() == 0
+    ids_np = ids.cpu().numpy()
+    loads = np.bincount(ids_np.ravel(), minlength=E)
+    assert loads.max() > 5 * loads.mean() and loads[loads > 0].min() < 0.1 * loads.mean(), "routing is not skewed"
+    # tokens that visit the three heaviest and the three lightest non-empty experts, plus both ends
+    order = np.argsort(loads)
+    light = [e for e in order if loads[e] > 0][:3]
+    heavy = list(order[-3:])
+    pick = {0, n - 1}
+    for e in light + heavy:
+        rows = np.nonzero((ids_np == e).any(axis=1))[0]
+        pick.update(int(r) for r in rows[[0, -1]])
+    pick = np.array(sorted(pick))
+    sel = torch.from_numpy(pick).to(dev)
+    r = oracle.moe_layer_w4(x[sel].float().cpu().numpy(), Lsk, logits_in=logits[sel].cpu().numpy())
+    assert np.array_equal(ids_np[pick], r["ids"])
+    assert_layer_close(out.cpu().numpy()[pick], r["out"], "glm prefill n=8192 Zipf-skewed, sampled tokens")
+    assert torch.equal(skewed.forward(x, path=ops.PATH_PREFILL), out)
+    # the permutation of all 65,536 slots (the many-block dispatch the layer runs) against the oracle
+    offs, tok, row = ops.moe_dispatch_ws(ids, E)
+    o_offs, o_tok, o_row = oracle.dispatch(ids_np, E)
+    assert np.array_equal(offs.cpu().numpy(), o_offs)
+    assert np.array_equal(tok.cpu().numpy(), o_tok) and np.array_equal(row.cpu().numpy(), o_row)
+
+
+def test_large_magnitude_activations_stay_finite(dev):
+    """Intermediates are kept in fp16 between the two GEMMs: values beyond +-65504 must saturate,
+    not become inf and then NaN (inf * 0) in the down projection or the combine.  Activations
+    of magnitude ~3e3 drive silu(gate) * up past the fp16 range on a layer with unit-size weights;
+    every path must return finite numbers, and where nothing saturates (the oracle's own
+    intermediates stay below 65504) the usual tolerance holds."""
+    from glmserve_b200 import ops
+    L = make_layer_np(CONFIGS["mid"], seed=41)
+    layer = ops.MoELayer(layer_to_torch(L, dev))
+    x_np = make_x_np(40, L["H"], seed=42)
+    for scale, expect_close in ((30.0, True), (3000.0, False)):
+        from glmserve_b200.quant import round_bf16_np
+        xs = round_bf16_np((x_np * scale).astype(np.float32))
+        for path in (ops.PATH_DECODE, ops.PATH_PREFILL):
+            out, logits, ids, w = layer.forward(bf16_tensor(xs, dev), path=path, return_routing=True)
+            assert layer.status() == 0
+            o = out.cpu().numpy()
+            assert np.isfinite(o).all(), f"non-finite output at activation scale {scale}"
+            if expect_close:
+                r = oracle.moe_layer_w4(xs, L, logits_in=logits.cpu().numpy())
+                ref = r["out"]
+                rel = float(np.linalg.norm(o - ref) / np.linalg.norm(ref))
+                assert rel <= 1e-3, f"scale {scale}: rel-L2 {rel:.2e}"
+
+
 def test_block_of_layers_with_prenorm_and_residual(dev):
     """Two chained layers h <- h + moe(rmsnorm(h)) (the speculative-verify block's shape,
-    scaled down)."""
+    scaled down), on the decode kernels, the tcgen05 kernels and the direct-layout kernels: the
+    norm rides the router-logits launch and the residual add rides the combine."""
     from glmserve_b200 import ops
+    from glmserve_b200.quant import round_bf16_np
     n, H = 32, CONFIGS["mid"]["H"]
-    rng = np.random.default_rng(9)
-    h_np = make_x_np(n, H, seed=77)
-    h = torch.from_numpy(h_np).to(dev)
-    for li in range(2):
-        L = make_layer_np(CONFIGS["mid"], seed=30 + li)
-        nw = (1.0 + 0.02 * rng.standard_normal(H)).astype(np.float32)
-        layer = ops.MoELayer(layer_to_torch(L, dev))
-        ids = torch.empty((n, L["topk"]), dtype=torch.int32, device=dev)
-        # oracle on the SAME input hidden state, routed with the GPU's logits
-        normed = oracle.rmsnorm_rows(h.cpu().numpy(), nw, 1e-5)
-        from glmserve_b200.quant import round_bf16_np
-        xb = round_bf16_np(normed)
-        logits = ops.router_logits(bf16_tensor(xb, dev), layer._keep["router_w"]).cpu().numpy()
-        want = h.cpu().numpy() + oracle.moe_layer_w4(xb, L, logits_in=logits)["out"]
-        layer.block_forward(h, torch.from_numpy(nw).to(dev), 1e-5, ids_out=ids)
+    for path in (ops.PATH_AUTO, ops.PATH_PREFILL, ops.PATH_DIRECT):
+        rng = np.random.default_rng(9)
+        h_np = make_x_np(n, H, seed=77)
+        h = torch.from_numpy(h_np).to(dev)
+        for li in range(2):
+            L = make_layer_np(CONFIGS["mid"], seed=30 + li)
+            nw = (1.0 + 0.02 * rng.standard_normal(H)).astype(np.float32)
+            layer = ops.MoELayer(layer_to_torch(L, dev))
+            ids = torch.empty((n, L["topk"]), dtype=torch.int32, device=dev)
+            # oracle on the SAME input hidden state, routed with the GPU's logits
+            normed = oracle.rmsnorm_rows(h.cpu().numpy(), nw, 1e-5)
+            xb = round_bf16_np(normed)
+            logits = ops.router_logits(bf16_tensor(xb, dev), layer._keep["router_w"]).cpu().numpy()
+            r = oracle.moe_layer_w4(xb, L, logits_in=logits)
+            want = h.cpu().numpy() + r["out"]
+            layer.block_forward(h, torch.from_numpy(nw).to(dev), 1e-5, path=path, ids_out=ids)
+            assert layer.status() == 0
+            assert np.array_equal(ids.cpu().numpy(), r["ids"]), f"block layer {li}: router ids differ"
+            assert_layer_close(h.cpu().numpy(), want, f"block layer {li} path {path}")
+
+
+def test_speculative_verify_block_glm_scale(dev):
+    """The benchmarked speculative-verify block at its stated shape: 8 consecutive GLM-scale layers,
+    each pre-RMSNorm (eps 1e-5, weight ~1 + N(0, 0.02)) with a residual add, on 64 x 4 = 256 tokens.
+    Layer by layer, the CPU reference (rmsnorm -> bf16 -> moe -> residual) runs on a 12-token sample
+    of the GPU's own input state (tokens are independent through norm, MoE and residual), routed with
+    logits the GPU computed for the whole 256-row batch; in addition a pure CPU chain from the initial
+    state (its own logits, no GPU input) is compared at the end on the tokens whose routing never
+    differed."""
+    from glmserve_b200 import ops
+    from glmserve_b200.quant import round_bf16_np
+    H, n, nl = 6144, 256, 8
+    pick = np.array([0, 1, 3, 4, 63, 64, 127, 128, 200, 252, 254, 255])
+    gen = torch.Generator(device=dev); gen.manual_seed(400)
+    h = torch.randn((n, H), generator=gen, device=dev).to(torch.bfloat16).float()
+    h_chain = h[torch.from_numpy(pick).to(dev)].cpu().numpy().copy()
+    chain_ok = np.ones(len(pick), bool)
+    for li in range(nl):
+        Lt = make_layer_torch(CONFIGS["glm"], seed=10 + li, device=dev)
+        layer = ops.MoELayer(Lt, keep_raw=False)
+        Lnp = layer_to_np(Lt)
+        del Lt
+        torch.cuda.empty_cache()
+        nw_t = (1.0 + 0.02 * torch.randn(H, generator=gen, device=dev)).float().contiguous()
+        nw = nw_t.cpu().numpy()
+        h_in = h.cpu().numpy()
+        xb_full = round_bf16_np(oracle.rmsnorm_rows(h_in, nw, 1e-5))
+        logits = ops.router_logits(bf16_tensor(xb_full, dev), layer._keep["router_w"]).cpu().numpy()
+        r = oracle.moe_layer_w4(xb_full[pick], Lnp, logits_in=logits[pick])
+        want = h_in[pick] + r["out"]
+        ids = torch.empty((n, 8), dtype=torch.int32, device=dev)
+        layer.block_forward(h, nw_t, 1e-5, path=ops.PATH_DECODE, ids_out=ids)
         assert layer.status() == 0
-        assert_layer_close(h.cpu().numpy(), want, f"block layer {li}")
+        assert np.array_equal(ids.cpu().numpy()[pick], r["ids"]), f"layer {li}: router ids differ"
+        assert_layer_close(h.cpu().numpy()[pick], want, f"verify block layer {li}")
+        # the pure CPU chain
+        h_chain, ids_chain = _cpu_block(h_chain, nw, Lnp)
+        chain_ok &= (ids_chain == r["ids"]).all(axis=1)
+        del layer, Lnp
+        torch.cuda.empty_cache()
+    assert chain_ok.sum() >= len(pick) - 3, f"routing of the CPU chain left the GPU's on {int((~chain_ok).sum())} of {len(pick)} tokens"
+    assert_layer_close(h.cpu().numpy()[pick][chain_ok], h_chain[chain_ok], "verify block, 8 layers chained on the CPU")
+
+
+def _cpu_block(h, nw, Lnp):
+    """One block layer on the CPU with bf16 activations into the MoE (what the GPU path feeds it)."""
+    from glmserve_b200.quant import round_bf16_np
+    xb = round_bf16_np(oracle.rmsnorm_rows(h, nw, 1e-5))
+    r = oracle.moe_layer_w4(xb, Lnp)
+    return h + r["out"], r["ids"]
