@@ -524,6 +524,9 @@ tile_list_kernel(const int* __restrict__ expert_offsets, int E, int shared_marke
 
 // Activations into expert order (natural feature order for TMA), from the fp16 copy the
 // router-logits launch left behind: xs[r] = xh[sorted_tok[r]] for r < P, xs[P + t] = xh[t].
+// (Fetching the rows by index in the GEMM's producer instead - TMA gather4, four 128-byte rows per
+// instruction - was built and is correct, but 48 such instructions per k-block keep the TMA unit busy
+// for ~2200 cycles against the ~380 the tensor core needs: 4x slower than this pass plus tiled loads.)
 __global__ void __launch_bounds__(256)
 gather_x_kernel(const __half* __restrict__ xh, const int* __restrict__ sorted_tok, int P,
                 int n, int H, int with_shared, __half* __restrict__ xs) {
@@ -534,7 +537,9 @@ gather_x_kernel(const __half* __restrict__ xh, const int* __restrict__ sorted_to
     const int64_t r = i / gpr;
     const int grp = (int)(i - r * gpr);
     const int64_t src = r < P ? sorted_tok[r] : r - P;
-    reinterpret_cast<uint4*>(xs + r * H)[grp] = __ldg(reinterpret_cast<const uint4*>(xh + src * H) + grp);
+    // streaming store: the 0.9 GB written here must not push the token-order matrix (which every row is
+    // read from top-k times) out of L2
+    __stcs(reinterpret_cast<uint4*>(xs + r * H) + grp, __ldg(reinterpret_cast<const uint4*>(xh + src * H) + grp));
 }
 
 // Deterministic combine over fp16 per-slot rows (same order as combine_kernel of the decode
