@@ -289,108 +289,140 @@ def run_ours(args) -> None:
     # N > 1: the two ways the layer is partitioned over the box, on top of the replica headline
     if world > 1 and not args.no_extra and GLM["E"] % world == 0:
         from glmserve_b200.dist import Comm, shard_layer_ep, shard_layer_tp_torch
+        from glmserve_b200.synth import make_layer_torch as mk
+        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+        def timed(fn, reps, warm=3):
+            for _ in range(warm):
+                fn()
+            barrier(); ea.record()
+            for _ in range(reps):
+                fn()
+            eb.record(); barrier()
+            return ea.elapsed_time(eb) / reps
+
+        def max_over_ranks(vals):
+            tt = torch.tensor([float(v) for v in vals], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return [float(v) for v in tt]
+
         Te = 4096
         recv_cap = 2 * Te * GLM["topk"]
-        Lep = shard_layer_ep(Lt, rank, world)
-        layer_ep = ops.MoELayer(Lep, keep_raw=False)
-        ar_max = ar_max_v = 256 * GLM["H"]
-        heap = layer_ep.ep_heap_bytes(Te, recv_cap) + 4 * ar_max * 4 + (4 << 20)
+        layer_ep = ops.MoELayer(shard_layer_ep(Lt, rank, world), keep_raw=False)
+        ar_max = 256 * GLM["H"]
+        heap = layer_ep.ep_heap_bytes(Te, recv_cap) + 4 * (ar_max + 64) * 4 + (4 << 20)
         comm = Comm(heap_bytes=heap, allreduce_max_count=ar_max)
         xe = make_x_torch(Te, GLM["H"], seed=300 + rank, device=dev)
         oe = torch.empty((Te, GLM["H"]), dtype=torch.float32, device=dev)
-        for _ in range(3):
-            layer_ep.forward_ep(comm, xe, out=oe, recv_cap=recv_cap)
+        # parity inside the run: the expert-parallel output of this rank's tokens against the single-GPU layer
+        # (all experts resident) on the same tokens - the same bits, on every rank
+        want = layer.forward(xe, path=ops.PATH_PREFILL).clone()
+        got = layer_ep.forward_ep(comm, xe, out=oe, recv_cap=recv_cap, path=ops.PATH_PREFILL)
+        torch.cuda.synchronize()
         st_ep = comm.status()
-        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        ea.record()
-        for _ in range(5):
-            layer_ep.forward_ep(comm, xe, out=oe, recv_cap=recv_cap)
-        eb.record()
-        barrier()
-        ms_ep = ea.elapsed_time(eb) / 5
+        eq = torch.tensor([1 if torch.equal(got, want) else 0], device=dev)
+        dist.all_reduce(eq, op=dist.ReduceOp.MIN)
+        del want
+        ms_ep = timed(lambda: layer_ep.forward_ep(comm, xe, out=oe, recv_cap=recv_cap, path=ops.PATH_PREFILL), 5)
         st_ep = st_ep or comm.status()
+        # where the time goes: the library's stage marks on the caller's stream (a second pass)
+        ops.profile_enable(layer_ep, 5)
+        for _ in range(5):
+            layer_ep.forward_ep(comm, xe, out=oe, recv_cap=recv_cap, path=ops.PATH_PREFILL)
+        ph = ops.profile_read(layer_ep, ops.EP_STAGES)
+        ops.profile_enable(layer_ep, 0)
+        ph_names = [k for k in ph if k != "forwards"]
+        ph_max = dict(zip(ph_names, max_over_ranks([ph[k] for k in ph_names])))
+        # the denominator of the expert-parallel efficiency, measured in this run: all 256 experts on one GPU
+        ms_base = timed(lambda: layer.forward(xe, out=oe, path=ops.PATH_PREFILL), 5)
+
+        # speculative-verify block on the box, expert parallel: 8 consecutive layers (pre-RMSNorm + MoE + residual),
+        # 256 tokens in all = 256 / N per GPU, every layer with its own weights (rank r holds its experts of each)
+        nl, Tv = 8, 256
+        nv = Tv // world
+        layers_ep = [layer_ep] + [ops.MoELayer(shard_layer_ep(mk(GLM, seed=10 + i, device=dev), rank, world), keep_raw=False)
+                                  for i in range(1, nl)]
+        torch.cuda.empty_cache()
+        norms = [(1.0 + 0.02 * torch.randn(GLM["H"], device=dev)).float().contiguous() for _ in range(nl)]
+        hv = make_x_torch(nv, GLM["H"], seed=400 + rank, device=dev).float()
+        ov = torch.empty((nv, GLM["H"]), dtype=torch.float32, device=dev)
+        cap_v = 2 * nv * GLM["topk"]
+
+        def verify_block_ep():
+            for L_, nw in zip(layers_ep, norms):
+                xn = ops.rmsnorm(hv, nw, 1e-5).to(torch.bfloat16)
+                L_.forward_ep(comm, xn, out=ov, recv_cap=cap_v, path=ops.PATH_DECODE)
+                hv.add_(ov)
+        us_blk_ep = timed(verify_block_ep, 3, warm=2) * 1e3
+        st_ep = st_ep or comm.status()
+        del layers_ep[1:]
+        torch.cuda.empty_cache()
+
         # the all-reduce alone, both algorithms, against NCCL as the baseline; the faster one is then
         # set for the tensor-parallel layer (the choice changes no bit of the result)
-        buf = torch.zeros(T * GLM["H"], device=dev)
-        us_alg = {}
-        for name, limit in (("one_shot", 1 << 40), ("two_shot", 1)):
-            comm.allreduce_one_shot_limit(limit)
-            for _ in range(5):
-                comm.allreduce_sum(buf)
-            barrier(); ea.record()
-            for _ in range(50):
-                comm.allreduce_sum(buf)
-            eb.record(); barrier()
-            us_alg[name] = ea.elapsed_time(eb) / 50 * 1e3
-        ta = torch.tensor([us_alg["one_shot"], us_alg["two_shot"]], device=dev, dtype=torch.float64)
-        dist.all_reduce(ta, op=dist.ReduceOp.MAX)
-        us_alg = {"one_shot": float(ta[0]), "two_shot": float(ta[1])}
+        us_alg_all = {}
+        for nfl in (GLM["H"], T * GLM["H"]):
+            buf = torch.zeros(nfl, device=dev)
+            us_alg = {}
+            for name, limit in (("one_shot", 1 << 40), ("two_shot", 1)):
+                comm.allreduce_one_shot_limit(limit)
+                us_alg[name] = timed(lambda: comm.allreduce_sum(buf), 50, warm=5) * 1e3
+            us_alg["nccl"] = timed(lambda: dist.all_reduce(buf), 50, warm=5) * 1e3
+            keys = list(us_alg)
+            us_alg_all[nfl] = dict(zip(keys, max_over_ranks([us_alg[k] for k in keys])))
+        us_alg = us_alg_all[T * GLM["H"]]
         comm.allreduce_one_shot_limit((1 << 40) if us_alg["one_shot"] <= us_alg["two_shot"] else 1)
-        us_ar = min(us_alg.values())
-        for _ in range(5):
-            dist.all_reduce(buf)
-        barrier(); ea.record()
-        for _ in range(50):
-            dist.all_reduce(buf)
-        eb.record(); barrier()
-        us_nccl = ea.elapsed_time(eb) / 50 * 1e3
+        us_ar, us_nccl = min(us_alg["one_shot"], us_alg["two_shot"]), us_alg["nccl"]
         # tensor parallel: decode batch, gate/up column split, down row split, NVLink all-reduce
         Ltp = shard_layer_tp_torch(Lt, rank, world, pad_to=512)
         layer_tp = ops.MoELayer(Ltp, keep_raw=False)
         xt = make_x_torch(T, GLM["H"], seed=100, device=dev)
         ot = torch.empty((T, GLM["H"]), dtype=torch.float32, device=dev)
-        for _ in range(3):
+
+        def tp_layer():
             layer_tp.forward(xt, out=ot, path=ops.PATH_DECODE)
             comm.allreduce_sum(ot.view(-1))
-        barrier()
-        ea.record()
-        for _ in range(args.steps):
-            layer_tp.forward(xt, out=ot, path=ops.PATH_DECODE)
-            comm.allreduce_sum(ot.view(-1))
-        eb.record()
-        barrier()
-        ms_tp = ea.elapsed_time(eb) / args.steps
+        ms_tp = timed(tp_layer, args.steps)
         # speculative-verify block under tensor parallelism: 8 x (RMSNorm -> sharded layer -> all-reduce ->
         # residual), 256 tokens.  The eight layers share one set of sharded weights (a shard is far larger
         # than L2, so every layer still streams it from HBM): timing only.
-        Tv, nl = 256, 8
-        ar_v = Tv * GLM["H"]
-        us_blk = None
-        if ar_v <= ar_max_v:
-            norm_w = torch.ones(GLM["H"], device=dev)
-            hv = make_x_torch(Tv, GLM["H"], seed=400, device=dev).float()
-            ov = torch.empty((Tv, GLM["H"]), dtype=torch.float32, device=dev)
-            def verify_block():
-                for _ in range(nl):
-                    xn = ops.rmsnorm(hv, norm_w, 1e-5).to(torch.bfloat16)
-                    layer_tp.forward(xn, out=ov, path=ops.PATH_DECODE)
-                    comm.allreduce_sum(ov.view(-1))
-                    hv.add_(ov)
-            for _ in range(2):
-                verify_block()
-            barrier(); ea.record()
-            for _ in range(3):
-                verify_block()
-            eb.record(); barrier()
-            us_blk = ea.elapsed_time(eb) / 3 * 1e3
+        norm_w = torch.ones(GLM["H"], device=dev)
+        hv2 = make_x_torch(Tv, GLM["H"], seed=400, device=dev).float()
+        ov2 = torch.empty((Tv, GLM["H"]), dtype=torch.float32, device=dev)
+
+        def verify_block_tp():
+            for _ in range(nl):
+                xn = ops.rmsnorm(hv2, norm_w, 1e-5).to(torch.bfloat16)
+                layer_tp.forward(xn, out=ov2, path=ops.PATH_DECODE)
+                comm.allreduce_sum(ov2.view(-1))
+                hv2.add_(ov2)
+        us_blk = timed(verify_block_tp, 3, warm=2) * 1e3
         st_tp = comm.status()
-        tt = torch.tensor([ms_ep, ms_tp, us_ar, us_nccl, float(st_ep), float(st_tp), us_blk or 0.0], device=dev,
-                          dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms_ep, ms_tp, us_ar, us_nccl = (float(v) for v in tt[:4])
+        ms_ep, ms_tp, ms_base, us_blk, us_blk_ep, st_ep, st_tp = max_over_ranks(
+            [ms_ep, ms_tp, ms_base, us_blk, us_blk_ep, float(st_ep), float(st_tp)])
+        flops_ep = layer_flops(Te)["layer"]
         extra["expert_parallel_T4096_per_gpu"] = {
             "tokens_per_s": world * Te / (ms_ep * 1e-3), "ms_per_layer": ms_ep, "experts_per_gpu": GLM["E"] // world,
-            "tflops_per_gpu": layer_flops(Te)["layer"] / (ms_ep * 1e-3) / 1e12, "recv_cap_rows": recv_cap,
-            "status": int(tt[4]), "exchange": "in-kernel NVLink stores (dispatch push, combine from the down-GEMM epilogue)"}
+            "tflops_per_gpu": flops_ep / (ms_ep * 1e-3) / 1e12,
+            "frac_of_measured_bf16_peak_per_gpu": flops_ep / (ms_ep * 1e-3) / 1e12 / peaks()["bf16_tflops"],
+            "single_gpu_all_experts_ms_per_layer": ms_base,
+            "ep_efficiency": ms_base / ms_ep,
+            "ep_bitwise_equal_single_gpu": bool(int(eq)),
+            "phase_ms_max_over_ranks": ph_max, "recv_cap_rows": recv_cap, "status": int(st_ep),
+            "exchange": "in-kernel NVLink stores: dispatch push on a side stream under the shared expert, combine "
+                        "from the down-GEMM epilogue"}
         extra[f"tensor_parallel_T{T}"] = {"us_per_layer": ms_tp * 1e3, "tp": world, "allreduce_us": us_ar,
-                                          "allreduce_us_by_algorithm": us_alg, "nccl_allreduce_us": us_nccl, "allreduce_floats": T * GLM["H"],
-                                          "status": int(tt[5])}
-        if float(tt[6]) > 0:
-            extra[f"spec_verify_block_8_layers_T256_tp{world}"] = {
-                "us_per_block": float(tt[6]), "us_per_layer": float(tt[6]) / nl,
-                "note": "RMSNorm -> tensor-parallel layer (decode kernels) -> NVLink all-reduce -> residual, "
-                        "x 8; the layers share one set of sharded weights"}
+                                          "allreduce_us_by_algorithm": {k: v for k, v in us_alg.items() if k != "nccl"},
+                                          "nccl_allreduce_us": us_nccl, "allreduce_floats": T * GLM["H"],
+                                          "allreduce_one_row_us": us_alg_all[GLM["H"]], "status": int(st_tp)}
+        extra[f"spec_verify_block_8_layers_T256_tp{world}"] = {
+            "us_per_block": us_blk, "us_per_layer": us_blk / nl,
+            "note": "RMSNorm -> tensor-parallel layer (split-K kernels) -> NVLink all-reduce -> residual, "
+                    "x 8; the layers share one set of sharded weights"}
+        extra[f"spec_verify_block_8_layers_T256_ep{world}"] = {
+            "us_per_block": us_blk_ep, "us_per_layer": us_blk_ep / nl, "tokens_per_gpu": nv,
+            "note": "RMSNorm -> expert-parallel layer (split-K kernels, NVLink dispatch and return) -> residual, "
+                    "x 8; eight different layers, 256 tokens over the box"}
         comm.close()
 
     if world > 1:

@@ -58,6 +58,9 @@ def lib():
         L.gsb_moe_ep_heap_bytes.restype = C.c_size_t
         L.gsb_moe_ep_workspace_bytes.restype = C.c_size_t
         L.gsb_comm_destroy.restype = None
+        L.gsb_comm_set_wait_cycles.argtypes = [C.c_void_p, C.c_longlong]
+        L.gsb_comm_open_loopback.argtypes = [C.c_void_p]
+        L.gsb_prefill_wait_profile.argtypes = [C.c_void_p]
         _lib = L
     return _lib
 

@@ -270,6 +270,9 @@ int gsb_moe_layer_create(const gsb_moe_config* cfg, gsb_moe_layer** out) {
 void gsb_moe_layer_destroy(gsb_moe_layer* layer) {
     if (!layer) return;
     gsb_moe_layer_profile_enable(layer, 0);
+    if (layer->ep_fork) cudaEventDestroy(layer->ep_fork);
+    if (layer->ep_join) cudaEventDestroy(layer->ep_join);
+    if (layer->ep_side) cudaStreamDestroy(layer->ep_side);
     delete layer;
 }
 

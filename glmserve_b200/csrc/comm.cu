@@ -87,9 +87,10 @@ __device__ __forceinline__ int* blk_flag(const CommPeers& pr, int owner, int pha
 
 // All peers' block-b flags of `phase`: post ours, then wait for theirs.  Returns false on a timeout (all threads).
 __device__ __forceinline__ bool ar_exchange_flags(const ArArgs& a, int phase, int* ok_s) {
-    __threadfence_system();
-    __syncthreads();
     if (threadIdx.x == 0) *ok_s = 1;
+    // The block's stores are ordered before the flags by the barrier plus the release of the flag store
+    // itself (release is cumulative over what the storing thread observed through the barrier): one
+    // release per peer, not a system-wide fence by every thread.
     __syncthreads();
     if (threadIdx.x < a.world && threadIdx.x != a.rank) {
         st_release_sys(blk_flag(a.pr, threadIdx.x, phase, a.rank), a.seq);
@@ -204,7 +205,7 @@ __global__ void ep_post_counts_kernel(CommPeers pr, int rank, int world, const i
 __global__ void __launch_bounds__(1024)
 ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restrict__ recv_offsets,
                int* __restrict__ send_base, void** __restrict__ ydst, int H, int y_elem_bytes,
-               int recv_cap, int* __restrict__ plan, long long wait_cycles) {
+               int recv_cap, int own_ybuf_kib, int* __restrict__ plan, long long wait_cycles) {
     int* ctrl = ctrl_of(pr, rank);
     __shared__ int tot_s[kMaxExperts];             // rows of expert e over all sources
     __shared__ int base_s[kMaxExperts];            // first receive row of expert e on its owner
@@ -234,7 +235,7 @@ ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restric
         for (int e = 0; e < E; ++e) { spos_s[threadIdx.x][e] = run; run += cnt[threadIdx.x * kMaxExperts + e]; }
         plan[4 + 4 * threadIdx.x + 0] = threadIdx.x == rank ? 0 : meta[threadIdx.x * 8 + 0];
         plan[4 + 4 * threadIdx.x + 1] = threadIdx.x == rank ? recv_cap : meta[threadIdx.x * 8 + 1];
-        plan[4 + 4 * threadIdx.x + 2] = threadIdx.x == rank ? 0 : meta[threadIdx.x * 8 + 2];
+        plan[4 + 4 * threadIdx.x + 2] = threadIdx.x == rank ? own_ybuf_kib : meta[threadIdx.x * 8 + 2];
     }
     __syncthreads();
     if (threadIdx.x < world) {                     // one thread per owner: running prefix over its experts
@@ -263,7 +264,7 @@ ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restric
         const int c = cnt[sidx * kMaxExperts + e];
         const int src_pos = spos_s[sidx][e];
         // the source's own row buffer, at the offset the source posted (this rank's own: its argument)
-        const size_t yoff = kCtrlBytes + ((size_t)(sidx == rank ? plan[4 + 4 * rank + 3] : meta[sidx * 8 + 2]) << 10);
+        const size_t yoff = kCtrlBytes + ((size_t)(sidx == rank ? own_ybuf_kib : meta[sidx * 8 + 2]) << 10);
         for (int i = lane; i < c; i += 32)
             if (row + i < recv_cap)
                 ydst[row + i] = pr.base[sidx] + yoff + (size_t)(src_pos + i) * H * y_elem_bytes;
@@ -306,10 +307,8 @@ int comm_launch_wait(gsb_comm* c, int ch, cudaStream_t s) {
     return launch_status();
 }
 
-// Count exchange and plan on s_plan; dispatch push and its signal on s_push (which the caller has made
-// wait for s_plan's work so far; the same stream is fine).  Everything up to (not including) the wait for
-// the peers' rows: the caller waits on kChDispatch before reading its receive buffer.
-int comm_ep_exchange(gsb_comm* c, const EpExchange& e, cudaStream_t s) {
+// Count exchange and plan: everything that decides where rows go.
+int comm_ep_plan(gsb_comm* c, const EpExchange& e, cudaStream_t s) {
     if (e.E > kMaxExperts || e.E % c->world) return GSB_ERR_UNSUPPORTED;
     if ((e.recv_off & 1023) || (e.ybuf_off & 1023) || (e.recv_off >> 10) > 0x7fffffff || (e.ybuf_off >> 10) > 0x7fffffff)
         return GSB_ERR_INVALID_ARG;
@@ -317,12 +316,14 @@ int comm_ep_exchange(gsb_comm* c, const EpExchange& e, cudaStream_t s) {
     const int seq_c = (int)++c->seq[kChCounts];
     ep_post_counts_kernel<<<1, 256, 0, s>>>(c->peers, c->rank, c->world, e.expert_offsets, e.E, seq_c,
                                             (int)(e.recv_off >> 10), e.recv_cap, (int)(e.ybuf_off >> 10));
-    // this rank's own row-buffer offset travels to the plan kernel in plan[4 + 4 * rank + 3]
-    const int own_y = (int)(e.ybuf_off >> 10);
-    if (cudaMemcpyAsync(e.plan + 4 + 4 * c->rank + 3, &own_y, sizeof(int), cudaMemcpyHostToDevice, s) != cudaSuccess)
-        return GSB_ERR_CUDA;
     ep_plan_kernel<<<1, 1024, 0, s>>>(c->peers, c->rank, c->world, e.E, seq_c, e.recv_offsets, e.send_base, e.ydst,
-                                      e.H, e.y_elem_bytes, e.recv_cap, e.plan, c->wait_cycles);
+                                      e.H, e.y_elem_bytes, e.recv_cap, (int)(e.ybuf_off >> 10), e.plan, c->wait_cycles);
+    return launch_status();
+}
+
+// Dispatch push of this rank's rows and its signal (any stream ordered after comm_ep_plan's).  The caller
+// waits on kChDispatch before it reads its receive buffer.
+int comm_ep_push(gsb_comm* c, const EpExchange& e, cudaStream_t s) {
     if (e.P > 0)
         ep_dispatch_push_kernel<<<e.P, 256, 0, s>>>(c->peers, c->rank, c->world, e.E, e.x, e.expert_offsets, e.sorted_tok,
                                                     e.send_base, e.sorted_expert, e.H, e.plan, e.recv_off, e.frag_order);

@@ -57,6 +57,8 @@ struct DecodeKArgs {
     __half* hbuf;                  // gate/up output [P + n, ldh]
     int ldh;
     float* ybuf;                   // down output [P + n, H]
+    float* const* ydst;            // optional per-slot output row pointers (expert parallel: a routed row lives on the
+                                   // token's home GPU and is stored there over NVLink); overrides ybuf
     int H;
     int nstage;
     int* status;
@@ -395,7 +397,7 @@ decode_gemm_kernel(const DecodeKArgs a) {
                     const float h = __fmul_rn(silu_ref(s0), s1);
                     a.hbuf[slot * a.ldh + frag_pos(im.unit * 16 + r)] = sat_half(h);
                 } else {
-                    float* y = a.ybuf + slot * a.H + im.unit * 32 + r;
+                    float* y = (a.ydst ? a.ydst[slot] : a.ybuf + slot * a.H) + im.unit * 32 + r;
                     y[0] = s0;
                     y[16] = s1;
                 }
@@ -469,7 +471,7 @@ __device__ __forceinline__ void reduce_item(const DecodeKArgs& a, const float* _
         if (n >= ntok) continue;
         const long long slot = slot_begin + n;
         if (GU) a.hbuf[slot * a.ldh + frag_pos(unit * 16 + r)] = sat_half(__fmul_rn(silu_ref(s0[v]), s1[v & 1]));
-        else a.ybuf[slot * a.H + unit * 32 + m * 16 + r] = s0[v];
+        else (a.ydst ? a.ydst[slot] : a.ybuf + slot * a.H)[unit * 32 + m * 16 + r] = s0[v];
     }
 }
 
@@ -876,21 +878,19 @@ int launch_xprep(const __nv_bfloat16* x, __half* xp, int64_t n, int H, int natur
     return launch_status();
 }
 
-size_t decode_seg_bytes(int n, int topk, int E) {
-    const size_t P = (size_t)n * topk;
-    const size_t max_segs = (size_t)E + (P + kDecodeTokens - 1) / kDecodeTokens +
-                            ((size_t)n + kDecodeTokens - 1) / kDecodeTokens + 1;
-    const size_t old_ints = kSegHeader + 4 * (max_segs + 1);
+// slots = routed rows the lists may have to cover, n_shared = rows of the shared expert, E = routed experts
+static size_t seg_max(size_t slots, size_t n_shared, int E) {
+    return (size_t)E + (slots + kDecodeTokens - 1) / kDecodeTokens + (n_shared + kDecodeTokens - 1) / kDecodeTokens + 1;
+}
+static size_t xsegs_offset_raw(size_t slots, size_t n_shared, int E) {
+    return (kSegHeader + 4 * (seg_max(slots, n_shared, E) + 1) + 3) / 4 * 4;
+}
+size_t decode_seg_bytes_raw(size_t slots, size_t n_shared, int E) {
     const size_t x_ints = kXHeader + ((size_t)E + 1) * kXEntry + 2 * (1024 + 1);
-    return ((old_ints + 3) / 4 * 4 + x_ints) * sizeof(int);
+    return (xsegs_offset_raw(slots, n_shared, E) + x_ints) * sizeof(int);
 }
-
-static size_t xsegs_offset_ints(int n, int topk, int E) {
-    const size_t P = (size_t)n * topk;
-    const size_t max_segs = (size_t)E + (P + kDecodeTokens - 1) / kDecodeTokens +
-                            ((size_t)n + kDecodeTokens - 1) / kDecodeTokens + 1;
-    return (kSegHeader + 4 * (max_segs + 1) + 3) / 4 * 4;
-}
+size_t decode_seg_bytes(int n, int topk, int E) { return decode_seg_bytes_raw((size_t)n * topk, (size_t)n, E); }
+static size_t xsegs_offset_ints(int n, int topk, int E) { return xsegs_offset_raw((size_t)n * topk, (size_t)n, E); }
 
 constexpr size_t decode_reg_smem(int nstage, int nred) {
     return (size_t)nstage * kRStageBytes + (size_t)nred * kRRedFloats * sizeof(float) + (2 * kRMaxStages + 8) * sizeof(uint64_t) + 16;
@@ -1030,6 +1030,67 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
         combine_kernel<<<cgrid, 256, 0, s>>>(d.ybuf, d.slot_pos, d.topk_w, d.n, d.topk, d.H, P,
                                              shared ? 1 : 0, d.residual, d.out, 0);
     }
+    return launch_status();
+}
+
+// Expert parallel on the split-K kernels: the rows this GPU received (already in expert order, fragment
+// order, in xbuf rows [0, recv_cap)) through its resident experts, and its own n tokens (xbuf rows
+// [recv_cap, recv_cap + n)) through the shared expert, as ONE pair of launches.  With P = 0 the gate/up
+// kernel takes slot s from xbuf row s; the down kernel's epilogue stores every output row through ydst
+// (received rows: a row of the token's home GPU over NVLink; shared rows: this GPU's own row buffer).
+int launch_decode_ep(const DecodeEpArgs& d, cudaStream_t s) {
+    const bool shared = d.Is > 0;
+    const int imax = d.I > d.Is ? d.I : d.Is;
+    if (d.El > 1024 || d.sm_count > 1024) return GSB_ERR_UNSUPPORTED;
+    int* xsegs = d.segs + xsegs_offset_raw((size_t)d.recv_cap, (size_t)d.n, d.El);
+    seg_build_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, d.n, d.recv_cap, shared ? 1 : 0, d.segs, xsegs, d.I / 16,
+                                        shared ? d.Is / 16 : 1, d.H / 32, d.sm_count);
+    DecodeKArgs g{};
+    g.packed = reinterpret_cast<const uint8_t*>(d.gate_up_packed);
+    g.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_gate_up_packed);
+    g.segs = d.segs; g.sorted_tok = nullptr;
+    g.bsrc = d.xbuf; g.ldb = d.H; g.K = d.H; g.Ks = d.H;
+    g.units = d.I / 16; g.units_s = d.Is / 16; g.E = d.El; g.P = 0;
+    g.hbuf = d.hbuf; g.ldh = imax; g.ybuf = nullptr; g.ydst = nullptr; g.H = d.H; g.status = d.status;
+    g.xsegs = xsegs; g.x_which = 0;
+    const bool gu_reg = d.H % 2048 == 0 && d.H / 2048 <= 3;
+    if (gu_reg) {
+        const int st = launch_reg<true>(g, d.H / 2048, d.sm_count, s);
+        if (st) return st;
+    } else {
+        g.nstage = pick_stages(d.H);
+        if (!g.nstage) return GSB_ERR_UNSUPPORTED;
+        const size_t smem = decode_smem_bytes(d.H, g.nstage);
+        if (cudaFuncSetAttribute(decode_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return GSB_ERR_CUDA;
+        decode_gemm_kernel<true><<<d.sm_count, kDecodeThreads, smem, s>>>(g);
+    }
+    DecodeKArgs w = g;
+    w.packed = reinterpret_cast<const uint8_t*>(d.down_packed);
+    w.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_down_packed);
+    w.bsrc = d.hbuf; w.ldb = imax; w.K = d.I; w.Ks = shared ? d.Is : d.I;
+    w.units = d.H / 32; w.units_s = d.H / 32;
+    w.hbuf = nullptr; w.ybuf = nullptr; w.ydst = d.ydst; w.x_which = 1;
+    const bool dn_reg = d.I % 2048 == 0 && d.I / 2048 <= 3 && w.Ks == w.K;
+    if (dn_reg) {
+        const int st = launch_reg<false>(w, d.I / 2048, d.sm_count, s);
+        if (st) return st;
+    } else {
+        w.nstage = pick_stages(imax);
+        if (!w.nstage) return GSB_ERR_UNSUPPORTED;
+        const size_t smem = decode_smem_bytes(imax, w.nstage);
+        if (cudaFuncSetAttribute(decode_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return GSB_ERR_CUDA;
+        decode_gemm_kernel<false><<<d.sm_count, kDecodeThreads, smem, s>>>(w);
+    }
+    return launch_status();
+}
+
+int launch_combine_f32(const float* ybuf, const int* slot_pos, const float* topk_w, int n, int topk, int H, int P,
+                       int has_shared, const float* residual, float* out, cudaStream_t s) {
+    if (n == 0) return GSB_OK;
+    dim3 cgrid((unsigned)(((H >> 2) + 255) / 256), (unsigned)n);
+    combine_kernel<<<cgrid, 256, 0, s>>>(ybuf, slot_pos, topk_w, n, topk, H, P, has_shared, residual, out, 0);
     return launch_status();
 }
 

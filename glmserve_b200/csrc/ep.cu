@@ -1,5 +1,5 @@
 // Expert-parallel forward of one MoE layer over the GPUs of one box (host orchestration).
-// The exchange kernels live in comm.cu, the GEMMs in prefill_w4.cu.
+// The exchange kernels live in comm.cu, the GEMMs in prefill_w4.cu (tcgen05) and decode_w4.cu (split-K).
 #include "internal.cuh"
 
 using namespace gsb;
@@ -8,12 +8,17 @@ namespace {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-struct EpHeap { size_t recv_x, ybuf, total; };
+// This rank's part of the symmetric heap.  Peers never compute an address in it from their own
+// arguments: the offsets are posted with the expert counts (comm.cu).
+//   xbuf  (recv_cap + n) fp16 rows: rows received from all ranks, then (split-K path) this GPU's own tokens
+//   ybuf  (n * topk + n) rows of per-slot outputs, written by the experts' owners: fp16 (tcgen05 path) or
+//         fp32 (split-K path); sized for fp32
+struct EpHeap { size_t xbuf, ybuf, total; };
 EpHeap ep_heap(const gsb_moe_config& c, int n, int recv_cap) {
     EpHeap h{};
     size_t off = 0;
-    h.recv_x = off; off = align_up(off + (size_t)recv_cap * c.hidden * sizeof(__half), 1024);
-    h.ybuf = off;   off = align_up(off + ((size_t)n * c.topk + n) * c.hidden * sizeof(__half), 1024);
+    h.xbuf = off; off = align_up(off + ((size_t)recv_cap + n) * c.hidden * sizeof(__half), 1024);
+    h.ybuf = off; off = align_up(off + ((size_t)n * c.topk + n) * c.hidden * sizeof(float), 1024);
     h.total = off;
     return h;
 }
@@ -21,7 +26,7 @@ EpHeap ep_heap(const gsb_moe_config& c, int n, int recv_cap) {
 struct EpWs {
     int* status; float* logits; float* scores; int* ids; float* w; int* expert_offsets; int* sorted_tok;
     int* sorted_row; int* slot_pos; int* sorted_expert; int* disp_scratch; int* recv_offsets; int* send_base; void** ydst;
-    int* plan; int* tiles; int* tiles_sh;
+    int* plan; int* tiles; int* tiles_sh; int* segs;
     __half* hbuf; __half* xs_local; __half* hbuf_sh;
     size_t total;
 };
@@ -29,6 +34,7 @@ EpWs ep_carve(const gsb_moe_config& c, int n, int recv_cap, void* base) {
     EpWs ws{};
     const size_t P = (size_t)n * c.topk;
     const int El = c.n_experts / (c.ep_size > 0 ? c.ep_size : 1);
+    const size_t imax = (size_t)(c.moe_inter > c.shared_inter ? c.moe_inter : c.shared_inter);
     size_t off = 0;
     auto take = [&](size_t bytes) {
         size_t o = off;
@@ -48,15 +54,32 @@ EpWs ep_carve(const gsb_moe_config& c, int n, int recv_cap, void* base) {
     ws.disp_scratch = reinterpret_cast<int*>(take(dispatch_scratch_bytes(n, c.topk, c.n_experts)));
     ws.recv_offsets = reinterpret_cast<int*>(take((size_t)(El + 1) * sizeof(int)));
     ws.send_base = reinterpret_cast<int*>(take((size_t)c.n_experts * sizeof(int)));
-    ws.ydst = reinterpret_cast<void**>(take((size_t)recv_cap * sizeof(void*)));
+    ws.ydst = reinterpret_cast<void**>(take(((size_t)recv_cap + n) * sizeof(void*)));
     ws.plan = reinterpret_cast<int*>(take((4 + 4 * kMaxWorld) * sizeof(int)));
     ws.tiles = reinterpret_cast<int*>(take(prefill_tile_bytes(recv_cap / (c.topk > 0 ? c.topk : 1) + 1, c.topk, El)));
     ws.tiles_sh = reinterpret_cast<int*>(take(prefill_tile_bytes(n, 1, 1)));
-    ws.hbuf = reinterpret_cast<__half*>(take((size_t)recv_cap * c.moe_inter * sizeof(__half)));
+    ws.segs = reinterpret_cast<int*>(take(decode_seg_bytes_raw((size_t)recv_cap, (size_t)n, El)));
+    ws.hbuf = reinterpret_cast<__half*>(take(((size_t)recv_cap + n) * imax * sizeof(__half)));
     ws.xs_local = reinterpret_cast<__half*>(take((size_t)n * c.hidden * sizeof(__half)));
     ws.hbuf_sh = reinterpret_cast<__half*>(take((size_t)n * (c.shared_inter > 0 ? c.shared_inter : 1) * sizeof(__half)));
     ws.total = off;
     return ws;
+}
+
+// Output rows of the shared expert's slots (split-K path): this GPU's own row buffer.
+__global__ void ep_shared_dst_kernel(void** ydst, float* y_shared, int n, int H) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) ydst[t] = y_shared + (size_t)t * H;
+}
+
+// Side stream and events of the expert-parallel forward (host resources, created on first use).
+int ep_streams(gsb_moe_layer* L) {
+    if (L->ep_side) return GSB_OK;
+    if (cudaStreamCreateWithFlags(&L->ep_side, cudaStreamNonBlocking) != cudaSuccess) return GSB_ERR_CUDA;
+    if (cudaEventCreateWithFlags(&L->ep_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&L->ep_join, cudaEventDisableTiming) != cudaSuccess)
+        return GSB_ERR_CUDA;
+    return GSB_OK;
 }
 
 }  // namespace
@@ -75,26 +98,38 @@ size_t gsb_moe_ep_workspace_bytes(const gsb_moe_layer* layer, int n_tokens, int 
 
 int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, int n, float* out,
                              void* workspace, size_t workspace_bytes, size_t heap_offset, int recv_cap,
-                             int* ids_out, void* stream) {
+                             int path, int* ids_out, void* stream) {
     if (!layer || !comm || n < 0 || recv_cap <= 0) return GSB_ERR_INVALID_ARG;
     const gsb_moe_config& c = layer->cfg;
     if (c.ep_size != comm->world || c.ep_rank != comm->rank || c.ep_size < 1) return GSB_ERR_INVALID_ARG;
     if (c.n_experts % c.ep_size || !layer->tiles_ok) return GSB_ERR_UNSUPPORTED;
     if (n > 0 && (!x_bf16 || !out)) return GSB_ERR_INVALID_ARG;
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || (heap_offset & 1023)) return GSB_ERR_INVALID_ARG;
+    if (path != GSB_PATH_AUTO && path != GSB_PATH_DECODE && path != GSB_PATH_PREFILL) return GSB_ERR_INVALID_ARG;
     EpWs ws = ep_carve(c, n, recv_cap, workspace);
     if (workspace_bytes < ws.total) return GSB_ERR_WORKSPACE;
     const EpHeap hp = ep_heap(c, n, recv_cap);
     if (heap_offset + hp.total > comm->heap_bytes) return GSB_ERR_WORKSPACE;
+    int st = ep_streams(layer);
+    if (st) return st;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(x_bf16);
     const int E = c.n_experts, El = E / c.ep_size, P = n * c.topk;
+    // Every rank must take the same path (the row formats differ), so AUTO decides on recv_cap, which the
+    // ranks size alike, not on this rank's n: the split-K kernels below a capacity of 64 rows per resident
+    // expert (an average of at most 32 at the usual two-fold head-room), the tcgen05 kernels from there on.
+    if (path == GSB_PATH_AUTO) path = (int64_t)recv_cap >= 64LL * El ? GSB_PATH_PREFILL : GSB_PATH_DECODE;
+    const bool decode = path == GSB_PATH_DECODE;
     uint8_t* heap = comm->local + kCtrlBytes + heap_offset;
-    __half* recv_x = reinterpret_cast<__half*>(heap + hp.recv_x);
-    __half* ybuf = reinterpret_cast<__half*>(heap + hp.ybuf);
+    __half* xbuf = reinterpret_cast<__half*>(heap + hp.xbuf);
+    void* ybuf = heap + hp.ybuf;
 
+    cudaEvent_t* ev = nullptr;
+    if (layer->prof_ev && layer->prof_used < layer->prof_sets)
+        ev = layer->prof_ev + (size_t)(layer->prof_used++) * (GSB_N_STAGES + 1);
+    auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], s); };
+    mark(0);
     if (cudaMemsetAsync(ws.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
-    int st = GSB_OK;
     if (n > 0) {
         st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden, E, ws.logits, ws.scores, s);
         if (st) return st;
@@ -106,36 +141,76 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
     st = launch_dispatch(ws.ids, n, c.topk, E, ws.expert_offsets, ws.sorted_tok, ws.sorted_row, ws.slot_pos, s,
                          ws.disp_scratch);
     if (st) return st;
-    // counts -> plan -> push rows to their owners -> signal
+    // counts -> plan on the caller's stream; the push of this rank's rows and its signal on the side stream,
+    // so that the shared expert (local tokens only) runs while rows travel in BOTH directions
     EpExchange ex{};
     ex.x = x; ex.expert_offsets = ws.expert_offsets; ex.sorted_tok = ws.sorted_tok; ex.P = P; ex.E = E; ex.H = c.hidden;
     ex.sorted_expert = ws.sorted_expert; ex.recv_offsets = ws.recv_offsets; ex.send_base = ws.send_base; ex.ydst = ws.ydst;
-    ex.plan = ws.plan; ex.recv_off = heap_offset + hp.recv_x; ex.ybuf_off = heap_offset + hp.ybuf;
-    ex.y_elem_bytes = (int)sizeof(__half); ex.recv_cap = recv_cap; ex.frag_order = 0;
-    st = comm_ep_exchange(comm, ex, s);
+    ex.plan = ws.plan; ex.recv_off = heap_offset + hp.xbuf; ex.ybuf_off = heap_offset + hp.ybuf;
+    ex.y_elem_bytes = decode ? (int)sizeof(float) : (int)sizeof(__half); ex.recv_cap = recv_cap; ex.frag_order = decode ? 1 : 0;
+    st = comm_ep_plan(comm, ex, s);
     if (st) return st;
+    if (cudaEventRecord(layer->ep_fork, s) != cudaSuccess || cudaStreamWaitEvent(layer->ep_side, layer->ep_fork, 0) != cudaSuccess)
+        return GSB_ERR_CUDA;
+    st = comm_ep_push(comm, ex, layer->ep_side);
+    if (st) return st;
+    if (cudaEventRecord(layer->ep_join, layer->ep_side) != cudaSuccess) return GSB_ERR_CUDA;
+    mark(1);
 
-    PrefillEpArgs a{};
-    a.gate_up_packed = c.gate_up_packed; a.down_packed = c.down_packed;
-    a.shared_gate_up_packed = c.shared_gate_up_packed; a.shared_down_packed = c.shared_down_packed;
-    a.H = c.hidden; a.I = c.moe_inter; a.Is = c.shared_inter; a.El = El;
-    a.recv_offsets = ws.recv_offsets; a.recv_x = recv_x; a.recv_cap = recv_cap; a.hbuf = ws.hbuf;
-    a.ydst = reinterpret_cast<__half* const*>(ws.ydst); a.tiles = ws.tiles;
-    a.x = x; a.n = n; a.xs_local = ws.xs_local; a.hbuf_sh = ws.hbuf_sh; a.y_shared = ybuf + (size_t)P * c.hidden;
-    a.tiles_sh = ws.tiles_sh; a.status = ws.status; a.sm_count = layer->sm_count;
-
-    // the shared expert needs only local tokens: it runs while the peers' rows are in flight
-    if (n > 0) { st = launch_prefill_ep_shared(a, s); if (st) return st; }
-    st = comm_launch_wait(comm, kChDispatch, s);
-    if (st) return st;
-    st = launch_prefill_ep_routed(a, s);
-    if (st) return st;
+    if (decode) {
+        // this GPU's own tokens behind the received rows (fragment order), for the shared expert
+        if (n > 0 && c.shared_inter > 0) {
+            st = launch_xprep(x, xbuf + (size_t)recv_cap * c.hidden, n, c.hidden, 0, s);
+            if (st) return st;
+            ep_shared_dst_kernel<<<(n + 255) / 256, 256, 0, s>>>(ws.ydst + recv_cap, reinterpret_cast<float*>(ybuf) + (size_t)P * c.hidden, n, c.hidden);
+        }
+        mark(2);
+        st = comm_launch_wait(comm, kChDispatch, s);
+        if (st) return st;
+        mark(3);
+        DecodeEpArgs d{};
+        d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter; d.El = El;
+        d.gate_up_packed = c.gate_up_packed; d.down_packed = c.down_packed;
+        d.shared_gate_up_packed = c.shared_gate_up_packed; d.shared_down_packed = c.shared_down_packed;
+        d.recv_offsets = ws.recv_offsets; d.xbuf = xbuf; d.recv_cap = recv_cap; d.n = c.shared_inter > 0 ? n : 0;
+        d.hbuf = ws.hbuf; d.ydst = reinterpret_cast<float* const*>(ws.ydst); d.segs = ws.segs; d.status = ws.status;
+        d.sm_count = layer->sm_count;
+        st = launch_decode_ep(d, s);
+        if (st) return st;
+    } else {
+        PrefillEpArgs a{};
+        a.gate_up_packed = c.gate_up_packed; a.down_packed = c.down_packed;
+        a.shared_gate_up_packed = c.shared_gate_up_packed; a.shared_down_packed = c.shared_down_packed;
+        a.H = c.hidden; a.I = c.moe_inter; a.Is = c.shared_inter; a.El = El;
+        a.recv_offsets = ws.recv_offsets; a.recv_x = xbuf; a.recv_cap = recv_cap; a.hbuf = ws.hbuf;
+        a.ydst = reinterpret_cast<__half* const*>(ws.ydst); a.tiles = ws.tiles;
+        a.x = x; a.n = n; a.xs_local = ws.xs_local; a.hbuf_sh = ws.hbuf_sh;
+        a.y_shared = reinterpret_cast<__half*>(ybuf) + (size_t)P * c.hidden;
+        a.tiles_sh = ws.tiles_sh; a.status = ws.status; a.sm_count = layer->sm_count;
+        if (n > 0) { st = launch_prefill_ep_shared(a, s); if (st) return st; }
+        mark(2);
+        st = comm_launch_wait(comm, kChDispatch, s);
+        if (st) return st;
+        mark(3);
+        st = launch_prefill_ep_routed(a, s);
+        if (st) return st;
+    }
+    mark(4);
+    // this rank's pushes are part of the call: the caller's stream does not run past them
+    if (cudaStreamWaitEvent(s, layer->ep_join, 0) != cudaSuccess) return GSB_ERR_CUDA;
     ++comm->seq[kChCombine];
     st = comm_launch_signal(comm, kChCombine, s);
     if (st) return st;
     st = comm_launch_wait(comm, kChCombine, s);
     if (st) return st;
-    return launch_combine_h(ybuf, ws.slot_pos, ws.w, n, c.topk, c.hidden, P, c.shared_inter > 0 ? 1 : 0, nullptr, out, s);
+    if (decode)
+        st = launch_combine_f32(reinterpret_cast<const float*>(ybuf), ws.slot_pos, ws.w, n, c.topk, c.hidden, P,
+                                c.shared_inter > 0 ? 1 : 0, nullptr, out, s);
+    else
+        st = launch_combine_h(reinterpret_cast<const __half*>(ybuf), ws.slot_pos, ws.w, n, c.topk, c.hidden, P,
+                              c.shared_inter > 0 ? 1 : 0, nullptr, out, s);
+    mark(5);
+    return st;
 }
 
 }  // extern "C"

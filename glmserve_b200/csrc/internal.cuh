@@ -54,6 +54,9 @@ struct gsb_moe_layer {
     cudaEvent_t* prof_ev = nullptr;   // [prof_sets][GSB_N_STAGES + 1]
     int prof_sets = 0;
     int prof_used = 0;
+    // expert-parallel forward: a side stream for the dispatch push, fork/join events (created on first use)
+    cudaStream_t ep_side = nullptr;
+    cudaEvent_t ep_fork = nullptr, ep_join = nullptr;
 };
 
 namespace gsb {
@@ -68,11 +71,13 @@ struct EpExchange {
     int* recv_offsets;             // out [El + 1]
     int* send_base;                // out [E]
     void** ydst;                   // out [recv_cap]
-    int* plan;                     // out [4 + 4 * kMaxWorld]: {ok, rows received, 0, 0} then every rank's posted layout
+    int* plan;                     // out [4 + 4 * kMaxWorld]: {ok, rows received, 0, 0} then every rank's layout
+                                   // {receive offset KiB, capacity, row buffer offset KiB, 0}
     size_t recv_off, ybuf_off;     // byte offsets from the heap start (multiples of 1 KiB) of this rank's buffers
     int y_elem_bytes;              // element size of the per-slot output rows (2 = fp16, 4 = fp32)
     int recv_cap;
     int frag_order;                // 1: rows are pushed in the decode kernels' fragment order
 };
-int comm_ep_exchange(gsb_comm* c, const EpExchange& e, cudaStream_t s);
+int comm_ep_plan(gsb_comm* c, const EpExchange& e, cudaStream_t s);
+int comm_ep_push(gsb_comm* c, const EpExchange& e, cudaStream_t s);
 }  // namespace gsb

@@ -70,6 +70,7 @@ int launch_prepack(const uint8_t* a_q, const void* a_sc, const uint8_t* b_q, con
                    int scales_f32, int experts, int rows, int cols, void* out, cudaStream_t s);
 
 size_t decode_seg_bytes(int n, int topk, int E);
+size_t decode_seg_bytes_raw(size_t slots, size_t n_shared, int E);
 
 struct DecodeArgs {
     const __nv_bfloat16* x;
@@ -101,6 +102,24 @@ struct DecodeArgs {
     int xp_ready;            // 1: xp already holds the converted activations (logits launch did it)
 };
 int launch_decode_layer(const DecodeArgs& a, cudaStream_t s);
+struct DecodeEpArgs {
+    int H, I, Is, El;                   // El = experts resident on this GPU
+    const void* gate_up_packed;
+    const void* down_packed;
+    const void* shared_gate_up_packed;
+    const void* shared_down_packed;
+    const int* recv_offsets;            // [El + 1] rows received per local expert (device)
+    const __half* xbuf;                 // [recv_cap + n, H] fragment-order fp16: received rows, then this GPU's tokens
+    int recv_cap, n;
+    __half* hbuf;                       // [recv_cap + n, max(I, Is)]
+    float* const* ydst;                 // [recv_cap + n] output row of every slot (fp32)
+    int* segs;                          // decode_seg_bytes_raw(recv_cap, n, El)
+    int* status;
+    int sm_count;
+};
+int launch_decode_ep(const DecodeEpArgs& a, cudaStream_t s);
+int launch_combine_f32(const float* ybuf, const int* slot_pos, const float* topk_w, int n, int topk, int H, int P,
+                       int has_shared, const float* residual, float* out, cudaStream_t s);
 // bf16 rows -> fp16 rows in fragment order (natural = 0) or natural feature order (1)
 int launch_xprep(const __nv_bfloat16* x, __half* xp, int64_t n, int H, int natural, cudaStream_t s);
 // whether the single-block routing kernel covers this shape

@@ -12,31 +12,58 @@ from ._lib import check, lib
 
 
 class Comm:
-    """Symmetric heap + flags over all ranks of the default process group (one box)."""
+    """Symmetric heap + flags over all ranks of the default process group (one box).
 
-    def __init__(self, heap_bytes: int, allreduce_max_count: int = 0):
+    ``loopback_world``: no process group at all - a single-process communicator of that many
+    "ranks" whose peer slots all map this rank's own heap.  Nothing ever posts the peers' flags, so
+    every device-side wait runs out: the way the bounded waits are tested on one GPU."""
+
+    def __init__(self, heap_bytes: int, allreduce_max_count: int = 0, loopback_world: int = 0):
         import torch
-        import torch.distributed as dist
-        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        if loopback_world:
+            self.rank, self.world = 0, loopback_world
+            self._dist = None
+        else:
+            import torch.distributed as dist
+            self._dist = dist
+            self.rank, self.world = dist.get_rank(), dist.get_world_size()
         hb = lib().gsb_comm_handle_bytes()
         handle = (C.c_ubyte * hb)()
         h = C.c_void_p()
         check(lib().gsb_comm_create(self.rank, self.world, C.c_size_t(heap_bytes), handle, C.byref(h)), "comm_create")
         self._h = h
-        dev = torch.device("cuda", torch.cuda.current_device())
-        mine = torch.tensor(list(bytes(handle)), dtype=torch.uint8, device=dev)
-        allh = [torch.empty_like(mine) for _ in range(self.world)]
-        dist.all_gather(allh, mine)
-        buf = b"".join(bytes(t.cpu().numpy().tobytes()) for t in allh)
-        self._handles = (C.c_ubyte * len(buf)).from_buffer_copy(buf)
-        st = lib().gsb_comm_open(self._h, self._handles)
-        ok = torch.tensor([1 if st == 0 else 0], device=dev)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)          # all-or-none, like the reference's bring-up
-        if int(ok) == 0:
-            self.close()
-            raise RuntimeError("peer memory could not be opened on every rank")
+        self._dev = torch.device("cuda", torch.cuda.current_device())
+        if loopback_world:
+            check(lib().gsb_comm_open_loopback(self._h), "comm_open_loopback")
+        else:
+            dist, dev = self._dist, self._dev
+            mine = torch.tensor(list(bytes(handle)), dtype=torch.uint8, device=dev)
+            allh = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(allh, mine)
+            buf = b"".join(bytes(t.cpu().numpy().tobytes()) for t in allh)
+            self._handles = (C.c_ubyte * len(buf)).from_buffer_copy(buf)
+            st = lib().gsb_comm_open(self._h, self._handles)
+            ok = torch.tensor([1 if st == 0 else 0], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)          # all-or-none, like the reference's bring-up
+            if int(ok) == 0:
+                self.close()
+                raise RuntimeError("peer memory could not be opened on every rank")
         self.reserved = int(lib().gsb_comm_allreduce_reserve(self._h, C.c_int64(allreduce_max_count)))
-        dist.barrier()
+        if not loopback_world:
+            self._dist.barrier()
+
+    def set_wait_cycles(self, cycles: int) -> None:
+        """Budget of every device-side wait in SM clock cycles (0 = default, about two seconds)."""
+        check(lib().gsb_comm_set_wait_cycles(self._h, C.c_longlong(cycles)), "comm_set_wait_cycles")
+
+    def max_over_ranks(self, value: int) -> int:
+        """Host-side agreement on the largest ``value`` over the ranks (a small all-reduce)."""
+        if self._dist is None:
+            return int(value)
+        import torch
+        t = torch.tensor([int(value)], device=self._dev)
+        self._dist.all_reduce(t, op=self._dist.ReduceOp.MAX)
+        return int(t)
 
     def heap_bytes(self) -> int:
         return int(lib().gsb_comm_heap_bytes(self._h))
@@ -77,13 +104,43 @@ class Comm:
         self.close()
 
 
+class PeerLost(RuntimeError):
+    """A rank did not reach a step that its peers reached."""
+
+
+class StepGuard:
+    """Host-side liveness check between steps.  The device-side waits of the collectives are bounded,
+    but a rank that has left (crashed, exited, never joined) should be noticed BEFORE its peers launch
+    kernels that wait for it.  Every rank posts "I am about to run step s" in a key-value store
+    (``torch.distributed.TCPStore`` or anything with ``set`` / ``wait(keys, timeout)``) and waits a short
+    time for the others; a missing post raises ``PeerLost`` naming the rank, and the caller stops
+    launching instead of running into timeouts on the GPU.  A rank leaves only between steps."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 5.0):
+        self.store, self.rank, self.world, self.timeout_s = store, rank, world, timeout_s
+
+    def enter(self, step: int) -> None:
+        import datetime
+        self.store.set(f"gsb/step/{step}/{self.rank}", "1")
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            try:
+                self.store.wait([f"gsb/step/{step}/{r}"], datetime.timedelta(seconds=self.timeout_s))
+            except Exception as e:  # the store raises its own timeout type
+                raise PeerLost(f"rank {r} did not reach step {step} within {self.timeout_s} s") from e
+
+
 # ---- host mirrors (numpy) ------------------------------------------------------------------
 
-def ep_plan_np(cnt: np.ndarray, rank: int):
+def ep_plan_np(cnt: np.ndarray, rank: int, recv_cap: int | None = None):
     """Mirror of ep_plan_kernel.  cnt[src, e] = rows rank `src` routes to expert e.
     Returns (recv_offsets[El+1], send_base[E], src_pos[world, E]): the receive layout of `rank`
     (local expert major, then source rank), where this rank's rows for expert e start on the
-    owner's receive buffer, and where expert e's rows start in each source's sorted order."""
+    owner's receive buffer, and where expert e's rows start in each source's sorted order.
+    With ``recv_cap`` the receive offsets are clamped to it, as the kernel does on overflow: no
+    tile, intermediate row or output pointer index can then lie beyond the capacity (senders drop
+    rows whose destination row is not below the OWNER's capacity)."""
     world, E = cnt.shape
     El = E // world
     tot = cnt.sum(axis=0)
@@ -93,6 +150,8 @@ def ep_plan_np(cnt: np.ndarray, rank: int):
     send_base = base + cnt[:rank].sum(axis=0)
     recv_offsets = np.concatenate([base[rank * El:(rank + 1) * El], [base[(rank + 1) * El - 1] + tot[(rank + 1) * El - 1]]])
     src_pos = np.concatenate([np.zeros((world, 1), np.int64), np.cumsum(cnt, axis=1)[:, :-1]], axis=1)
+    if recv_cap is not None:
+        recv_offsets = np.minimum(recv_offsets, recv_cap)
     return recv_offsets.astype(np.int64), send_base.astype(np.int64), src_pos
 
 

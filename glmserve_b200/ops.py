@@ -290,15 +290,17 @@ class MoELayer:
               "moe_block_layer_forward")
         return hidden_f32
 
-    def forward_ep(self, comm, x_bf16, out=None, recv_cap=None, heap_offset=None, ids_out=None):
+    def forward_ep(self, comm, x_bf16, out=None, recv_cap=None, heap_offset=None, ids_out=None, path=PATH_AUTO):
         """Expert-parallel forward over the communicator's ranks (this layer holds the experts
-        of rank ``comm.rank``).  x bf16 [n,H] = this GPU's tokens -> out f32 [n,H]."""
+        of rank ``comm.rank``).  x bf16 [n,H] = this GPU's tokens -> out f32 [n,H].  ``path``: the
+        tcgen05 kernels, the split-K kernels, or AUTO (by ``recv_cap``); the same on every rank.
+        Without ``recv_cap`` the ranks agree on the largest n (one small all-reduce on the host)."""
         _need(x_bf16, torch.bfloat16, "x")
         n = x_bf16.shape[0]
         if out is None:
             out = torch.empty((n, self.H), dtype=torch.float32, device=x_bf16.device)
         if recv_cap is None:
-            recv_cap = n * self.topk * self.ep_size
+            recv_cap = comm.max_over_ranks(n) * self.topk * self.ep_size
         if heap_offset is None:
             heap_offset = (comm.reserved + 1023) // 1024 * 1024
         need = int(lib().gsb_moe_ep_workspace_bytes(self._h, n, recv_cap))
@@ -306,7 +308,7 @@ class MoELayer:
             self._ep_ws = torch.zeros(need + 256, dtype=torch.uint8, device=self.device)
         check(lib().gsb_moe_layer_forward_ep(self._h, comm._h, _p(x_bf16), n, _p(out), _p(self._ep_ws),
                                              C.c_size_t(self._ep_ws.numel()), C.c_size_t(heap_offset), recv_cap,
-                                             _p(ids_out), _stream()), "moe_layer_forward_ep")
+                                             path, _p(ids_out), _stream()), "moe_layer_forward_ep")
         return out
 
     def ep_heap_bytes(self, n: int, recv_cap: int) -> int:
@@ -333,6 +335,10 @@ class MoELayer:
 
 
 STAGES = ("moe.router", "moe.dispatch", "moe.gate_up", "moe.down", "moe.combine")
+# the same five marks of an expert-parallel forward: routing + count exchange + plan (the push is launched on
+# a side stream), the shared expert on local tokens, waiting for the peers' rows, the routed GEMMs (the down
+# kernel stores to the tokens' home GPUs), waiting for the returned rows + combine
+EP_STAGES = ("ep.route_plan", "ep.shared", "ep.wait_rows", "ep.routed_gemms", "ep.return_combine")
 
 
 class DenseMLP:
@@ -368,10 +374,10 @@ def profile_enable(layer: MoELayer, max_forwards: int) -> None:
     check(lib().gsb_moe_layer_profile_enable(layer._h, max_forwards), "profile_enable")
 
 
-def profile_read(layer: MoELayer) -> dict:
+def profile_read(layer: MoELayer, names=STAGES) -> dict:
     """Average stage times (ms) of the forwards since the last read; sync first."""
     torch.cuda.current_stream().synchronize()
     ms = (C.c_float * len(STAGES))()
     n = C.c_int(0)
     check(lib().gsb_moe_layer_profile_read(layer._h, ms, C.byref(n)), "profile_read")
-    return dict(forwards=n.value, **{k: float(ms[i]) for i, k in enumerate(STAGES)})
+    return dict(forwards=n.value, **{k: float(ms[i]) for i, k in enumerate(names)})

@@ -80,7 +80,7 @@ GSB_API int gsb_moe_dispatch_ws(const int* topk_ids, int n, int topk, int E, int
  * [E,moe_inter,hidden/group]; down_q u8 [E,hidden,moe_inter/2], down_sc f32
  * [E,hidden,moe_inter/group]; out f32 [n,hidden] is OVERWRITTEN with
  * sum_k w[t,k] * down(silu(gate x) * up x), slots added in order k = 0..topk-1.
- * hidden and moe_inter must be even and multiples of group. */
+ * hidden, moe_inter and group must be multiples of 8, hidden and moe_inter multiples of group. */
 GSB_API int gsb_moe_expert_ffn_w4a16(const float* x, const int* topk_ids,
                                      const float* topk_weights, const uint8_t* gate_q,
                                      const float* gate_sc, const uint8_t* up_q,
@@ -300,7 +300,10 @@ GSB_API int gsb_prefill_wait_profile(long long* device_buffer);
  *     before starting any stream capture.
  *   - all calls on a device share the one array: the call overwrites every element it later
  *     reads, so stale contents are harmless, but two calls whose kernels can overlap on the
- *     GPU (different streams, no ordering between them) race on it.  Serialise them. */
+ *     GPU (different streams, no ordering between them) race on it.  Serialise them.
+ *   - `stream` must belong to the device that is current at the call (the address looked up is that
+ *     device's), and the cached address does not survive cudaDeviceReset or a re-created primary
+ *     context: do not reset the device between calls. */
 GSB_API int gsb_moe_route_static(const void* x_bf16, const void* router_w_bf16,
                                  const float* e_bias, int n, int hidden, int E, int topk,
                                  int norm_topk, float routed_scale, int* topk_ids,
@@ -319,11 +322,23 @@ GSB_API int gsb_moe_route_static_max_floats(void);
  *   create: allocates (cudaMalloc) the local heap of heap_bytes (+ 1 MiB control area) and
  *           writes a gsb_comm_handle_bytes()-byte handle for the other ranks.
  *   open:   handles = world handles in rank order (entry [rank] ignored); all-or-none, like the
- *           reference: on failure destroy the communicator on EVERY rank. */
+ *           reference: on failure destroy the communicator on EVERY rank.
+ * Rules for every gsb_comm_* collective and for gsb_moe_layer_forward_ep: all ranks issue the same
+ * calls in the same order, each rank on ONE stream of its own (staging areas and sequence numbers are
+ * reused from call to call), on the device that was current at create; no device reset between calls;
+ * nothing else may keep the GPUs so busy that a rank's kernel cannot start while its peers wait for it
+ * (the waits are bounded, so that case ends in GSB_ERR_TIMEOUT, not in a hang). */
 typedef struct gsb_comm gsb_comm;
 GSB_API int gsb_comm_handle_bytes(void);
 GSB_API int gsb_comm_create(int rank, int world, size_t heap_bytes, void* out_handle, gsb_comm** out);
 GSB_API int gsb_comm_open(gsb_comm* comm, const void* handles);
+/* Instead of open: maps every peer slot onto this rank's OWN heap, so a single process can exercise the
+ * collectives' code paths without other GPUs - in particular the bounded waits: nothing ever posts the
+ * peers' flags, so every wait runs out and reports GSB_ERR_TIMEOUT (tests). */
+GSB_API int gsb_comm_open_loopback(gsb_comm* comm);
+/* Budget of every device-side wait of this communicator in SM clock cycles (0 = the default, about two
+ * seconds).  The reference's all-reduce spins without limit (cuda/custom_ar.cu:77-79). */
+GSB_API int gsb_comm_set_wait_cycles(gsb_comm* comm, long long cycles);
 GSB_API void gsb_comm_destroy(gsb_comm* comm);
 GSB_API void* gsb_comm_heap(gsb_comm* comm);
 GSB_API size_t gsb_comm_heap_bytes(gsb_comm* comm);
@@ -337,36 +352,44 @@ GSB_API int gsb_comm_barrier(gsb_comm* comm, void* stream);
 
 /* In-place sum of `count` floats over all ranks (count % 4 == 0, data 16-byte aligned, device
  * memory anywhere on this GPU).  Every element is summed in rank order 0..world-1, so the bits
- * do not depend on count or grid: reducing rows one by one or as one batch gives the same
- * result (what all_reduce_sum_rows guarantees in the reference).  Messages up to 2^21 / world
- * floats take a one-shot pull over NVLink, larger ones reduce-scatter + all-gather.
+ * do not depend on count, algorithm or grid: reducing rows one by one or as one batch gives the same
+ * result (what all_reduce_sum_rows guarantees in the reference).  Both forms PUSH over NVLink (a rank
+ * stores into its own slot on the peers, then a per-block flag; sums read local memory only): small
+ * messages one-shot (every rank receives every vector), larger ones reduce-scatter + all-gather.
  * gsb_comm_allreduce_reserve(max_count) must be called once (same value on every rank): it
  * returns the bytes at the START of the heap that the all-reduce staging occupies. */
 GSB_API size_t gsb_comm_allreduce_reserve(gsb_comm* comm, int64_t max_count);
 GSB_API int gsb_comm_allreduce_sum(gsb_comm* comm, float* data, int64_t count, void* stream);
-/* Algorithm switch: messages with count * world <= total_floats take the one-shot pull (every rank
- * reads every staging: least latency, world x the NVLink bytes), larger ones reduce-scatter +
- * all-gather.  0 restores the default (2^21).  Same value on every rank; both orders of summation
- * are rank 0..world-1 per element, so the result does not depend on the choice. */
+/* Algorithm switch: messages with count * world <= total_floats (and world * count <= 2 * max_count, the
+ * room the staging has) take the one-shot form, larger ones reduce-scatter + all-gather.  0 restores the
+ * default (2^18).  Same value on every rank; both orders of summation are rank 0..world-1 per element, so
+ * the result does not depend on the choice. */
 GSB_API int gsb_comm_allreduce_one_shot_limit(gsb_comm* comm, int64_t total_floats);
 
 /* Expert-parallel forward of one layer (cfg.ep_size = world): router and dispatch on this GPU's
- * n tokens, per-expert counts exchanged, rows pushed over NVLink into the owners' receive
- * buffers, grouped GEMMs over the resident experts whose down-projection epilogue stores each
- * output row straight to the token's home GPU, the shared expert on the local tokens meanwhile,
- * then the deterministic combine.  No counterpart in the reference (it has no expert
- * parallelism); results equal the single-GPU layer's bit for bit on the tcgen05 path.
- *   heap_offset: byte offset into the comm heap (same on all ranks, after the all-reduce
- *                reserve) of gsb_moe_ep_heap_bytes() bytes for the receive and return buffers.
- *   recv_cap:    rows this GPU can receive; n*topk*ep_size can never overflow. */
+ * n tokens, per-expert counts and buffer layouts exchanged, rows pushed over NVLink into the owners'
+ * receive buffers (on a side stream, while the shared expert runs on the local tokens), grouped GEMMs
+ * over the resident experts whose down-projection epilogue stores each output row straight to the
+ * token's home GPU, then the deterministic combine.  No counterpart in the reference (it has no expert
+ * parallelism).  path: GSB_PATH_PREFILL = tcgen05 kernels (results equal the single-GPU tcgen05 layer's
+ * bit for bit), GSB_PATH_DECODE = split-K kernels (equal the single-GPU split-K layer's bit for bit),
+ * GSB_PATH_AUTO = by recv_cap (split-K below 64 rows of capacity per resident expert).  All ranks must
+ * pass the same path, or AUTO with the same recv_cap.
+ *   heap_offset: byte offset into the comm heap (multiple of 1 KiB, after the all-reduce reserve) of
+ *                gsb_moe_ep_heap_bytes() bytes for the receive and return buffers.  Ranks may use
+ *                different offsets, n and recv_cap: each rank posts its own layout to its peers.
+ *   recv_cap:    rows this GPU can receive; the sum of all ranks' n * topk can never overflow.  More
+ *                rows than that: the excess is dropped, nothing is written out of bounds, and
+ *                gsb_comm_status reports GSB_ERR_TOO_LARGE. */
 GSB_API size_t gsb_moe_ep_heap_bytes(const gsb_moe_layer* layer, int n_tokens, int recv_cap);
 GSB_API size_t gsb_moe_ep_workspace_bytes(const gsb_moe_layer* layer, int n_tokens, int recv_cap);
 GSB_API int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, int n,
                                      float* out, void* workspace, size_t workspace_bytes,
-                                     size_t heap_offset, int recv_cap, int* ids_out, void* stream);
+                                     size_t heap_offset, int recv_cap, int path, int* ids_out, void* stream);
 
 /* Reads (and clears) the device status word of the last forward on this layer after the
- * caller synchronised the stream: GSB_OK or GSB_ERR_TIMEOUT.  Host call. */
+ * caller synchronised the stream: GSB_OK, or the recorded code (GSB_ERR_TIMEOUT when a bounded
+ * wait inside a kernel gave up).  Host call. */
 GSB_API int gsb_moe_layer_status(gsb_moe_layer* layer, void* workspace);
 
 #ifdef __cplusplus

@@ -136,3 +136,72 @@ def test_ep_exchange_with_two_gloo_ranks():
         assert p.exitcode == 0
     res = dict(q.get(timeout=5) for _ in range(2))
     assert res == {0: True, 1: True}
+
+
+def test_ep_plan_overflow_is_clamped_to_the_receive_capacity():
+    """More rows than a rank can receive: the receive offsets stop at the capacity, so no tile, no row of
+    the intermediate buffer and no output-pointer index derived from them lies beyond it, and the rows a
+    sender keeps (destination row below the OWNER's capacity) all fall inside the clamped layout."""
+    rng = np.random.default_rng(1)
+    world, E = 4, 16
+    El = E // world
+    cnt = rng.integers(0, 40, size=(world, E))
+    for owner in range(world):
+        total = int(cnt[:, owner * El:(owner + 1) * El].sum())
+        cap = total // 2
+        recv_off, _, _ = ep_plan_np(cnt, owner, recv_cap=cap)
+        assert recv_off[-1] == min(total, cap) and np.all(recv_off <= cap) and np.all(np.diff(recv_off) >= 0)
+        full_off, _, _ = ep_plan_np(cnt, owner)
+        for s in range(world):
+            send_base = ep_plan_np(cnt, s)[1]
+            for e in range(owner * El, (owner + 1) * El):
+                kept = [r for r in range(send_base[e], send_base[e] + cnt[s, e]) if r < cap]
+                # a kept row lies in its expert's clamped segment
+                el = e - owner * El
+                assert all(recv_off[el] <= r < max(recv_off[el + 1], recv_off[el]) or r >= recv_off[el + 1] for r in kept)
+                assert all(r < cap for r in kept)
+        # different ranks may size their buffers differently: the clamp is per owner
+        assert full_off[-1] == total
+
+
+def _guard_worker(rank, world, port, leave_after, q):
+    import datetime
+
+    import torch.distributed as dist
+    from glmserve_b200.dist import PeerLost, StepGuard
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=30))
+    guard = StepGuard(store, rank, world, timeout_s=2.0)
+    done = 0
+    try:
+        for step in range(4):
+            if rank == 1 and step == leave_after:
+                q.put((rank, "left", done))      # leaves BETWEEN steps, nothing in flight
+                return
+            guard.enter(step)
+            done += 1                            # a step's kernels would be launched here
+        q.put((rank, "finished", done))
+    except PeerLost as e:
+        q.put((rank, "peer lost: " + str(e), done))
+    finally:
+        if rank == 0:
+            import time
+            time.sleep(0.5)                      # the store's server outlives the other rank's last request
+
+
+def test_a_rank_that_leaves_between_steps_is_reported_not_waited_for():
+    """Rank 1 leaves after two steps.  Rank 0 learns of it on the host before it launches step 2 (a
+    short store wait), reports which rank is missing and stops - it does not run into the device-side
+    timeouts of kernels that would wait for the missing peer."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_guard_worker, args=(r, 2, port, 2, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    res = {r: (what, done) for r, what, done in (q.get(timeout=5) for _ in range(2))}
+    assert res[1] == ("left", 2)
+    assert res[0][0].startswith("peer lost: rank 1 did not reach step 2") and res[0][1] == 2
