@@ -374,7 +374,7 @@ def run_ours(args) -> None:
         comm.allreduce_one_shot_limit((1 << 40) if us_alg["one_shot"] <= us_alg["two_shot"] else 1)
         us_ar, us_nccl = min(us_alg["one_shot"], us_alg["two_shot"]), us_alg["nccl"]
         # tensor parallel: decode batch, gate/up column split, down row split, NVLink all-reduce
-        Ltp = shard_layer_tp_torch(Lt, rank, world, pad_to=512)
+        Ltp = shard_layer_tp_torch(Lt, rank, world)
         layer_tp = ops.MoELayer(Ltp, keep_raw=False)
         xt = make_x_torch(T, GLM["H"], seed=100, device=dev)
         ot = torch.empty((T, GLM["H"]), dtype=torch.float32, device=dev)

@@ -30,7 +30,7 @@ class MoeConfig(C.Structure):
                 ("sd_q", C.c_void_p), ("sd_sc", C.c_void_p), ("gate_up_packed", C.c_void_p),
                 ("down_packed", C.c_void_p), ("shared_gate_up_packed", C.c_void_p),
                 ("shared_down_packed", C.c_void_p), ("ep_size", C.c_int), ("ep_rank", C.c_int),
-                ("fixed_routing", C.c_int)]
+                ("fixed_routing", C.c_int), ("down_inter", C.c_int), ("shared_down_inter", C.c_int)]
 
 
 _lib = None

@@ -40,7 +40,9 @@ struct Workspace {
 Workspace carve(const gsb_moe_config& c, int n, void* base) {
     Workspace ws{};
     const size_t P = (size_t)n * c.topk;
-    const size_t imax = (size_t)(c.moe_inter > c.shared_inter ? c.moe_inter : c.shared_inter);
+    size_t imax = (size_t)(c.moe_inter > c.shared_inter ? c.moe_inter : c.shared_inter);
+    if ((size_t)c.down_inter > imax) imax = (size_t)c.down_inter;
+    if ((size_t)c.shared_down_inter > imax) imax = (size_t)c.shared_down_inter;
     size_t off = 0;
     auto take = [&](size_t bytes) {
         size_t o = off;
@@ -69,8 +71,11 @@ Workspace carve(const gsb_moe_config& c, int n, void* base) {
 
 bool tile_shapes_ok(const gsb_moe_config& c) {
     if (c.group != 128) return false;
-    if (c.hidden % 512 || c.moe_inter % 512) return false;
-    if (c.shared_inter && c.shared_inter % 512) return false;
+    // gate/up: units of 16 + 16 rows, row blocks of 64 features; every input dim in 512-column chunks
+    const int id = c.down_inter ? c.down_inter : c.moe_inter;
+    const int isd = c.shared_down_inter ? c.shared_down_inter : c.shared_inter;
+    if (c.hidden % 512 || c.moe_inter % 64 || id % 512 || id < c.moe_inter) return false;
+    if (c.shared_inter && (c.shared_inter % 64 || isd % 512 || isd < c.shared_inter)) return false;
     if (!c.gate_up_packed || !c.down_packed) return false;
     if (c.shared_inter && (!c.shared_gate_up_packed || !c.shared_down_packed)) return false;
     return true;
@@ -250,6 +255,8 @@ int gsb_moe_layer_create(const gsb_moe_config* cfg, gsb_moe_layer** out) {
     if (c.shared_inter && (c.shared_inter % c.group || c.shared_inter % 8)) return GSB_ERR_UNSUPPORTED;
     if (!c.router_w && !c.fixed_routing) return GSB_ERR_INVALID_ARG;
     if (c.fixed_routing && c.ep_size > 1) return GSB_ERR_UNSUPPORTED;
+    if (c.down_inter < 0 || c.shared_down_inter < 0) return GSB_ERR_INVALID_ARG;
+    if ((c.down_inter || c.shared_down_inter) && c.ep_size > 1) return GSB_ERR_UNSUPPORTED;
     const bool raw = c.gate_q && c.gate_sc && c.up_q && c.up_sc && c.down_q && c.down_sc;
     const bool tiles = tile_shapes_ok(c);
     if (!raw && !tiles) return GSB_ERR_INVALID_ARG;
@@ -321,6 +328,18 @@ int forward_impl(gsb_moe_layer* layer, const __nv_bfloat16* x, const float* hidd
     if (path != GSB_PATH_DIRECT && !decode_path && path != GSB_PATH_PREFILL) return GSB_ERR_INVALID_ARG;
 
     int st = GSB_OK;
+    const int Id = c.down_inter ? c.down_inter : c.moe_inter;
+    const int Isd = c.shared_inter ? (c.shared_down_inter ? c.shared_down_inter : c.shared_inter) : Id;
+    if (path != GSB_PATH_DIRECT && (Id > c.moe_inter || Isd > c.shared_inter)) {
+        // zero-weight columns of a padded down projection meet these columns of the intermediate buffer:
+        // they must hold finite numbers (0 x NaN is NaN), whatever the caller's scratch held before
+        const size_t ldh = (size_t)(Id > Isd ? Id : Isd), P = (size_t)n * c.topk;
+        if (Id > c.moe_inter && cudaMemset2DAsync(ws.hbuf + c.moe_inter, ldh * 2, 0, (ldh - c.moe_inter) * 2, P, s) != cudaSuccess)
+            return GSB_ERR_CUDA;
+        if (c.shared_inter && Isd > c.shared_inter &&
+            cudaMemset2DAsync(ws.hbuf + P * ldh + c.shared_inter, ldh * 2, 0, (ldh - c.shared_inter) * 2, (size_t)n, s) != cudaSuccess)
+            return GSB_ERR_CUDA;
+    }
     // the logits launch can leave the activations behind as fp16 rows for the expert GEMMs (an extra
     // column of blocks): fragment order for the decode kernels, natural order for the tcgen05 path
     const bool can_fuse_x = !c.fixed_routing && c.hidden % 256 == 0;
@@ -393,7 +412,7 @@ int forward_impl(gsb_moe_layer* layer, const __nv_bfloat16* x, const float* hidd
         DecodeArgs d{};
         d.force_smem_variant = path == GSB_PATH_DECODE_SMEM ? 1 : 0;
         d.x = x; d.n = n; d.topk = c.topk; d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter;
-        d.E = c.n_experts;
+        d.E = c.n_experts; d.Id = Id; d.Isd = Isd;
         d.gate_up_packed = c.gate_up_packed; d.down_packed = c.down_packed;
         d.shared_gate_up_packed = c.shared_gate_up_packed; d.shared_down_packed = c.shared_down_packed;
         d.expert_offsets = ws.expert_offsets; d.sorted_tok = ws.sorted_tok; d.slot_pos = ws.slot_pos;
@@ -414,7 +433,7 @@ int forward_impl(gsb_moe_layer* layer, const __nv_bfloat16* x, const float* hidd
     }
     PrefillArgs d{};
     d.x = x; d.n = n; d.topk = c.topk; d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter;
-    d.E = c.n_experts;
+    d.E = c.n_experts; d.Id = Id; d.Isd = Isd;
     d.gate_up_packed = c.gate_up_packed; d.down_packed = c.down_packed;
     d.shared_gate_up_packed = c.shared_gate_up_packed; d.shared_down_packed = c.shared_down_packed;
     d.expert_offsets = ws.expert_offsets; d.sorted_tok = ws.sorted_tok; d.slot_pos = ws.slot_pos;

@@ -442,42 +442,53 @@ constexpr int kRMaxStages = 6;
 // g + 8*(c>>1) of the half unit, token 2t + (c&1)).  A thread takes V adjacent lanes (same g,
 // tokens two apart), so a warp reads consecutive words of each consumer warp's block: no bank
 // conflicts, sixteen vector loads per thread.
-template <bool GU>
+template <bool GU, int UPS>
 __device__ __forceinline__ void reduce_item(const DecodeKArgs& a, const float* __restrict__ redbuf, int et,
-                                         int unit, int slot_begin, int ntok) {
+                                         int unit0, int slot_begin, int ntok) {
     constexpr int V = GU ? 2 : 4;
+    constexpr int WPU = kRConsumerWarps / UPS;           // consumer warps that split one unit's input dim
     if (et >= 64) return;
     const int q = et * V;                              // first float of the m-block(s)
     const int m = GU ? 0 : q >> 7;
     const int c = (q >> 5) & 3, L0 = q & 31;
     const int r = (L0 >> 2) + ((c >> 1) << 3);
     const int n0 = ((L0 & 3) << 1) + (c & 1);
-    const float* rbuf = redbuf + q;
-    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[2] = {0.f, 0.f};
 #pragma unroll
-    for (int w = 0; w < kRConsumerWarps; ++w) {
-        if (GU) {
-            const float2 p0 = *reinterpret_cast<const float2*>(rbuf + w * 256);
-            const float2 p1 = *reinterpret_cast<const float2*>(rbuf + w * 256 + 128);
-            s0[0] += p0.x; s0[1] += p0.y; s1[0] += p1.x; s1[1] += p1.y;
-        } else {
-            const float4 p0 = *reinterpret_cast<const float4*>(rbuf + w * 256);
-            s0[0] += p0.x; s0[1] += p0.y; s0[2] += p0.z; s0[3] += p0.w;
+    for (int us = 0; us < UPS; ++us) {                 // the units of a stage (one, unless the input dim is short)
+        const float* rbuf = redbuf + us * WPU * 256 + q;
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[2] = {0.f, 0.f};
+#pragma unroll
+        for (int w = 0; w < WPU; ++w) {
+            if (GU) {
+                const float2 p0 = *reinterpret_cast<const float2*>(rbuf + w * 256);
+                const float2 p1 = *reinterpret_cast<const float2*>(rbuf + w * 256 + 128);
+                s0[0] += p0.x; s0[1] += p0.y; s1[0] += p1.x; s1[1] += p1.y;
+            } else {
+                const float4 p0 = *reinterpret_cast<const float4*>(rbuf + w * 256);
+                s0[0] += p0.x; s0[1] += p0.y; s0[2] += p0.z; s0[3] += p0.w;
+            }
         }
-    }
+        const int unit = unit0 * UPS + us;
 #pragma unroll
-    for (int v = 0; v < V; ++v) {
-        const int n = n0 + 2 * v;
-        if (n >= ntok) continue;
-        const long long slot = slot_begin + n;
-        if (GU) a.hbuf[slot * a.ldh + frag_pos(unit * 16 + r)] = sat_half(__fmul_rn(silu_ref(s0[v]), s1[v & 1]));
-        else (a.ydst ? a.ydst[slot] : a.ybuf + slot * a.H)[unit * 32 + m * 16 + r] = s0[v];
+        for (int v = 0; v < V; ++v) {
+            const int n = n0 + 2 * v;
+            if (n >= ntok) continue;
+            const long long slot = slot_begin + n;
+            if (GU) a.hbuf[slot * a.ldh + frag_pos(unit * 16 + r)] = sat_half(__fmul_rn(silu_ref(s0[v]), s1[v & 1]));
+            else (a.ydst ? a.ydst[slot] : a.ybuf + slot * a.H)[unit * 32 + m * 16 + r] = s0[v];
+        }
     }
 }
 
-template <bool GU, int NKB>
+// UPS > 1 (NKB = 1 only): the input dim is 2048 / UPS, so a 33 KiB stage holds UPS complete units (they are
+// contiguous in the tile stream); an "item" is then a stage = UPS units, consumer warp (ck, ks) works on
+// unit ck / (4 / UPS) of the stage, and the K-split of a unit runs over 16 / UPS warps.  Without this a
+// tensor-parallel shard's 512-column down projection would be one 8 KiB chunk per item: all hand-offs.
+template <bool GU, int NKB, int UPS>
 __global__ void __launch_bounds__(RCfg<GU>::kThreads, 1)
 decode_reg_kernel(const DecodeKArgs a) {
+    static_assert(UPS == 1 || NKB == 1, "several units per stage only when a unit fits one stage");
+    constexpr int CPU = kRStageChunks / UPS;          // chunks of one unit inside a stage
     constexpr int kREpiWarps = RCfg<GU>::kEpiWarps;
     constexpr int kRed = RCfg<GU>::kRed;
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -560,7 +571,7 @@ decode_reg_kernel(const DecodeKArgs a) {
                 const uint4* src = reinterpret_cast<const uint4*>(a.bsrc + row * a.ldb);
 #pragma unroll
                 for (int st = 0; st < NKB; ++st) {
-                    const int kb = (st * kRStageChunks + ck) * 4 + ks;
+                    const int kb = (st * kRStageChunks + (UPS == 1 ? ck : ck % CPU)) * 4 + ks;
                     float sg = 0.f;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -644,7 +655,7 @@ decode_reg_kernel(const DecodeKArgs a) {
                     dead = true;
                     break;
                 }
-                reduce_item<GU>(a, red + (size_t)rb * kRRedFloats, et, unit, run.slot_begin, run.ntok);
+                reduce_item<GU, UPS>(a, red + (size_t)rb * kRRedFloats, et, unit, run.slot_begin, run.ntok);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&red_free[rb]);
                 if (++rb == (uint32_t)kRed) { rb = 0; rph ^= 1u; }
@@ -896,14 +907,15 @@ constexpr size_t decode_reg_smem(int nstage, int nred) {
     return (size_t)nstage * kRStageBytes + (size_t)nred * kRRedFloats * sizeof(float) + (2 * kRMaxStages + 8) * sizeof(uint64_t) + 16;
 }
 
+// nkb: 2048-column stages per unit (1..3), or 0 with ups = 2 / 4: units of 1024 / 512 columns, ups per stage
 template <bool GU>
-static int launch_reg(const DecodeKArgs& k, int nkb, int grid, cudaStream_t s) {
+static int launch_reg(const DecodeKArgs& k, int nkb, int grid, cudaStream_t s, int ups = 1) {
     DecodeKArgs a = k;
     a.nstage = 5;
     const size_t smem = decode_reg_smem(a.nstage, RCfg<GU>::kRed);
-#define GSB_LAUNCH_REG(N)                                                                              \
-    case N:                                                                                            \
-        if (cudaFuncSetAttribute(decode_reg_kernel<GU, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+#define GSB_LAUNCH_REG(N, U)                                                                           \
+    {                                                                                                  \
+        if (cudaFuncSetAttribute(decode_reg_kernel<GU, N, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                  (int)smem) != cudaSuccess)                                            \
             return GSB_ERR_CUDA;                                                                       \
         if (a.pdl_wait || a.pdl_wait_all) {                                                            \
@@ -914,24 +926,42 @@ static int launch_reg(const DecodeKArgs& k, int nkb, int grid, cudaStream_t s) {
             at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                             \
             at[0].val.programmaticStreamSerializationAllowed = 1;                                      \
             cfg.attrs = at; cfg.numAttrs = 1;                                                          \
-            if (cudaLaunchKernelEx(&cfg, decode_reg_kernel<GU, N>, a) != cudaSuccess) return GSB_ERR_LAUNCH; \
+            if (cudaLaunchKernelEx(&cfg, decode_reg_kernel<GU, N, U>, a) != cudaSuccess) return GSB_ERR_LAUNCH; \
         } else {                                                                                       \
-            decode_reg_kernel<GU, N><<<grid, RCfg<GU>::kThreads, smem, s>>>(a);                        \
+            decode_reg_kernel<GU, N, U><<<grid, RCfg<GU>::kThreads, smem, s>>>(a);                     \
         }                                                                                              \
-        return GSB_OK;
-    switch (nkb) {
-        GSB_LAUNCH_REG(1)
-        GSB_LAUNCH_REG(2)
-        GSB_LAUNCH_REG(3)
-        default: return GSB_ERR_UNSUPPORTED;
+        return GSB_OK;                                                                                 \
     }
+    if (ups == 1) {
+        if (nkb == 1) GSB_LAUNCH_REG(1, 1)
+        if (nkb == 2) GSB_LAUNCH_REG(2, 1)
+        if (nkb == 3) GSB_LAUNCH_REG(3, 1)
+        return GSB_ERR_UNSUPPORTED;
+    }
+    if constexpr (!GU) {   // short input dims occur for the down projection of tensor-parallel shards
+        if (ups == 2) GSB_LAUNCH_REG(1, 2)
+        if (ups == 4) GSB_LAUNCH_REG(1, 4)
+    }
+    return GSB_ERR_UNSUPPORTED;
 #undef GSB_LAUNCH_REG
+}
+
+// Register-resident form of the down kernel for this input dim: 0 = none, else units per stage.
+static int down_reg_ups(int K) {
+    if (K % 2048 == 0 && K / 2048 <= 3) return 1;
+    if (K == 1024) return 2;
+    if (K == 512) return 4;
+    return 0;
 }
 
 int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     const int P = d.n * d.topk;
     const bool shared = d.Is > 0;
-    const int imax = d.I > d.Is ? d.I : d.Is;
+    // input dims of the down projections as packed (zero-weight columns beyond I / Is, see DecodeArgs)
+    const int Id = d.Id > 0 ? d.Id : d.I, Isd = shared ? (d.Isd > 0 ? d.Isd : d.Is) : Id;
+    const int imax = Id > Isd ? Id : Isd;
+    const int ups = (!d.force_smem_variant && Isd == Id) ? down_reg_ups(Id) : 0;   // register-resident down kernel?
+    const int units_dn = ups ? (d.H / 32) / ups : d.H / 32;                         // its items per expert
     if (d.E > 1024) return GSB_ERR_UNSUPPORTED;
     if (d.sm_count > 1024) return GSB_ERR_UNSUPPORTED;
     if (!d.xp_ready) {
@@ -947,7 +977,7 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
         r.expert_offsets = const_cast<int*>(d.expert_offsets); r.sorted_tok = const_cast<int*>(d.sorted_tok);
         r.sorted_row = d.sorted_row; r.slot_pos = const_cast<int*>(d.slot_pos);
         r.has_shared = shared ? 1 : 0; r.segs = d.segs; r.xsegs = xsegs;
-        r.units_gu = d.I / 16; r.units_gu_s = shared ? d.Is / 16 : 1; r.units_dn = d.H / 32; r.grid = d.sm_count;
+        r.units_gu = d.I / 16; r.units_gu_s = shared ? d.Is / 16 : 1; r.units_dn = units_dn; r.grid = d.sm_count;
         r.status = d.status;
         const size_t smem = (size_t)(kDispWarps * d.E + 1024) * sizeof(int);   // 36 KiB at 256 experts
         cudaLaunchConfig_t cfg = {};
@@ -960,7 +990,7 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     } else {
         if (cudaMemsetAsync(d.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
         seg_build_kernel<<<1, 1024, 0, s>>>(d.expert_offsets, d.E, d.n, P, shared ? 1 : 0, d.segs, xsegs, d.I / 16,
-                                            shared ? d.Is / 16 : 1, d.H / 32, d.sm_count);
+                                            shared ? d.Is / 16 : 1, units_dn, d.sm_count);
     }
     if (d.ev_prep) cudaEventRecord(d.ev_prep, s);
 
@@ -974,7 +1004,7 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     g.xsegs = xsegs; g.x_which = 0;
     // register-resident variant when the input dim is a multiple of 2048 (at most 3 x 2048)
     const bool gu_reg = !d.force_smem_variant && d.H % 2048 == 0 && d.H / 2048 <= 3;
-    const bool dn_reg_ok = !d.force_smem_variant && d.I % 2048 == 0 && d.I / 2048 <= 3 && (!shared || d.Is == d.I);
+    const bool dn_reg_ok = ups != 0;
     const bool pdl = gu_reg && dn_reg_ok;   // both register-resident: the down kernel starts under gate/up's tail
     g.pdl_trigger = pdl ? 1 : 0;
     g.pdl_wait_all = (pdl && d.fused_route) ? 1 : 0;   // the fused routing kernel is the one that triggers
@@ -995,13 +1025,13 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
     DecodeKArgs w = g;
     w.packed = reinterpret_cast<const uint8_t*>(d.down_packed);
     w.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_down_packed);
-    w.bsrc = d.hbuf; w.ldb = imax; w.K = d.I; w.Ks = shared ? d.Is : d.I;
-    w.units = d.H / 32; w.units_s = d.H / 32;
+    w.bsrc = d.hbuf; w.ldb = imax; w.K = Id; w.Ks = Isd;
+    w.units = units_dn; w.units_s = units_dn;
     w.hbuf = nullptr; w.ybuf = d.ybuf; w.x_which = 1;
     w.pdl_trigger = pdl ? 1 : 0; w.pdl_wait = pdl ? 1 : 0; w.pdl_wait_all = 0;
-    const bool dn_reg = !d.force_smem_variant && d.I % 2048 == 0 && d.I / 2048 <= 3 && w.Ks == w.K;
+    const bool dn_reg = dn_reg_ok;
     if (dn_reg) {
-        const int st = launch_reg<false>(w, d.I / 2048, d.sm_count, s);
+        const int st = launch_reg<false>(w, ups == 1 ? Id / 2048 : 0, d.sm_count, s, ups);
         if (st) return st;
     } else {
         w.nstage = pick_stages(imax);
@@ -1042,9 +1072,11 @@ int launch_decode_ep(const DecodeEpArgs& d, cudaStream_t s) {
     const bool shared = d.Is > 0;
     const int imax = d.I > d.Is ? d.I : d.Is;
     if (d.El > 1024 || d.sm_count > 1024) return GSB_ERR_UNSUPPORTED;
+    const int ups = (!shared || d.Is == d.I) ? down_reg_ups(d.I) : 0;
+    const int units_dn = ups ? (d.H / 32) / ups : d.H / 32;
     int* xsegs = d.segs + xsegs_offset_raw((size_t)d.recv_cap, (size_t)d.n, d.El);
     seg_build_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, d.n, d.recv_cap, shared ? 1 : 0, d.segs, xsegs, d.I / 16,
-                                        shared ? d.Is / 16 : 1, d.H / 32, d.sm_count);
+                                        shared ? d.Is / 16 : 1, units_dn, d.sm_count);
     DecodeKArgs g{};
     g.packed = reinterpret_cast<const uint8_t*>(d.gate_up_packed);
     g.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_gate_up_packed);
@@ -1069,11 +1101,10 @@ int launch_decode_ep(const DecodeEpArgs& d, cudaStream_t s) {
     w.packed = reinterpret_cast<const uint8_t*>(d.down_packed);
     w.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_down_packed);
     w.bsrc = d.hbuf; w.ldb = imax; w.K = d.I; w.Ks = shared ? d.Is : d.I;
-    w.units = d.H / 32; w.units_s = d.H / 32;
+    w.units = units_dn; w.units_s = units_dn;
     w.hbuf = nullptr; w.ybuf = nullptr; w.ydst = d.ydst; w.x_which = 1;
-    const bool dn_reg = d.I % 2048 == 0 && d.I / 2048 <= 3 && w.Ks == w.K;
-    if (dn_reg) {
-        const int st = launch_reg<false>(w, d.I / 2048, d.sm_count, s);
+    if (ups) {
+        const int st = launch_reg<false>(w, ups == 1 ? d.I / 2048 : 0, d.sm_count, s, ups);
         if (st) return st;
     } else {
         w.nstage = pick_stages(imax);

@@ -75,6 +75,9 @@ size_t decode_seg_bytes_raw(size_t slots, size_t n_shared, int E);
 struct DecodeArgs {
     const __nv_bfloat16* x;
     int n, topk, H, I, Is, E;
+    int Id, Isd;             // input dims of the down projections as packed (0 = I / Is): a tensor-parallel shard
+                             // whose intermediate slice is narrower than a 512-column chunk carries zero-weight
+                             // columns beyond I / Is; the matching columns of hbuf must be finite (zeroed by the caller)
     const void* gate_up_packed;
     const void* down_packed;
     const void* shared_gate_up_packed;
@@ -130,6 +133,7 @@ size_t prefill_tile_bytes(int n, int topk, int E);
 struct PrefillArgs {
     const __nv_bfloat16* x;
     int n, topk, H, I, Is, E;
+    int Id, Isd;    // as in DecodeArgs
     const void* gate_up_packed;
     const void* down_packed;
     const void* shared_gate_up_packed;

@@ -697,7 +697,8 @@ int launch_combine_h(const __half* ybuf, const int* slot_pos, const float* topk_
 int launch_prefill_layer(const PrefillArgs& d, cudaStream_t s) {
     const int P = d.n * d.topk;
     const bool shared = d.Is > 0;
-    const int imax = d.I > d.Is ? d.I : d.Is;
+    const int Id = d.Id > 0 ? d.Id : d.I, Isd = shared ? (d.Isd > 0 ? d.Isd : d.Is) : Id;
+    const int imax = Id > Isd ? Id : Isd;
     if (d.E > 1024 || d.H % 128 || d.I % 64 || (shared && d.Is % 64)) return GSB_ERR_UNSUPPORTED;
     if (cudaMemsetAsync(d.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
     const int64_t rows = (int64_t)P + (shared ? d.n : 0);
@@ -722,7 +723,7 @@ int launch_prefill_layer(const PrefillArgs& d, cudaStream_t s) {
     w.packed = reinterpret_cast<const uint8_t*>(d.down_packed);
     w.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_down_packed);
     w.RB = d.H / 128; w.RBs = d.H / 128;
-    w.K = d.I; w.Ks = shared ? d.Is : d.I; w.units = d.H / 32; w.units_s = d.H / 32;
+    w.K = Id; w.Ks = Isd; w.units = d.H / 32; w.units_s = d.H / 32;
     w.hbuf = nullptr; w.ybuf = d.ybuf;
     const int st = run_gemm_pair(g, w, d.xs, rows, d.H, d.hbuf, rows, imax, d.sm_count, s, d.ev_gate_up);
     if (st) return st;

@@ -155,12 +155,15 @@ def ep_plan_np(cnt: np.ndarray, rank: int, recv_cap: int | None = None):
     return recv_offsets.astype(np.int64), send_base.astype(np.int64), src_pos
 
 
-def shard_layer_tp(L: dict, rank: int, tp: int, pad_to: int = 0) -> dict:
+def shard_layer_tp(L: dict, rank: int, tp: int, pad_to: int = 0, pad_down_to: int = 0) -> dict:
     """Tensor-parallel shard of a numpy layer dict, the reference's rule
     (src/model_glm52.cpp:314-422): gate/up split on their output rows (intermediate dim),
-    down on its input columns - contiguous, group-aligned slices; router replicated.  With
-    ``pad_to`` the local intermediate size is padded with zero weights (nibble 8, scale 1) up
-    to a multiple of ``pad_to`` so that the tile-stream kernels (512-column chunks) apply."""
+    down on its input columns - contiguous, group-aligned slices; router replicated.
+    ``pad_down_to``: only the down matrices' input columns are padded with zero weights (nibble 8,
+    scale 1) up to a multiple of it, so that a slice narrower than the tile stream's 512-column
+    chunk can be packed; the result carries ``Id`` / ``Isd`` (the padded dims) next to the true
+    ``I`` / ``Is``, and gate/up keep their true size.  ``pad_to`` pads gate/up rows as well (twice
+    the bytes of what is needed; kept for comparison)."""
     g = int(L["group"])
     out = dict(L)
 
@@ -168,6 +171,19 @@ def shard_layer_tp(L: dict, rank: int, tp: int, pad_to: int = 0) -> dict:
         assert I % tp == 0 and (I // tp) % g == 0, "slice must be group aligned"
         Il = I // tp
         r0, r1 = rank * Il, (rank + 1) * Il
+        if pad_down_to and not pad_to:
+            Ipd = (Il + pad_down_to - 1) // pad_down_to * pad_down_to
+            res = {}
+            for nm in (name_g, name_u):
+                res[nm + "_q"] = np.ascontiguousarray(L[nm + "_q"][..., r0:r1, :])
+                res[nm + "_sc"] = np.ascontiguousarray(L[nm + "_sc"][..., r0:r1, :])
+            q, sc = L[name_d + "_q"][..., r0 // 2:r1 // 2], L[name_d + "_sc"][..., r0 // g:r1 // g]
+            if Ipd > Il:
+                padq = np.full(q.shape[:-1] + ((Ipd - Il) // 2,), 0x88, np.uint8)
+                pads = np.ones(sc.shape[:-1] + ((Ipd - Il) // g,), np.float32)
+                q, sc = np.concatenate([q, padq], axis=-1), np.concatenate([sc, pads], axis=-1)
+            res[name_d + "_q"], res[name_d + "_sc"] = np.ascontiguousarray(q), np.ascontiguousarray(sc)
+            return res, (Il, Ipd)
         Ip = ((Il + pad_to - 1) // pad_to * pad_to) if pad_to else Il
         res = {}
         for nm in (name_g, name_u):
@@ -187,11 +203,17 @@ def shard_layer_tp(L: dict, rank: int, tp: int, pad_to: int = 0) -> dict:
 
     r, Ip = split("gate", "up", "down", int(L["I"]))
     out.update(r)
-    out["I"] = Ip
+    if isinstance(Ip, tuple):
+        out["I"], out["Id"] = Ip
+    else:
+        out["I"] = Ip
     if L.get("sg_q") is not None:
         r, Isp = split("sg", "su", "sd", int(L["Is"]))
         out.update(r)
-        out["Is"] = Isp
+        if isinstance(Isp, tuple):
+            out["Is"], out["Isd"] = Isp
+        else:
+            out["Is"] = Isp
     return out
 
 
@@ -208,7 +230,7 @@ def shard_layer_ep(L: dict, rank: int, ep: int) -> dict:
     return out
 
 
-def shard_layer_tp_torch(L: dict, rank: int, tp: int, pad_to: int = 512) -> dict:
+def shard_layer_tp_torch(L: dict, rank: int, tp: int, pad_to: int = 0, pad_down_to: int = 512) -> dict:
     """torch form of shard_layer_tp for layers generated on the GPU (scales fp16)."""
     import torch
     g = int(L["group"])
@@ -218,6 +240,17 @@ def shard_layer_tp_torch(L: dict, rank: int, tp: int, pad_to: int = 512) -> dict
         Il = I // tp
         assert I % tp == 0 and Il % g == 0
         r0, r1 = rank * Il, (rank + 1) * Il
+        if pad_down_to and not pad_to:
+            Ipd = (Il + pad_down_to - 1) // pad_down_to * pad_down_to
+            res = {}
+            for nm in (ng, nu):
+                res[nm + "_q"], res[nm + "_sc"] = L[nm + "_q"][..., r0:r1, :].contiguous(), L[nm + "_sc"][..., r0:r1, :].contiguous()
+            q, sc = L[nd + "_q"][..., r0 // 2:r1 // 2], L[nd + "_sc"][..., r0 // g:r1 // g]
+            if Ipd > Il:
+                q = torch.cat([q, torch.full(q.shape[:-1] + ((Ipd - Il) // 2,), 0x88, dtype=torch.uint8, device=q.device)], dim=-1)
+                sc = torch.cat([sc, torch.ones(sc.shape[:-1] + ((Ipd - Il) // g,), dtype=sc.dtype, device=sc.device)], dim=-1)
+            res[nd + "_q"], res[nd + "_sc"] = q.contiguous(), sc.contiguous()
+            return res, (Il, Ipd)
         Ip = (Il + pad_to - 1) // pad_to * pad_to if pad_to else Il
         res = {}
         for nm in (ng, nu):
@@ -235,9 +268,15 @@ def shard_layer_tp_torch(L: dict, rank: int, tp: int, pad_to: int = 512) -> dict
 
     r, Ip = split("gate", "up", "down", int(L["I"]))
     out.update(r)
-    out["I"] = Ip
+    if isinstance(Ip, tuple):
+        out["I"], out["Id"] = Ip
+    else:
+        out["I"] = Ip
     if L.get("sg_q") is not None:
         r, Isp = split("sg", "su", "sd", int(L["Is"]))
         out.update(r)
-        out["Is"] = Isp
+        if isinstance(Isp, tuple):
+            out["Is"], out["Isd"] = Isp
+        else:
+            out["Is"] = Isp
     return out

@@ -201,8 +201,11 @@ class MoELayer:
         self.H, self.E, self.topk, self.I, self.Is, self.group = (int(L[k]) for k in
                                                                    ("H", "E", "topk", "I", "Is", "group"))
         shared = L.get("sg_q") is not None
-        can_pack = self.group == 128 and self.H % 512 == 0 and self.I % 512 == 0 and \
-            (not shared or self.Is % 512 == 0)
+        # input dims of the down matrices as given (larger than I / Is when a tensor-parallel shard padded them)
+        self.Id = int(L.get("Id") or self.I)
+        self.Isd = int(L.get("Isd") or self.Is)
+        can_pack = self.group == 128 and self.H % 512 == 0 and self.I % 64 == 0 and self.Id % 512 == 0 and \
+            (not shared or (self.Is % 64 == 0 and self.Isd % 512 == 0))
         if prepack is None:
             prepack = can_pack
         if prepack and not can_pack:
@@ -220,6 +223,8 @@ class MoELayer:
             return t.data_ptr()
 
         cfg.fixed_routing = int(fixed_routing)
+        cfg.down_inter = self.Id if self.Id != self.I else 0
+        cfg.shared_down_inter = self.Isd if (shared and self.Isd != self.Is) else 0
         if not fixed_routing:
             cfg.router_w = hold("router_w", L["router_w"].to(torch.bfloat16).contiguous())
         if L.get("e_bias") is not None:

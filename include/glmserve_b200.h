@@ -174,7 +174,7 @@ typedef struct gsb_moe_config {
     int hidden;              /* H */
     int n_experts;           /* E routed experts resident on this GPU */
     int topk;                /* k */
-    int moe_inter;           /* I (per-expert intermediate, already /tp under TP) */
+    int moe_inter;           /* I (per-expert intermediate, already /tp under TP); tile kernels: multiple of 64 */
     int shared_inter;        /* Is, 0 = no shared expert */
     int group;               /* int4 group size along the input dim */
     int norm_topk;           /* normalise the top-k weights */
@@ -211,6 +211,12 @@ typedef struct gsb_moe_config {
      * whose intermediate dim is cut into E = topk slices is exactly such a layer: the first
      * dense layers of the model (src/model_gpu.cpp:1432-1445) run through the same kernels. */
     int fixed_routing;
+    /* Input dim of the packed down matrices when it is larger than moe_inter / shared_inter (0 = the same):
+     * a tensor-parallel shard whose intermediate slice is narrower than the 512 columns a chunk of the tile
+     * stream covers (e.g. 2048 / 8 = 256) packs its down matrices with zero weights (nibble 8) in the columns
+     * beyond moe_inter; gate/up stay unpadded.  Multiples of 512. */
+    int down_inter;
+    int shared_down_inter;
 } gsb_moe_config;
 
 typedef struct gsb_moe_layer gsb_moe_layer; /* opaque, host memory only */

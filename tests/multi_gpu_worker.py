@@ -67,7 +67,7 @@ def check_mid(comm, rank, world, dev):
     x_np = make_x_np(n, L["H"], seed=52)                # same tokens on every rank
     x = bf16_tensor(x_np, dev)
     if (L["I"] // world) % L["group"] == 0:             # the shard rule wants group-aligned slices
-        Lt = shard_layer_tp(L, rank, world, pad_to=512)
+        Lt = shard_layer_tp(L, rank, world, pad_down_to=512)
         layer_tp = ops.MoELayer(layer_to_torch(Lt, dev))
         out, logits, ids, w = layer_tp.forward(x, path=ops.PATH_DECODE, return_routing=True)
         comm.allreduce_sum(out.view(-1))
@@ -140,7 +140,7 @@ def check_glm(comm, rank, world, dev):
             assert_layer_close(got.cpu().numpy()[pick], r["out"], f"GLM-scale expert-parallel vs oracle (n={n})")
     del layer_ep
     # tensor parallel, decode batch: same tokens on every rank, local intermediate 2048 / world
-    layer_tp = ops.MoELayer(shard_layer_tp_torch(Lt, rank, world, pad_to=512), keep_raw=False)
+    layer_tp = ops.MoELayer(shard_layer_tp_torch(Lt, rank, world), keep_raw=False)
     x = make_x_torch(64, cfg["H"], seed=100, device=dev)
     dist.barrier()
     out, logits, ids, _ = layer_tp.forward(x, path=ops.PATH_DECODE, return_routing=True)

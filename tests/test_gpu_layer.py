@@ -132,6 +132,34 @@ def test_mid_config_automatic_path(dev, n):
     _check_layer(layer, L, x, dev, ops.PATH_AUTO, f"mid auto n={n}")
 
 
+@pytest.mark.parametrize("cfg_name,tp", [("wide", 2), ("wide", 4), ("wide", 8), ("mid", 4)])
+def test_tensor_parallel_shard_shapes(dev, cfg_name, tp):
+    """One rank's shard of a tensor-parallel layer (the reference's rule, src/model_glm52.cpp:363-393: gate/up
+    split on the intermediate dim, down on its input columns): the rank's partial output against the oracle
+    on the same shard.  Local intermediate sizes of 1024 and 512 take the split-K down kernel with two and
+    four units per stage; 256 and 128 are narrower than a chunk of the tile stream, so only the down matrices
+    are padded to 512 input columns with zero weights (gate/up keep their size) - and the padded columns of
+    the intermediate buffer must not leak whatever the scratch held before (it is poisoned with NaN here)."""
+    from glmserve_b200 import ops
+    from glmserve_b200.dist import shard_layer_tp
+    L = make_layer_np(CONFIGS[cfg_name], seed=61)
+    rank = tp - 1
+    Lo = shard_layer_tp(L, rank, tp)                               # what the oracle sees: no padding
+    Lk = shard_layer_tp(L, rank, tp, pad_down_to=512)              # what the kernels get
+    assert Lk["I"] == L["I"] // tp and Lk["gate_q"].shape[1] == L["I"] // tp and Lk["Id"] % 512 == 0
+    layer = ops.MoELayer(layer_to_torch(Lk, dev))
+    assert layer.prepacked
+    for n in (5, 40, 300):
+        x_np = make_x_np(n, L["H"], seed=70 + n)
+        for path in (ops.PATH_DECODE, ops.PATH_PREFILL):
+            layer._workspace(n).view(torch.float16).fill_(float("nan"))
+            out, logits, ids, w = layer.forward(bf16_tensor(x_np, dev), path=path, return_routing=True)
+            assert layer.status() == 0
+            r = oracle.moe_layer_w4(x_np, Lo, logits_in=logits.cpu().numpy())
+            assert np.array_equal(ids.cpu().numpy(), r["ids"])
+            assert_layer_close(out.cpu().numpy(), r["out"], f"{cfg_name} tp={tp} shard, n={n}, path {path}")
+
+
 def test_mid_config_without_shared_expert_and_skew(dev):
     from glmserve_b200 import ops
     L = make_layer_np(CONFIGS["mid"], seed=22, shared=False, zipf_amplitude=0.1)
