@@ -883,6 +883,34 @@ int pick_stages(int Kmax) {
 
 }  // namespace
 
+// fp32 activations (the reference's operator surface) -> fp16 rows, saturating, in either order
+__global__ void __launch_bounds__(256)
+xprep_f32_kernel(const float* __restrict__ x, __half* __restrict__ xp, int64_t n, int H, int natural) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // one 8-feature group each
+    const int gpr = H >> 3;
+    if (i >= n * gpr) return;
+    const int64_t row = i / gpr;
+    const int grp = (int)(i - row * gpr);
+    const float4* src = reinterpret_cast<const float4*>(x + row * H) + 2 * grp;
+    const float4 a = __ldg(src), b = __ldg(src + 1);
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    uint4 o;
+    uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const __half2 h = __halves2half2(sat_half(v[2 * q]), sat_half(v[2 * q + 1]));
+        op[q] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(xp + row * H + (natural ? (grp << 3) : frag_pos(grp << 3))) = o;
+}
+
+int launch_xprep_f32(const float* x, __half* xp, int64_t n, int H, int natural, cudaStream_t s) {
+    if (n == 0) return GSB_OK;
+    if (H % 8 || (reinterpret_cast<uintptr_t>(x) & 15)) return GSB_ERR_UNSUPPORTED;
+    xprep_f32_kernel<<<(unsigned)((n * (H >> 3) + 255) / 256), 256, 0, s>>>(x, xp, n, H, natural);
+    return launch_status();
+}
+
 int launch_xprep(const __nv_bfloat16* x, __half* xp, int64_t n, int H, int natural, cudaStream_t s) {
     if (n == 0) return GSB_OK;
     xprep_kernel<<<(unsigned)((n * (H >> 3) + 255) / 256), 256, 0, s>>>(x, xp, n, H, natural);
@@ -1114,6 +1142,35 @@ int launch_decode_ep(const DecodeEpArgs& d, cudaStream_t s) {
             return GSB_ERR_CUDA;
         decode_gemm_kernel<false><<<d.sm_count, kDecodeThreads, smem, s>>>(w);
     }
+    return launch_status();
+}
+
+// A dense W4A16 projection y[n, rows] = x[n, K] W^T on the split-K down kernel: W packed like one expert's
+// down matrix, the n rows as one expert's tokens (xf: fp16 rows in fragment order), fp32 rows out.
+// zero2: two zero ints (the dispatch offsets of a routed expert without tokens).
+int launch_decode_dense(const void* packed, const __half* xf, int n, int K, int rows, float* y, int* segs,
+                        const int* zero2, int* status, int sm_count, cudaStream_t s) {
+    if (n == 0) return GSB_OK;
+    if (K % 512 || rows % 32 || sm_count > 1024) return GSB_ERR_UNSUPPORTED;
+    const int ups = down_reg_ups(K);
+    if (ups > 1 && (rows / 32) % ups) return GSB_ERR_UNSUPPORTED;
+    const int units = ups ? (rows / 32) / ups : rows / 32;
+    int* xsegs = segs + xsegs_offset_raw(0, (size_t)n, 1);
+    if (cudaMemsetAsync(status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
+    seg_build_kernel<<<1, 1024, 0, s>>>(zero2, 1, n, 0, 1, segs, xsegs, 1, 1, units, sm_count);
+    DecodeKArgs w{};
+    w.packed = nullptr; w.shared_packed = reinterpret_cast<const uint8_t*>(packed);
+    w.segs = segs; w.sorted_tok = nullptr; w.bsrc = xf; w.ldb = K; w.K = K; w.Ks = K;
+    w.units = units; w.units_s = units; w.E = 1; w.P = 0;
+    w.hbuf = nullptr; w.ybuf = y; w.ydst = nullptr; w.H = rows; w.status = status;
+    w.xsegs = xsegs; w.x_which = 1;
+    if (ups) return launch_reg<false>(w, ups == 1 ? K / 2048 : 0, sm_count, s, ups);
+    w.nstage = pick_stages(K);
+    if (!w.nstage) return GSB_ERR_UNSUPPORTED;
+    const size_t smem = decode_smem_bytes(K, w.nstage);
+    if (cudaFuncSetAttribute(decode_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return GSB_ERR_CUDA;
+    decode_gemm_kernel<false><<<sm_count, kDecodeThreads, smem, s>>>(w);
     return launch_status();
 }
 

@@ -197,6 +197,15 @@ __global__ void add_inplace_kernel(float* y, const float* x, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) y[i] = __fadd_rn(y[i], x[i]);
 }
+__global__ void add_bias_rows_kernel(float* y, const float* __restrict__ bias, int64_t total, int64_t cols) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) y[i] = __fadd_rn(y[i], bias[i % cols]);
+}
+int launch_add_bias_rows(float* y, const float* bias, int64_t n, int64_t cols, cudaStream_t s) {
+    if (n * cols == 0) return GSB_OK;
+    add_bias_rows_kernel<<<(unsigned)((n * cols + 255) / 256), 256, 0, s>>>(y, bias, n * cols, cols);
+    return launch_status();
+}
 int launch_silu_mul(const float* g, const float* u, float* out, int64_t n, cudaStream_t s) {
     if (n == 0) return GSB_OK;
     silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(g, u, out, n);

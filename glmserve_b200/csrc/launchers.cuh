@@ -125,6 +125,10 @@ int launch_combine_f32(const float* ybuf, const int* slot_pos, const float* topk
                        int has_shared, const float* residual, float* out, cudaStream_t s);
 // bf16 rows -> fp16 rows in fragment order (natural = 0) or natural feature order (1)
 int launch_xprep(const __nv_bfloat16* x, __half* xp, int64_t n, int H, int natural, cudaStream_t s);
+int launch_xprep_f32(const float* x, __half* xp, int64_t n, int H, int natural, cudaStream_t s);
+int launch_decode_dense(const void* packed, const __half* xf, int n, int K, int rows, float* y, int* segs,
+                        const int* zero2, int* status, int sm_count, cudaStream_t s);
+int launch_add_bias_rows(float* y, const float* bias, int64_t n, int64_t cols, cudaStream_t s);
 // whether the single-block routing kernel covers this shape
 inline bool decode_route_fusable(int n, int topk, int E) { return n <= 128 && E <= 256 && topk <= 32 && n * topk <= 4096; }
 

@@ -113,6 +113,17 @@ def gemm_w4a16(x, qW, scales, group, bias=None):
     return y
 
 
+def operator_cache_enable(max_weight_bytes: int) -> None:
+    """Fast path behind moe_expert_ffn_w4a16 / gemm_w4a16 called with the reference's signatures: weights are
+    repacked once per set of pointers and the tile-stream kernels run (0 = off, frees everything)."""
+    check(lib().gsb_operator_cache_enable(C.c_size_t(max_weight_bytes)), "operator_cache_enable")
+
+
+def operator_cache_bytes() -> int:
+    lib().gsb_operator_cache_bytes.restype = C.c_size_t
+    return int(lib().gsb_operator_cache_bytes())
+
+
 def silu_mul(g, u):
     out = torch.empty_like(g)
     check(lib().gsb_silu_mul(_p(g), _p(u), _p(out), C.c_int64(g.numel()), _stream()), "silu_mul")

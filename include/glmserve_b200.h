@@ -102,6 +102,21 @@ GSB_API int gsb_gemm_w4a16(const float* x, const uint8_t* qW, const float* scale
                            const float* bias, float* y, int64_t n, int64_t in, int64_t out,
                            int64_t group_size, void* stream);
 
+/* A fast path behind the two signatures above, for a caller that cannot change its call sites (the
+ * reference's src/model_gpu.cpp:1460-1494, :441-445 passes the raw resident layout and fp32 activations on
+ * every call).  After gsb_operator_cache_enable(max_weight_bytes) the first call that sees a set of weight
+ * pointers repacks them ONCE into the tile stream - keyed on the pointers and shapes, so the weights must stay
+ * where they are and unchanged - and that call and every later one runs the split-K / tcgen05 kernels
+ * (group 128, hidden and moe_inter multiples of 512 for the expert FFN; group 128, in % 512 == 0,
+ * out % 128 == 0, n <= 512 for gemm_w4a16); anything else, or a cache that is full, takes the direct-layout
+ * kernels as before.  Activations are rounded from fp32 to fp16 for the tensor cores (the direct kernels
+ * keep fp32).  This is the one place where the library allocates device memory by itself: packed copies
+ * (the same size as the int4 originals) and a scratch area that grows to the largest batch seen.  0 switches
+ * it off and frees everything (device-wide synchronise).  Off by default.  One device, host calls
+ * serialised by a lock. */
+GSB_API int gsb_operator_cache_enable(size_t max_weight_bytes);
+GSB_API size_t gsb_operator_cache_bytes(void);
+
 /* Replace silu_mul / add_inplace / rmsnorm (cuda/kernels.cuh:18-19, :282-283), the glue the
  * reference runs around the shared expert and the residual (src/model_gpu.cpp:1430,
  * :1486-1502).  rmsnorm sums squares in double like the CPU reference. */

@@ -214,3 +214,64 @@ def test_prepack_matches_numpy_twin(dev, pair):
         got32 = ops.prepack_down(_t(qa, dev), _t(sa, dev))
     assert np.array_equal(got.cpu().numpy(), want)
     assert np.array_equal(got32.cpu().numpy(), want)
+
+
+def _glm_dim_experts(E=8, topk=2, seed=31):
+    cfg = dict(H=6144, E=E, topk=topk, I=2048, Is=2048, group=128)
+    return make_layer_np(cfg, seed=seed, shared=False)
+
+
+def test_expert_ffn_w4a16_operator_at_glm_dimensions(dev):
+    """moe_expert_ffn_w4a16 with the reference's own signature (raw layout, fp32 activations and scales) at
+    hidden 6144 / intermediate 2048, where the reference's kernel cannot launch (it asks for more than the
+    48 KiB of shared memory a kernel gets without opting in, cuda/moe_expert.cu:232-243): first the
+    direct-layout kernel, then - with the operator cache on - the tile-stream kernels behind the same call,
+    for a decode-sized and a prefill-sized batch; the cached call repeats bit for bit."""
+    from glmserve_b200 import ops
+    L = _glm_dim_experts()
+    args = [_t(L[k], dev) for k in ("gate_q", "gate_sc", "up_q", "up_sc", "down_q", "down_sc")]
+    for n in (8, 600):
+        x = make_x_np(n, L["H"], seed=n)
+        rng = np.random.default_rng(n)
+        ids = np.stack([rng.permutation(L["E"])[:L["topk"]] for _ in range(n)]).astype(np.int32)
+        w = rng.random((n, L["topk"])).astype(np.float32)
+        want = oracle.moe_experts_w4(x, ids, w, L)
+        xt, it, wt = _t(x, dev), _t(ids, dev), _t(w, dev)
+        if n == 8:
+            assert ops.operator_cache_bytes() == 0
+            direct = ops.moe_expert_ffn_w4a16(xt, it, wt, *args, L["group"])
+            assert_layer_close(direct.cpu().numpy(), want, "direct-layout kernel at GLM dimensions")
+        ops.operator_cache_enable(1 << 30)
+        try:
+            fast = ops.moe_expert_ffn_w4a16(xt, it, wt, *args, L["group"])
+            assert ops.operator_cache_bytes() > 0
+            assert_layer_close(fast.cpu().numpy(), want, f"cached tile-stream kernels, n={n}")
+            again = ops.moe_expert_ffn_w4a16(xt, it, wt, *args, L["group"])
+            assert torch.equal(fast, again)
+        finally:
+            ops.operator_cache_enable(0)
+        assert ops.operator_cache_bytes() == 0
+
+
+@pytest.mark.parametrize("n,inn,out,bias", [(8, 6144, 2048, False), (64, 2048, 6144, True), (5, 512, 256, True),
+                                            (33, 1536, 128, False), (1, 1024, 6144, False)])
+def test_gemm_w4a16_operator_cached_fast_path(dev, n, inn, out, bias):
+    """gemm_w4a16 with the reference's signature through the operator cache: the matrix is packed like one
+    expert's down projection and the rows run on the split-K kernel (2048-column stages, several units per
+    stage for 512 / 1024 columns, the shared-memory variant otherwise)."""
+    from glmserve_b200 import ops
+    rng = np.random.default_rng(inn + out)
+    q, s = quantize_w4_np((rng.standard_normal((out, inn)) * 0.02).astype(np.float32), 128)
+    x = rng.standard_normal((n, inn)).astype(np.float32)
+    b = rng.standard_normal(out).astype(np.float32) if bias else None
+    want = oracle.gemm_w4a16(x, q, s, 128, b)
+    ops.operator_cache_enable(1 << 28)
+    try:
+        got = ops.gemm_w4a16(_t(x, dev), _t(q, dev), _t(s, dev), 128, _t(b, dev) if bias else None)
+        assert ops.operator_cache_bytes() > 0
+        got2 = ops.gemm_w4a16(_t(x, dev), _t(q, dev), _t(s, dev), 128, _t(b, dev) if bias else None)
+    finally:
+        ops.operator_cache_enable(0)
+    g = got.cpu().numpy()
+    rel = float(np.linalg.norm(g - want) / np.linalg.norm(want))
+    assert np.isfinite(g).all() and rel <= 1e-3, f"rel-L2 {rel:.2e}"   # activations rounded to fp16
