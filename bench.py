@@ -57,7 +57,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "25",
                  "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.th = threading.Thread(target=self._read, daemon=True)
             self.th.start()
@@ -76,7 +76,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in self.rows:
             f = [c.strip() for c in r.split(",")]
@@ -86,11 +86,16 @@ class ClockSampler:
                 sm.append(float(f[1])); mx.append(float(f[2]))
             except ValueError:
                 continue
+            try:
+                pw.append(float(f[3]))
+            except ValueError:
+                pass
             for nm, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         sm.sort()
-        return dict(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=max(mx) if mx else None,
+        return dict(sm_mhz=sm[len(sm) // 2] if sm else None, sm_min_mhz=min(sm) if sm else None,
+                    sm_max_mhz=max(mx) if mx else None, power_w_max=max(pw) if pw else None,
                     reasons=sorted(reasons), samples=len(sm))
 
 
@@ -102,8 +107,12 @@ def algorithmic_bytes(ids_np, T: int) -> dict:
     wbytes = (distinct + 1) * W_EXPERT_BYTES
     total = wbytes + GLM["E"] * GLM["H"] * 2 + T * GLM["H"] * 2 + T * GLM["H"] * 4
     gate_up = (distinct + 1) * (2 * GLM["H"] * GLM["I"] // 2 + 2 * GLM["H"] * GLM["I"] // GLM["group"] * 2)
+    # what the split-K kernels actually stream: an expert once per group of 8 of its tokens, the shared expert
+    # once per group of 8 tokens of the batch
+    cnt = np.bincount(ids_np.ravel(), minlength=GLM["E"])
+    passes = int(((cnt + 7) // 8).sum() + (T + 7) // 8)
     return dict(distinct_experts=distinct, layer_bytes=total, gate_up_bytes=gate_up,
-                down_bytes=wbytes - gate_up)
+                down_bytes=wbytes - gate_up, passes=passes)
 
 
 def cpu_port_baseline(Lnp, x_np, sample_tokens: int) -> dict:
@@ -123,24 +132,29 @@ def layer_flops(T: int) -> dict:
     shared = 2 * T * 3 * GLM["H"] * GLM["Is"]
     router = 2 * T * GLM["H"] * GLM["E"]
     gate_up = 2 * (T * GLM["topk"] * 2 * GLM["H"] * GLM["I"] + T * 2 * GLM["H"] * GLM["Is"])
-    return dict(layer=routed + shared + router, gate_up=gate_up)
+    return dict(layer=routed + shared + router, gate_up=gate_up, down=gate_up // 2)
 
 
-def time_layer(layer, x, out, path, steps, warmup, barrier, ops):
-    """Device time of `steps` forwards (CUDA events on the launching stream) and the stage
-    times from the library's stage marks."""
+def time_layer(layer, x, out, path, steps, warmup, barrier, ops, batches=10):
+    """Device time of `steps` forwards (CUDA events on the launching stream, barrier + synchronise on both
+    sides), taken `batches` times back to back: the median batch is reported and all of them are returned, so a
+    number does not rest on one burst of a few milliseconds.  Plus the stage times from the library's stage
+    marks, in a pass of their own."""
     import torch
     for _ in range(max(warmup, 3)):
         layer.forward(x, out=out, path=path)
     assert layer.status() == 0, "device-side wait timed out during warm-up"
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(steps):
-        layer.forward(x, out=out, path=path)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1) / steps
+    per_step = []
+    for _ in range(batches):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            layer.forward(x, out=out, path=path)
+        e1.record()
+        barrier()
+        per_step.append(e0.elapsed_time(e1) / steps)
+    ms = sorted(per_step)[len(per_step) // 2]
     # stage marks in a pass of their own: an event recorded between two kernels keeps the second from
     # being scheduled under the first one's tail (programmatic dependent launch), which the timed
     # steps above are allowed to do
@@ -150,7 +164,55 @@ def time_layer(layer, x, out, path, steps, warmup, barrier, ops):
     stages = ops.profile_read(layer)
     ops.profile_enable(layer, 0)
     assert layer.status() == 0, "device-side wait timed out"
-    return ms, {k: v for k, v in stages.items() if k != "forwards"}
+    return ms, {k: v for k, v in stages.items() if k != "forwards"}, per_step
+
+
+def copy_same_schedule(dev, steps, batches, barrier):
+    """A plain device copy (read + write bytes, like the measured HBM peak) timed under the schedule of the
+    headline: `batches` back-to-back batches of `steps` copies of 2 GiB.  A memory-bound kernel that runs for
+    a good fraction of a second no longer sees the burst bandwidth; this is what the memory system gives a
+    copy under the same load pattern."""
+    import torch
+    a = torch.empty(1 << 30, dtype=torch.bfloat16, device=dev)
+    b = torch.empty_like(a)
+    for _ in range(3):
+        b.copy_(a)
+    gbs = []
+    for _ in range(batches):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier(); e0.record()
+        for _ in range(steps):
+            b.copy_(a)
+        e1.record(); barrier()
+        gbs.append(2 * a.numel() * 2 / (e0.elapsed_time(e1) / steps * 1e-3) / 1e9)
+    del a, b
+    torch.cuda.empty_cache()
+    return gbs
+
+
+def reference_stage_names(stages: dict, allreduce_ms=None) -> dict:
+    """The library's stage marks grouped under the names the reference's StageProf prints
+    (src/model_gpu.cpp:1451-1499): moe.router = router GEMM + top-k + dispatch; moe.experts = the grouped
+    gate/up, down and combine launches; the shared expert has no stage of its own here (it is the last
+    segment of the same grouped launches, so moe.shared is part of moe.experts); ar.mlp = the all-reduce after
+    a tensor-parallel layer."""
+    d = {"moe.router": stages["moe.router"] + stages["moe.dispatch"],
+         "moe.experts": stages["moe.gate_up"] + stages["moe.down"] + stages["moe.combine"],
+         "moe.shared": 0.0}
+    if allreduce_ms is not None:
+        d["ar.mlp"] = allreduce_ms
+    return d
+
+
+def measured_traffic(key: str):
+    """DRAM bytes of the dominant kernel per unit of work (one distinct expert for the decode kernel), from
+    the single-kernel ncu capture of a small case summarised in profiles/traffic.json; the caller scales it
+    by the units one launch of the full workload processes.  None when the file has no entry."""
+    p = os.path.join(ROOT, "profiles", "traffic.json")
+    if not os.path.exists(p):
+        return None
+    with open(p) as f:
+        return json.load(f).get(key)
 
 
 def run_ours(args) -> None:
@@ -195,7 +257,9 @@ def run_ours(args) -> None:
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    ms_step, stages = time_layer(layer, x, out, path, args.steps, args.warmup, barrier, ops)
+    ms_step, stages, batches_ms = time_layer(layer, x, out, path, args.steps, args.warmup, barrier, ops, batches=args.batches)
+
+    copy_gbs = copy_same_schedule(dev, args.steps, args.batches, barrier) if (world == 1 and not args.no_extra) else None
 
     # end to end through the host-buffer call: H2D of the step's tokens, D2H of its output
     for _ in range(3):
@@ -236,12 +300,16 @@ def run_ours(args) -> None:
         op_ = torch.empty((Tp, GLM["H"]), dtype=torch.float32, device=dev)
         _, _, ip, _ = layer_p.forward(xp, out=op_, path=ops.PATH_PREFILL, return_routing=True)
         lp = np.bincount(ip.cpu().numpy().ravel(), minlength=GLM["E"])
-        msp, stp = time_layer(layer_p, xp, op_, ops.PATH_PREFILL, 5, 3, barrier, ops)
+        msp, stp, _ = time_layer(layer_p, xp, op_, ops.PATH_PREFILL, 5, 3, barrier, ops, batches=5)
         fl = layer_flops(Tp)
         pk = peaks()
         extra["prefill_T8192"] = {"tokens_per_s": Tp / (msp * 1e-3), "ms_per_layer": msp,
                                   "tflops": fl["layer"] / (msp * 1e-3) / 1e12,
                                   "frac_of_measured_bf16_peak": fl["layer"] / (msp * 1e-3) / 1e12 / pk["bf16_tflops"],
+                                  "gate_up_kernel_tflops": fl["gate_up"] / (stp["moe.gate_up"] * 1e-3) / 1e12,
+                                  "gate_up_kernel_frac": fl["gate_up"] / (stp["moe.gate_up"] * 1e-3) / 1e12 / pk["bf16_tflops"],
+                                  "down_kernel_tflops": fl["down"] / (stp["moe.down"] * 1e-3) / 1e12,
+                                  "down_kernel_frac": fl["down"] / (stp["moe.down"] * 1e-3) / 1e12 / pk["bf16_tflops"],
                                   "stage_ms": stp, "load_max_over_mean": float(lp.max() / lp.mean()),
                                   "load_min_over_mean": float(lp.min() / lp.mean()),
                                   "routing": "Zipf(1.1)-ranked router bias, amplitude 0.04"}
@@ -251,7 +319,7 @@ def run_ours(args) -> None:
         Te = 4096
         xe = make_x_torch(Te, GLM["H"], seed=300, device=dev)
         oe = torch.empty((Te, GLM["H"]), dtype=torch.float32, device=dev)
-        mse, ste = time_layer(layer, xe, oe, ops.PATH_PREFILL, 5, 3, barrier, ops)
+        mse, ste, _ = time_layer(layer, xe, oe, ops.PATH_PREFILL, 5, 3, barrier, ops, batches=3)
         extra["ep_base_T4096"] = {"tokens_per_s": Te / (mse * 1e-3), "ms_per_layer": mse, "stage_ms": ste,
                                   "tflops": layer_flops(Te)["layer"] / (mse * 1e-3) / 1e12,
                                   "note": "one GPU holding all 256 experts, uniform routing; denominator of the "
@@ -284,6 +352,36 @@ def run_ours(args) -> None:
                                                     "kernels": best, "all_us_per_block": res,
                                                     "hbm_floor_us_per_layer_at_measured_peak": 257 * W_EXPERT_BYTES / peaks()["hbm_gbs"] / 1e3}
         del layers[1:]
+        torch.cuda.empty_cache()
+
+    # the same experts through the reference's own operator signature (raw layout, fp32 activations and scales,
+    # ids and weights from the caller): the direct-layout kernel, and the tile-stream kernels behind the
+    # operator cache (weights repacked once, keyed on their pointers)
+    if world == 1 and not args.no_extra and not prefill and T == 64 and GLM["E"] == 256:
+        n8 = 8
+        x8 = x[:n8].contiguous()
+        _, _, i8, w8 = layer.forward(x8, path=ops.PATH_DECODE, return_routing=True)
+        raw = [Lt["gate_q"], Lt["gate_sc"].float(), Lt["up_q"], Lt["up_sc"].float(), Lt["down_q"], Lt["down_sc"].float()]
+        xf = x8.float().contiguous()
+
+        def op_call():
+            return ops.moe_expert_ffn_w4a16(xf, i8.contiguous(), w8.contiguous(), *raw, GLM["group"])
+        res = {}
+        for name, cache in (("direct_layout_kernel", 0), ("operator_cache", 8 << 30)):
+            ops.operator_cache_enable(cache)
+            for _ in range(3):
+                op_call()
+            ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(); ea.record()
+            for _ in range(10):
+                op_call()
+            eb.record(); torch.cuda.synchronize()
+            res[name] = ea.elapsed_time(eb) / 10 * 1e3
+        ops.operator_cache_enable(0)
+        extra["operator_surface_moe_expert_ffn_w4a16_T8"] = {
+            "us_per_call": res, "note": "routed experts only (no router, no shared expert), 8 tokens, "
+                                        "the call src/model_gpu.cpp makes; includes the output allocation of the wrapper"}
+        del raw
         torch.cuda.empty_cache()
 
     # N > 1: the two ways the layer is partitioned over the box, on top of the replica headline
@@ -412,6 +510,7 @@ def run_ours(args) -> None:
             "exchange": "in-kernel NVLink stores: dispatch push on a side stream under the shared expert, combine "
                         "from the down-GEMM epilogue"}
         extra[f"tensor_parallel_T{T}"] = {"us_per_layer": ms_tp * 1e3, "tp": world, "allreduce_us": us_ar,
+                                          "stage_us_reference_names": {"ar.mlp": us_ar, "layer_without_ar": ms_tp * 1e3 - us_ar},
                                           "allreduce_us_by_algorithm": {k: v for k, v in us_alg.items() if k != "nccl"},
                                           "nccl_allreduce_us": us_nccl, "allreduce_floats": T * GLM["H"],
                                           "allreduce_one_row_us": us_alg_all[GLM["H"]], "status": int(st_tp)}
@@ -462,32 +561,42 @@ def run_ours(args) -> None:
             "value": world * T / (ms_step * 1e-3),
             "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3,
+            "ms_per_step": ms_step, "us_per_layer": ms_step * 1e3, "timing": f"median of {len(batches_ms)} back-to-back batches of {args.steps} steps",
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "w4a16 (int4 weights, fp16 tensor-core math, fp32 accumulate)", "data": "synthetic",
             "config": {"workload": f"GLM-scale {shape} MoE layer, T={T} tokens per GPU: hidden 6144, {GLM['E']} routed "
                                    "experts top-8, expert intermediate 2048, 1 shared expert, W4A16 group 128, "
                                    "fp16 scales, bf16 activations" + (", Zipf(1.1)-skewed routing" if prefill else ""),
                        "multi_gpu": "independent replicas (tokens shard, no collective)" if world > 1 else "single GPU",
-                       "l2": l2, "distinct_experts": alg["distinct_experts"]},
+                       "l2": l2, "distinct_experts": alg["distinct_experts"], "expert_passes": alg["passes"]},
             **whole,
             "stage_ms": stages,
+            "stage_ms_reference_names": reference_stage_names(stages),
+            "timed_batches_ms_per_step": batches_ms,
             "roofline": roof,
             "e2e": {"value": world * T / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": T * GLM["H"] * 2, "d2h_bytes_per_step": T * GLM["H"] * 4},
             # decode-sized batches: logits (+ activation conversion), fused routing, gate/up, down, combine;
-            # above 128 tokens top-k, dispatch, conversion and the work lists are launches of their own
-            "gpu_launches": (12 if prefill else (5 if T <= 128 else 8)) * args.steps,
+            # above 128 tokens top-k, dispatch and the work lists are launches of their own; the tcgen05 path:
+            # logits, top-k, 3 dispatch launches, gather, tile list, gate/up, down, combine.  All timed batches.
+            "gpu_launches": (10 if prefill else (5 if T <= 128 else 8)) * args.steps * len(batches_ms),
             "clocks": clocks,
         }
         line.update(extra)
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_port_baseline(layer_to_np(Lt), x.float().cpu().numpy(),
                                                      min(T, args.cpu_tokens))
-        # DRAM bytes per launch of the dominant kernel from the ncu launch lists summarised under
-        # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum at these exact workloads)
-        measured_traffic = {("decode", 64, 256): 3031.7e6 + 5.3e6, ("prefill", 8192, 256): 4270.5e6 + 285.4e6}
-        line["roofline"]["traffic"] = measured_traffic.get((shape, T, GLM["E"]))
+        if copy_gbs:
+            med = sorted(copy_gbs)[len(copy_gbs) // 2]
+            line["roofline"]["copy_same_schedule_gbs"] = {"median": med, "batches": copy_gbs}
+            if not prefill:
+                line["roofline"]["frac_of_copy_same_schedule"] = line["roofline"]["achieved"] / med
+        tr = measured_traffic(f"{shape}_gate_up")
+        if tr:   # scaled from a small-case capture by the units one launch processes
+            units = alg["passes"] if not prefill else 1
+            line["roofline"]["traffic"] = tr["bytes_per_unit"] * units
+            line["roofline"]["traffic_units"] = units
+            line["roofline"]["traffic_source"] = tr["source"]
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -560,6 +669,7 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=16, help="token sample of the CPU baseline leg")
     ap.add_argument("--ref-tokens", type=int, default=4, help="token sample of --impl reference")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--batches", type=int, default=10, help="timed batches of --steps forwards (the median is reported)")
     ap.add_argument("--no-extra", action="store_true", help="skip the T=1, T=8 and T=8192 legs")
     ap.add_argument("--path", default="auto", choices=["auto", "decode", "prefill"],
                     help="auto: tcgen05 grouped GEMM from 256 tokens, split-K decode kernels below")

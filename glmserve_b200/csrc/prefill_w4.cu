@@ -439,7 +439,13 @@ prefill_gemm_kernel(const PrefillKArgs a, const __grid_constant__ CUtensorMap tm
                 const int ks = kb8 >> 1, tq0 = (kb8 & 1) << 1;
                 const uint8_t* chunk = sQ + qs * kQBytes + uu * kChunkBytes;
                 const uint4* piece = reinterpret_cast<const uint4*>(chunk + (ks * 2 + m) * 1024 + h * 512 + (g * 4 + tq0) * 16);
-                const uint4 wv0 = piece[0], wv1 = piece[1];
+                // A row's two 16-byte pieces sit 64 bytes from the next row's, so eight lanes reading "their
+                // first piece" fall on two bank groups (4-way conflict).  Rows 2,3,6,7 read their second piece
+                // first: four bank groups per load, 2-way - the best this layout allows for one k-block, and
+                // it matters: the shared-memory pipe also feeds the tensor core its activation tiles.
+                const int swp = (g >> 1) & 1;
+                const uint4 wa = piece[swp], wb = piece[swp ^ 1];
+                const uint4 wv0 = swp ? wb : wa, wv1 = swp ? wa : wb;
                 const __half sc = reinterpret_cast<const __half*>(chunk + kChunkWeightBytes)[(ks * 2 + m) * 16 + g + 8 * h];
                 const __half2 s2 = __half2half2(sc);
                 const uint32_t wq[8] = {wv0.x, wv0.y, wv0.z, wv0.w, wv1.x, wv1.y, wv1.z, wv1.w};

@@ -34,6 +34,12 @@ inline int b200_last_status() {
     return st;
 }
 
+// Not in the reference: switches on the fast path behind moe_expert_ffn_w4a16 / gemm_w4a16 (weights repacked
+// once per set of pointers, tile-stream kernels from then on; see gsb_operator_cache_enable).  A maintainer
+// calls it once after the weights are uploaded (src/model_gpu.cpp:948-1000), with the bytes of int4 weights
+// the engine is willing to hold twice; without it every call runs the direct-layout kernels.
+inline void b200_enable_operator_cache(size_t max_weight_bytes) { b200_note(gsb_operator_cache_enable(max_weight_bytes)); }
+
 // cuda/kernels.cuh:243-245
 inline void moe_router(const float* logits, const float* e_bias, int n, int E, int topk,
                        bool norm_topk, float routed_scale, int* topk_ids, float* topk_weights,

@@ -22,13 +22,20 @@ _i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
 _u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 
 
+def ref_root():
+    """The reference checkout: $REF_ROOT, else a folder named ``reference`` beside this repository
+    (None when neither exists)."""
+    cand = os.environ.get("REF_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "src")) else None
+
+
 def build(with_ref: bool = True) -> None:
     """Compile liboracle.so and, when the reference tree exists, _ref/libglmref.so."""
     env = dict(os.environ, CC="gcc", CXX="g++")
     subprocess.run(["make", "-C", _HERE, "all"], check=True, env=env, capture_output=True)
-    ref_root = os.environ.get("REF_ROOT", "/root/reference")
-    if with_ref and os.path.isdir(os.path.join(ref_root, "src")):
-        subprocess.run(["make", "-C", _HERE, "ref", f"REF_ROOT={ref_root}"], check=True, env=env,
+    ref_root_ = ref_root()
+    if with_ref and ref_root_:
+        subprocess.run(["make", "-C", _HERE, "ref", f"REF_ROOT={ref_root_}"], check=True, env=env,
                        capture_output=True)
 
 

@@ -30,7 +30,9 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF_ROOT = os.environ.get("REF_ROOT", "/root/reference")
+REF_ROOT = os.environ.get("REF_ROOT") or os.path.join(os.path.dirname(ROOT), "reference")
+if not os.path.isdir(os.path.join(REF_ROOT, "tools")):
+    sys.exit("set REF_ROOT to the reference checkout (its tools/ folder is imported to generate the vectors)")
 
 import oracle  # noqa: E402
 from glmserve_b200.checkpoint import Checkpoint, SafetensorsFile, write_safetensors  # noqa: E402

@@ -48,6 +48,12 @@ def test_route_static_matches_regular_entry_points_twice_in_a_row():
         torch.cuda.synchronize()
         assert torch.equal(ids, ids_ref)
         np.testing.assert_allclose(w.cpu().numpy(), w_ref.cpu().numpy(), rtol=0, atol=1e-6)
+        # and against the CPU oracle's selection on the same logits (the regular entry points are
+        # oracle-tested elsewhere; this closes the chain for this entry point directly)
+        import oracle
+        o_ids, o_w, ties = oracle.router(logits.cpu().numpy(), None if bias is None else bias.cpu().numpy(), topk, True, 2.5)
+        assert ties == 0 and np.array_equal(ids.cpu().numpy(), o_ids)
+        np.testing.assert_allclose(w.cpu().numpy(), o_w, rtol=0, atol=1e-6)
     # beyond the built-in buffer: refused with a clear status, nothing launched
     limit = lib().gsb_moe_route_static_max_floats()
     n_big = limit // 256 + 1
