@@ -533,19 +533,39 @@ tile_list_kernel(const int* __restrict__ expert_offsets, int E, int shared_marke
 // (Fetching the rows by index in the GEMM's producer instead - TMA gather4, four 128-byte rows per
 // instruction - was built and is correct, but 48 such instructions per k-block keep the TMA unit busy
 // for ~2200 cycles against the ~380 the tensor core needs: 4x slower than this pass plus tiled loads.)
+// Two rows per block, each thread up to four 16-byte groups of each: eight independent loads are in flight
+// per thread before the first store (one load per thread left the pass bound by latency, 2.2 TB/s).
 __global__ void __launch_bounds__(256)
 gather_x_kernel(const __half* __restrict__ xh, const int* __restrict__ sorted_tok, int P,
                 int n, int H, int with_shared, __half* __restrict__ xs) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int gpr = H >> 3;
     const int64_t rows = (int64_t)P + (with_shared ? n : 0);
-    if (i >= rows * gpr) return;
-    const int64_t r = i / gpr;
-    const int grp = (int)(i - r * gpr);
-    const int64_t src = r < P ? sorted_tok[r] : r - P;
-    // streaming store: the 0.9 GB written here must not push the token-order matrix (which every row is
-    // read from top-k times) out of L2
-    __stcs(reinterpret_cast<uint4*>(xs + r * H) + grp, __ldg(reinterpret_cast<const uint4*>(xh + src * H) + grp));
+    const int64_t r0 = (int64_t)blockIdx.x * 2;
+    const uint4* sp[2];
+    uint4* dp[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const int64_t r = r0 + j < rows ? r0 + j : r0;            // an odd row count: the last block has one row
+        const int64_t src = r < P ? sorted_tok[r] : r - P;
+        sp[j] = reinterpret_cast<const uint4*>(xh + src * H);
+        dp[j] = reinterpret_cast<uint4*>(xs + r * H);
+    }
+    const int nj = r0 + 1 < rows ? 2 : 1;
+    for (int g0 = threadIdx.x; g0 < gpr; g0 += 4 * 256) {
+        uint4 v[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (j < nj && g0 + u * 256 < gpr) v[j][u] = __ldg(sp[j] + g0 + u * 256);
+        // streaming stores: the 0.9 GB written here must not push the token-order matrix (which every row is
+        // read from top-k times) out of L2
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (j < nj && g0 + u * 256 < gpr) __stcs(dp[j] + g0 + u * 256, v[j][u]);
+    }
 }
 
 // Deterministic combine over fp16 per-slot rows (same order as combine_kernel of the decode
@@ -713,8 +733,8 @@ int launch_prefill_layer(const PrefillArgs& d, cudaStream_t s) {
         const int st0 = launch_xprep(d.x, d.xh, d.n, d.H, 1, s);
         if (st0) return st0;
     }
-    gather_x_kernel<<<(unsigned)((rows * (d.H >> 3) + 255) / 256), 256, 0, s>>>(d.xh, d.sorted_tok, P, d.n, d.H,
-                                                                              shared ? 1 : 0, d.xs);
+    if (rows > 0)
+        gather_x_kernel<<<(unsigned)((rows + 1) / 2), 256, 0, s>>>(d.xh, d.sorted_tok, P, d.n, d.H, shared ? 1 : 0, d.xs);
     tile_list_kernel<<<1, 1024, 0, s>>>(d.expert_offsets, d.E, d.E, shared ? d.n : 0, P, d.tiles);
     if (d.ev_prep) cudaEventRecord(d.ev_prep, s);
 
