@@ -386,6 +386,43 @@ def test_block_of_layers_with_prenorm_and_residual(dev):
             assert_layer_close(h.cpu().numpy(), want, f"block layer {li} path {path}")
 
 
+def test_cuda_graph_replay_matches_eager_launches(dev):
+    """The layer allocates nothing and never synchronises, so a forward can be captured into a CUDA graph
+    (what a decode loop does to shed launch overhead): a replay on new token values gives the bits of
+    eager launches, on the split-K kernels, the tcgen05 kernels and the block entry point."""
+    from glmserve_b200 import ops
+    L = make_layer_np(CONFIGS["mid"], seed=41)
+    layer = ops.MoELayer(layer_to_torch(L, dev))
+    H = L["H"]
+    nw = torch.ones(H, device=dev)
+    for n, path in ((6, ops.PATH_DECODE), (300, ops.PATH_PREFILL)):
+        x = bf16_tensor(make_x_np(n, H, seed=5), dev)
+        out = torch.empty((n, H), dtype=torch.float32, device=dev)
+        hid = torch.empty((n, H), dtype=torch.float32, device=dev)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                   # warm-up off the default stream, as capture wants
+            layer.forward(x, out=out, path=path)
+            layer.block_forward(hid.zero_(), nw, 1e-5, path=path)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            layer.forward(x, out=out, path=path)
+            layer.block_forward(hid, nw, 1e-5, path=path)
+        for seed in (6, 7):                              # new values in the captured buffers
+            x2 = bf16_tensor(make_x_np(n, H, seed=seed), dev)
+            h2 = torch.from_numpy(make_x_np(n, H, seed=seed + 10)).to(dev)
+            want = layer.forward(x2, path=path).clone()
+            want_h = h2.clone()
+            layer.block_forward(want_h, nw, 1e-5, path=path)
+            x.copy_(x2); hid.copy_(h2)
+            g.replay()
+            torch.cuda.synchronize()
+            assert layer.status() == 0
+            assert torch.equal(out, want), f"graph replay differs from eager launches (n={n}, path {path})"
+            assert torch.equal(hid, want_h), f"graph replay of the block differs (n={n}, path {path})"
+
+
 def test_speculative_verify_block_glm_scale(dev):
     """The benchmarked speculative-verify block at its stated shape: 8 consecutive GLM-scale layers,
     each pre-RMSNorm (eps 1e-5, weight ~1 + N(0, 0.02)) with a residual add, on 64 x 4 = 256 tokens.
