@@ -108,27 +108,49 @@ allreduce_kernel(const ArArgs a) {
     __shared__ int ok_s;
     const int B = (int)gridDim.x, b = (int)blockIdx.x;
     float4* data = reinterpret_cast<float4*>(a.data);
+    // Every loop below first asks for all the values a thread will need in one go and only then stores or adds:
+    // written as load-store pairs, the stores (which may alias the loads for all the compiler knows) keep
+    // the next load from being issued, and a pass becomes a chain of memory round trips.
     if (!a.two_shot) {
+        constexpr int U = 4;
         const int64_t chunk = (a.count4 + B - 1) / B;
         const int64_t lo = min(a.count4, chunk * b), hi = min(a.count4, lo + chunk);
         const size_t slot_bytes = (size_t)a.count4 * sizeof(float4);
-        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-            const float4 v = data[i];
-            for (int p = 0; p < a.world; ++p)
-                if (p != a.rank) reinterpret_cast<float4*>(a.pr.base[p] + a.stage_off + a.rank * slot_bytes)[i] = v;
+        for (int64_t i0 = lo + threadIdx.x; i0 < hi; i0 += (int64_t)U * blockDim.x) {
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                if (i0 + u * (int64_t)blockDim.x < hi) v[u] = data[i0 + u * (int64_t)blockDim.x];
+            for (int p = 0; p < a.world; ++p) {
+                if (p == a.rank) continue;
+                float4* dst = reinterpret_cast<float4*>(a.pr.base[p] + a.stage_off + a.rank * slot_bytes);
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (i0 + u * (int64_t)blockDim.x < hi) dst[i0 + u * (int64_t)blockDim.x] = v[u];
+            }
         }
         if (!ar_exchange_flags(a, 0, &ok_s)) return;
         const uint8_t* mine = a.pr.base[a.rank] + a.stage_off;
-        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-            float4 v[kMaxWorld];
+        for (int64_t i0 = lo + threadIdx.x; i0 < hi; i0 += 2 * (int64_t)blockDim.x) {
+            float4 v[2][kMaxWorld];
 #pragma unroll
-            for (int r = 0; r < kMaxWorld; ++r)
-                if (r < a.world) v[r] = r == a.rank ? data[i] : ld_cg4(reinterpret_cast<const float4*>(mine + r * slot_bytes) + i);
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int u = 0; u < 2; ++u) {
+                const int64_t i = i0 + u * (int64_t)blockDim.x;
 #pragma unroll
-            for (int r = 0; r < kMaxWorld; ++r)
-                if (r < a.world) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
-            data[i] = acc;
+                for (int r = 0; r < kMaxWorld; ++r)
+                    if (i < hi && r < a.world)
+                        v[u][r] = r == a.rank ? data[i] : ld_cg4(reinterpret_cast<const float4*>(mine + r * slot_bytes) + i);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int64_t i = i0 + u * (int64_t)blockDim.x;
+                if (i >= hi) continue;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int r = 0; r < kMaxWorld; ++r)
+                    if (r < a.world) { acc.x += v[u][r].x; acc.y += v[u][r].y; acc.z += v[u][r].z; acc.w += v[u][r].w; }
+                data[i] = acc;
+            }
         }
         return;
     }
@@ -136,12 +158,22 @@ allreduce_kernel(const ArArgs a) {
     const int64_t sub = (per + B - 1) / B;                     // this block's part of a slice
     const size_t slot_bytes = (size_t)per * sizeof(float4);
     // scatter: my part of slice j goes to rank j's slot for me
-    for (int j = 0; j < a.world; ++j) {
-        if (j == a.rank) continue;
-        const int64_t slo = min(a.count4, per * j), shi = min(a.count4, slo + per);
-        const int64_t lo = min(shi, slo + sub * b), hi = min(shi, lo + sub);
-        float4* dst = reinterpret_cast<float4*>(a.pr.base[j] + a.stage_off + a.rank * slot_bytes);
-        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) dst[i - slo] = data[i];
+    for (int64_t k = threadIdx.x; k < sub; k += blockDim.x) {
+        float4 v[kMaxWorld];
+#pragma unroll
+        for (int j = 0; j < kMaxWorld; ++j) {
+            if (j >= a.world || j == a.rank) continue;
+            const int64_t slo = min(a.count4, per * j), shi = min(a.count4, slo + per);
+            const int64_t i = slo + sub * b + k;
+            if (i < shi) v[j] = data[i];
+        }
+#pragma unroll
+        for (int j = 0; j < kMaxWorld; ++j) {
+            if (j >= a.world || j == a.rank) continue;
+            const int64_t slo = min(a.count4, per * j), shi = min(a.count4, slo + per);
+            const int64_t i = slo + sub * b + k;
+            if (i < shi) reinterpret_cast<float4*>(a.pr.base[j] + a.stage_off + a.rank * slot_bytes)[i - slo] = v[j];
+        }
     }
     if (!ar_exchange_flags(a, 0, &ok_s)) return;
     {   // reduce my part of my slice in rank order, write it home and into every peer's gather area
@@ -164,11 +196,22 @@ allreduce_kernel(const ArArgs a) {
     }
     if (!ar_exchange_flags(a, 1, &ok_s)) return;
     const float4* gathered = reinterpret_cast<const float4*>(a.pr.base[a.rank] + a.stage_off + a.area_bytes);
-    for (int j = 0; j < a.world; ++j) {
-        if (j == a.rank) continue;
-        const int64_t slo = min(a.count4, per * j), shi = min(a.count4, slo + per);
-        const int64_t lo = min(shi, slo + sub * b), hi = min(shi, lo + sub);
-        for (int64_t i = lo + threadIdx.x; i < hi; i += blockDim.x) data[i] = ld_cg4(gathered + i);
+    for (int64_t k = threadIdx.x; k < sub; k += blockDim.x) {
+        float4 v[kMaxWorld];
+#pragma unroll
+        for (int j = 0; j < kMaxWorld; ++j) {
+            if (j >= a.world || j == a.rank) continue;
+            const int64_t slo = min(a.count4, per * j), shi = min(a.count4, slo + per);
+            const int64_t i = slo + sub * b + k;
+            if (i < shi) v[j] = ld_cg4(gathered + i);
+        }
+#pragma unroll
+        for (int j = 0; j < kMaxWorld; ++j) {
+            if (j >= a.world || j == a.rank) continue;
+            const int64_t slo = min(a.count4, per * j), shi = min(a.count4, slo + per);
+            const int64_t i = slo + sub * b + k;
+            if (i < shi) data[i] = v[j];
+        }
     }
 }
 
@@ -273,29 +316,106 @@ ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restric
 
 // Dispatch: every local (token, slot) row, in sorted order, is stored as fp16 into the owner's
 // receive buffer over NVLink (16-byte stores), at the offset and within the capacity the OWNER
-// posted; one block per row.  frag_order: the decode kernels' fragment order instead of natural order.
-__global__ void __launch_bounds__(256)
-ep_dispatch_push_kernel(CommPeers pr, int rank, int world, int E, const __nv_bfloat16* __restrict__ x,
-                        const int* __restrict__ expert_offsets, const int* __restrict__ sorted_tok,
-                        const int* __restrict__ send_base, const int* __restrict__ sorted_expert, int H,
-                        const int* __restrict__ plan, size_t own_recv_off, int frag_order) {
-    if (!plan[0]) return;
-    const int r = blockIdx.x;
-    const int e = sorted_expert[r];
-    const int owner = e / (E / world);
-    const int dst_row = send_base[e] + (r - expert_offsets[e]);
-    if (dst_row >= plan[4 + 4 * owner + 1]) return;     // beyond what the owner can receive
-    const size_t recv_off = owner == rank ? own_recv_off : ((size_t)plan[4 + 4 * owner + 0] << 10);
-    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)sorted_tok[r] * H);
-    __half* dst = reinterpret_cast<__half*>(pr.base[owner] + kCtrlBytes + recv_off) + (size_t)dst_row * H;
-    for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x)
-        *reinterpret_cast<uint4*>(dst + (frag_order ? frag_pos(v << 3) : (v << 3))) = bf16x8_to_half8(__ldg(src + v));
+// posted.  frag_order: the decode kernels' fragment order instead of natural order.
+// The push owns a FEW WHOLE SMs (kPushBlocks blocks whose staging buffers take most of an SM's shared memory,
+// so no GEMM CTA can sit beside them) and the shared expert's GEMMs, launched right after on the caller's
+// stream, take the others (comm_ep_push_sms).  The rows are pushed as they lie in `xh` (fp16, already in the
+// order the receiving kernels want), so the copy unit does all of it: one lane per warp runs a two-buffer
+// pipeline of bulk copies, global -> shared (completion on an mbarrier) and shared -> the owner's memory,
+// the load of one piece in flight while the previous piece is stored.  192 KiB are in flight per SM.
+// Measured on 2 and 4 GPUs with 4096 tokens each (400 MB of rows per GPU): as one block per row with 16-byte
+// stores the push filled every SM first and the GEMMs waited for it (4 GPUs: shared-expert phase 1.13 ms =
+// push 0.5 + GEMMs 0.62); as one small block per SM, sized to fit beside a GEMM CTA, it was no better
+// (1.14 ms); on 16 SMs of its own it took 0.6 ms by itself, however the bytes were moved: an SM copies
+// ~47 GB/s, and half (2 GPUs) or a quarter (4) of the rows stay on the GPU and take SM time all the same.
+constexpr int kPushWarps = 32, kPushThreads = kPushWarps * 32;
+constexpr int kDestShift = 27;                                   // row_dest = owner << 27 | row (receive capacities stay below 2^27 rows)
+constexpr int kPushChunk = 3072;                                  // bytes per staged piece
+constexpr int kPushSmem = kPushWarps * 2 * kPushChunk + kPushWarps * 2 * 8;
+__device__ __forceinline__ void bulk_s2g(void* dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__global__ void __launch_bounds__(kPushThreads, 1)
+ep_dispatch_push_kernel(CommPeers pr, int rank, int world, const __half* __restrict__ xh,
+                        const int* __restrict__ sorted_tok, const int* __restrict__ row_dest, int H, int P,
+                        const int* __restrict__ plan, size_t own_recv_off, long long wait_cycles) {
+    extern __shared__ __align__(128) uint8_t push_smem[];
+    if (!plan[0] || (threadIdx.x & 31)) return;                  // one lane per warp drives the copy unit
+    const int warp = threadIdx.x >> 5;
+    uint8_t* stage = push_smem + (size_t)warp * 2 * kPushChunk;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(push_smem + (size_t)kPushWarps * 2 * kPushChunk) + warp * 2;
+    mbar_init(&bars[0], 1); mbar_init(&bars[1], 1);
+    fence_barrier_init();
+    const int warps = (int)gridDim.x * kPushWarps;
+    const int row_bytes = H * 2;
+    // cursor over the pieces this warp sends: positions k, k + warps, ... of a row order that deals the sorted
+    // rows out over `world` equal runs (k -> (k % world) * (P / world) + k / world; the last P % world rows
+    // as they are), each row cut into pieces of kPushChunk bytes.  In sorted order all warps would send the
+    // rows of one owner after those of another - the local rows (SM-bound) in one phase, the remote rows
+    // (link-bound) in the next, 0.15 + 0.3 ms instead of the larger of the two.
+    int k = (int)blockIdx.x * kPushWarps + warp;
+    const int run = P / world, dealt = run * world;
+    int off = 0;
+    const uint8_t* src_row = nullptr;
+    uint8_t* dst_row = nullptr;
+    auto seek = [&]() -> bool {                                   // first position at or after k whose row is sent
+        for (; k < P; k += warps) {
+            const int r = k < dealt ? (k % world) * run + k / world : k;
+            const int dest = row_dest[r];
+            if (dest < 0) continue;                               // beyond what the owner can receive
+            const int owner = dest >> kDestShift;
+            const size_t recv_off = owner == rank ? own_recv_off : ((size_t)plan[4 + 4 * owner + 0] << 10);
+            src_row = reinterpret_cast<const uint8_t*>(xh) + (size_t)sorted_tok[r] * row_bytes;
+            dst_row = pr.base[owner] + kCtrlBytes + recv_off + (size_t)(dest & ((1 << kDestShift) - 1)) * row_bytes;
+            off = 0;
+            return true;
+        }
+        return false;
+    };
+    uint8_t* dstp[2];
+    uint32_t nbytes[2], ph[2] = {0u, 0u};
+    auto load = [&](int b) {                                      // the piece under the cursor into buffer b; cursor on
+        const uint32_t len = (uint32_t)min(kPushChunk, row_bytes - off);
+        dstp[b] = dst_row + off; nbytes[b] = len;
+        mbar_arrive_expect_tx(&bars[b], len);
+        bulk_g2s(stage + b * kPushChunk, src_row + off, len, &bars[b]);
+        off += (int)len;
+        if (off >= row_bytes) { k += warps; return seek(); }
+        return true;
+    };
+    if (!seek()) return;
+    bool more = load(0);
+    for (int i = 0;; ++i) {
+        const int b = i & 1;
+        const bool had_more = more;
+        if (had_more) {
+            // buffer b ^ 1 was last read by the store of piece i - 1, the only store that can be pending here
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            more = load(b ^ 1);
+        }
+        if (!mbar_wait(&bars[b], ph[b], wait_cycles)) {           // a local copy that never lands: give up, say so
+            atomicCAS(ctrl_of(pr, rank) + kStatusWord, 0, GSB_ERR_TIMEOUT);
+            break;
+        }
+        ph[b] ^= 1u;
+        bulk_s2g(dstp[b], stage + b * kPushChunk, nbytes[b]);
+        if (!had_more) break;
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every piece this lane sent has been written
 }
 
-// expert id of every sorted row (inverse of the offsets), for the push kernel
-__global__ void rows_to_expert_kernel(const int* __restrict__ expert_offsets, int E, int* __restrict__ sorted_expert) {
-    const int e = blockIdx.x;
-    for (int r = expert_offsets[e] + threadIdx.x; r < expert_offsets[e + 1]; r += blockDim.x) sorted_expert[r] = e;
+// Where every sorted row goes, for the push kernel: owner rank and row of the owner's receive buffer packed
+// into one int (-1: the owner has no room for it), from the plan's send bases and the owners' posted capacities.
+__global__ void ep_rows_dest_kernel(const int* __restrict__ expert_offsets, int E, int world,
+                                    const int* __restrict__ send_base, const int* __restrict__ plan,
+                                    int* __restrict__ row_dest) {
+    const int e = blockIdx.x, owner = e / (E / world);
+    const int base = send_base[e], cap = plan[4 + 4 * owner + 1], beg = expert_offsets[e];
+    for (int r = beg + threadIdx.x; r < expert_offsets[e + 1]; r += blockDim.x) {
+        const int dst_row = base + (r - beg);
+        row_dest[r] = dst_row < cap ? ((owner << kDestShift) | dst_row) : -1;
+    }
 }
 
 int comm_launch_signal(gsb_comm* c, int ch, cudaStream_t s) {
@@ -312,21 +432,35 @@ int comm_ep_plan(gsb_comm* c, const EpExchange& e, cudaStream_t s) {
     if (e.E > kMaxExperts || e.E % c->world) return GSB_ERR_UNSUPPORTED;
     if ((e.recv_off & 1023) || (e.ybuf_off & 1023) || (e.recv_off >> 10) > 0x7fffffff || (e.ybuf_off >> 10) > 0x7fffffff)
         return GSB_ERR_INVALID_ARG;
-    rows_to_expert_kernel<<<e.E, 128, 0, s>>>(e.expert_offsets, e.E, e.sorted_expert);
     const int seq_c = (int)++c->seq[kChCounts];
     ep_post_counts_kernel<<<1, 256, 0, s>>>(c->peers, c->rank, c->world, e.expert_offsets, e.E, seq_c,
                                             (int)(e.recv_off >> 10), e.recv_cap, (int)(e.ybuf_off >> 10));
     ep_plan_kernel<<<1, 1024, 0, s>>>(c->peers, c->rank, c->world, e.E, seq_c, e.recv_offsets, e.send_base, e.ydst,
                                       e.H, e.y_elem_bytes, e.recv_cap, (int)(e.ybuf_off >> 10), e.plan, c->wait_cycles);
+    ep_rows_dest_kernel<<<e.E, 128, 0, s>>>(e.expert_offsets, e.E, c->world, e.send_base, e.plan, e.sorted_expert);
     return launch_status();
 }
 
 // Dispatch push of this rank's rows and its signal (any stream ordered after comm_ep_plan's).  The caller
 // waits on kChDispatch before it reads its receive buffer.
+// SMs the push of P rows keeps to itself while it runs (a warp per row in flight).  An SM copies ~47 GB/s
+// (measured, plain stores and bulk copies alike, local or remote), NVLink takes ~670 GB/s per sender, and
+// (world - 1) / world of the rows are remote: with more ranks the link bounds the push and fewer SMs keep up
+// with it; with two ranks half the rows stay local and it pays to give the copy more SMs.
+int comm_ep_push_sms(int P, int world) {
+    const int blocks = world <= 2 ? 28 : (world <= 4 ? 20 : 16);
+    const int want = (P + kPushWarps - 1) / kPushWarps;
+    return want < blocks ? want : blocks;
+}
+
 int comm_ep_push(gsb_comm* c, const EpExchange& e, cudaStream_t s) {
     if (e.P > 0)
-        ep_dispatch_push_kernel<<<e.P, 256, 0, s>>>(c->peers, c->rank, c->world, e.E, e.x, e.expert_offsets, e.sorted_tok,
-                                                    e.send_base, e.sorted_expert, e.H, e.plan, e.recv_off, e.frag_order);
+    {
+        if (cudaFuncSetAttribute(ep_dispatch_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPushSmem) != cudaSuccess)
+            return GSB_ERR_CUDA;
+        ep_dispatch_push_kernel<<<comm_ep_push_sms(e.P, c->world), kPushThreads, kPushSmem, s>>>(
+            c->peers, c->rank, c->world, e.xh, e.sorted_tok, e.sorted_expert, e.H, e.P, e.plan, e.recv_off, c->wait_cycles);
+    }
     ++c->seq[kChDispatch];
     return comm_launch_signal(c, kChDispatch, s);
 }

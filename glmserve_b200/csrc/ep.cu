@@ -99,7 +99,7 @@ size_t gsb_moe_ep_workspace_bytes(const gsb_moe_layer* layer, int n_tokens, int 
 int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, int n, float* out,
                              void* workspace, size_t workspace_bytes, size_t heap_offset, int recv_cap,
                              int path, int* ids_out, void* stream) {
-    if (!layer || !comm || n < 0 || recv_cap <= 0) return GSB_ERR_INVALID_ARG;
+    if (!layer || !comm || n < 0 || recv_cap <= 0 || recv_cap >= (1 << 27)) return GSB_ERR_INVALID_ARG;
     const gsb_moe_config& c = layer->cfg;
     if (c.ep_size != comm->world || c.ep_rank != comm->rank || c.ep_size < 1) return GSB_ERR_INVALID_ARG;
     if (c.n_experts % c.ep_size || !layer->tiles_ok) return GSB_ERR_UNSUPPORTED;
@@ -124,6 +124,7 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
     __half* xbuf = reinterpret_cast<__half*>(heap + hp.xbuf);
     void* ybuf = heap + hp.ybuf;
 
+    __half* xh_local = decode ? xbuf + (size_t)recv_cap * c.hidden : ws.xs_local;
     cudaEvent_t* ev = nullptr;
     if (layer->prof_ev && layer->prof_used < layer->prof_sets)
         ev = layer->prof_ev + (size_t)(layer->prof_used++) * (GSB_N_STAGES + 1);
@@ -131,7 +132,11 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
     mark(0);
     if (cudaMemsetAsync(ws.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
     if (n > 0) {
-        st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden, E, ws.logits, ws.scores, s);
+        // the logits launch leaves this rank's tokens behind as fp16 rows in the order the receiving kernels read
+        // (fragment order behind the receive buffer for the split-K path, natural order for the tcgen05 path):
+        // the push copies them as they lie, and the shared expert reads the same rows
+        st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden, E, ws.logits, ws.scores, s,
+                                  xh_local, decode ? 0 : 1);
         if (st) return st;
         st = launch_router_topk(ws.scores, c.e_bias, n, E, c.topk, c.norm_topk, c.routed_scale, ws.ids, ws.w, s, true);
         if (st) return st;
@@ -144,10 +149,10 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
     // counts -> plan on the caller's stream; the push of this rank's rows and its signal on the side stream,
     // so that the shared expert (local tokens only) runs while rows travel in BOTH directions
     EpExchange ex{};
-    ex.x = x; ex.expert_offsets = ws.expert_offsets; ex.sorted_tok = ws.sorted_tok; ex.P = P; ex.E = E; ex.H = c.hidden;
+    ex.xh = xh_local; ex.expert_offsets = ws.expert_offsets; ex.sorted_tok = ws.sorted_tok; ex.P = P; ex.E = E; ex.H = c.hidden;
     ex.sorted_expert = ws.sorted_expert; ex.recv_offsets = ws.recv_offsets; ex.send_base = ws.send_base; ex.ydst = ws.ydst;
     ex.plan = ws.plan; ex.recv_off = heap_offset + hp.xbuf; ex.ybuf_off = heap_offset + hp.ybuf;
-    ex.y_elem_bytes = decode ? (int)sizeof(float) : (int)sizeof(__half); ex.recv_cap = recv_cap; ex.frag_order = decode ? 1 : 0;
+    ex.y_elem_bytes = decode ? (int)sizeof(float) : (int)sizeof(__half); ex.recv_cap = recv_cap;
     st = comm_ep_plan(comm, ex, s);
     if (st) return st;
     if (cudaEventRecord(layer->ep_fork, s) != cudaSuccess || cudaStreamWaitEvent(layer->ep_side, layer->ep_fork, 0) != cudaSuccess)
@@ -160,8 +165,6 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
     if (decode) {
         // this GPU's own tokens behind the received rows (fragment order), for the shared expert
         if (n > 0 && c.shared_inter > 0) {
-            st = launch_xprep(x, xbuf + (size_t)recv_cap * c.hidden, n, c.hidden, 0, s);
-            if (st) return st;
             ep_shared_dst_kernel<<<(n + 255) / 256, 256, 0, s>>>(ws.ydst + recv_cap, reinterpret_cast<float*>(ybuf) + (size_t)P * c.hidden, n, c.hidden);
         }
         mark(2);
@@ -186,12 +189,19 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
         a.ydst = reinterpret_cast<__half* const*>(ws.ydst); a.tiles = ws.tiles;
         a.x = x; a.n = n; a.xs_local = ws.xs_local; a.hbuf_sh = ws.hbuf_sh;
         a.y_shared = reinterpret_cast<__half*>(ybuf) + (size_t)P * c.hidden;
-        a.tiles_sh = ws.tiles_sh; a.status = ws.status; a.sm_count = layer->sm_count;
+        a.tiles_sh = ws.tiles_sh; a.status = ws.status;
+        // the push keeps a few SMs to itself: the shared expert's persistent CTAs take the others, or the
+        // CTAs without an SM would start their tiles only when the push is over
+        a.sm_count = layer->sm_count - comm_ep_push_sms(P, comm->world);
         if (n > 0) { st = launch_prefill_ep_shared(a, s); if (st) return st; }
         mark(2);
         st = comm_launch_wait(comm, kChDispatch, s);
         if (st) return st;
+        // the routed experts take every SM: this rank's own push has to be off them first (it normally is by
+        // the time every peer's rows have arrived)
+        if (cudaStreamWaitEvent(s, layer->ep_join, 0) != cudaSuccess) return GSB_ERR_CUDA;
         mark(3);
+        a.sm_count = layer->sm_count;
         st = launch_prefill_ep_routed(a, s);
         if (st) return st;
     }

@@ -63,11 +63,12 @@ namespace gsb {
 int comm_launch_signal(gsb_comm* c, int ch, cudaStream_t s);
 int comm_launch_wait(gsb_comm* c, int ch, cudaStream_t s);
 struct EpExchange {
-    const __nv_bfloat16* x;        // this rank's tokens [n, H]
+    const __half* xh;              // this rank's tokens [n, H] as fp16, in the feature order the receiving kernels
+                                   // read (natural for the tcgen05 path, fragment order for the split-K path)
     const int* expert_offsets;     // local dispatch [E + 1]
     const int* sorted_tok;         // [P]
     int P, E, H;
-    int* sorted_expert;            // scratch [P]
+    int* sorted_expert;            // scratch [P]: destination (owner, row) of every sorted row
     int* recv_offsets;             // out [El + 1]
     int* send_base;                // out [E]
     void** ydst;                   // out [recv_cap]
@@ -76,8 +77,8 @@ struct EpExchange {
     size_t recv_off, ybuf_off;     // byte offsets from the heap start (multiples of 1 KiB) of this rank's buffers
     int y_elem_bytes;              // element size of the per-slot output rows (2 = fp16, 4 = fp32)
     int recv_cap;
-    int frag_order;                // 1: rows are pushed in the decode kernels' fragment order
 };
 int comm_ep_plan(gsb_comm* c, const EpExchange& e, cudaStream_t s);
 int comm_ep_push(gsb_comm* c, const EpExchange& e, cudaStream_t s);
+int comm_ep_push_sms(int P, int world);   // SMs that push occupies by itself while it runs
 }  // namespace gsb

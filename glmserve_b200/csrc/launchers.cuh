@@ -174,7 +174,7 @@ struct PrefillEpArgs {
     __half* const* ydst;                // [recv_cap] where each received row's output goes
     int* tiles;                         // token-tile list over the received rows
     const __nv_bfloat16* x; int n;      // this GPU's own tokens (shared expert)
-    __half* xs_local;                   // [n, H]
+    __half* xs_local;                   // [n, H] this GPU's tokens as fp16 in natural order, filled by the caller
     __half* hbuf_sh;                    // [n, Is]
     __half* y_shared;                   // [n, H]
     int* tiles_sh;                      // token-tile list of the shared expert over the local tokens

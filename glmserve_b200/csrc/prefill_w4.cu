@@ -680,8 +680,6 @@ static int run_gemm_pair(const PrefillKArgs& g_in, const PrefillKArgs& w_in, con
 // into y_shared [n, H] (the tail of the local per-slot row buffer).
 int launch_prefill_ep_shared(const PrefillEpArgs& d, cudaStream_t s) {
     if (d.Is <= 0) return GSB_OK;
-    int st0 = launch_xprep(d.x, d.xs_local, d.n, d.H, 1, s);   // this GPU's own rows, already in order
-    if (st0) return st0;
     tile_list_kernel<<<1, 1024, 0, s>>>(nullptr, 0, d.El, d.n, 0, d.tiles_sh);
     PrefillKArgs g{};
     g.packed = nullptr; g.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_gate_up_packed);
