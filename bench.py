@@ -456,16 +456,20 @@ def run_ours(args) -> None:
         torch.cuda.empty_cache()
         norms = [(1.0 + 0.02 * torch.randn(GLM["H"], device=dev)).float().contiguous() for _ in range(nl)]
         hv = make_x_torch(nv, GLM["H"], seed=400 + rank, device=dev).float()
-        ov = torch.empty((nv, GLM["H"]), dtype=torch.float32, device=dev)
         cap_v = 2 * nv * GLM["topk"]
 
         def verify_block_ep():
             for L_, nw in zip(layers_ep, norms):
-                xn = ops.rmsnorm(hv, nw, 1e-5).to(torch.bfloat16)
-                L_.forward_ep(comm, xn, out=ov, recv_cap=cap_v, path=ops.PATH_DECODE)
-                hv.add_(ov)
+                L_.block_forward_ep(comm, hv, nw, 1e-5, recv_cap=cap_v, path=ops.PATH_DECODE)
         us_blk_ep = timed(verify_block_ep, 3, warm=2) * 1e3
         st_ep = st_ep or comm.status()
+        ops.profile_enable(layer_ep, 4)
+        for _ in range(4):
+            layer_ep.block_forward_ep(comm, hv, norms[0], 1e-5, recv_cap=cap_v, path=ops.PATH_DECODE)
+        phv = ops.profile_read(layer_ep, ops.EP_STAGES)
+        ops.profile_enable(layer_ep, 0)
+        phv_names = [k for k in phv if k != "forwards"]
+        phv_max = dict(zip(phv_names, max_over_ranks([phv[k] * 1e3 for k in phv_names])))
         del layers_ep[1:]
         torch.cuda.empty_cache()
 
@@ -533,8 +537,9 @@ def run_ours(args) -> None:
                     "x 8; the layers share one set of sharded weights"}
         extra[f"spec_verify_block_8_layers_T256_ep{world}"] = {
             "us_per_block": us_blk_ep, "us_per_layer": us_blk_ep / nl, "tokens_per_gpu": nv,
-            "note": "RMSNorm -> expert-parallel layer (split-K kernels, NVLink dispatch and return) -> residual, "
-                    "x 8; eight different layers, 256 tokens over the box"}
+            "phase_us_max_over_ranks": phv_max,
+            "note": "expert-parallel block entry (pre-norm in the router-logits launch, split-K kernels, NVLink "
+                    "dispatch and return, residual in the combine) x 8; eight different layers, 256 tokens over the box"}
         comm.close()
 
     if world > 1:

@@ -96,14 +96,20 @@ size_t gsb_moe_ep_workspace_bytes(const gsb_moe_layer* layer, int n_tokens, int 
     return ep_carve(layer->cfg, n_tokens, recv_cap, nullptr).total;
 }
 
-int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, int n, float* out,
-                             void* workspace, size_t workspace_bytes, size_t heap_offset, int recv_cap,
-                             int path, int* ids_out, void* stream) {
+}  // extern "C"
+
+namespace {
+// x (bf16 rows) or, when `hidden` is given, bf16(rmsnorm(hidden, norm_w, eps)) computed inside the
+// router-logits launch; `residual` (nullable) rides the combine pass.
+int forward_ep_impl(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, const float* hidden, const float* norm_w,
+                    float eps, int n, float* out, const float* residual, void* workspace, size_t workspace_bytes,
+                    size_t heap_offset, int recv_cap, int path, int* ids_out, void* stream) {
     if (!layer || !comm || n < 0 || recv_cap <= 0 || recv_cap >= (1 << 27)) return GSB_ERR_INVALID_ARG;
     const gsb_moe_config& c = layer->cfg;
     if (c.ep_size != comm->world || c.ep_rank != comm->rank || c.ep_size < 1) return GSB_ERR_INVALID_ARG;
     if (c.n_experts % c.ep_size || !layer->tiles_ok) return GSB_ERR_UNSUPPORTED;
-    if (n > 0 && (!x_bf16 || !out)) return GSB_ERR_INVALID_ARG;
+    if (n > 0 && ((!x_bf16 && !hidden) || !out)) return GSB_ERR_INVALID_ARG;
+    if (hidden && !norm_w) return GSB_ERR_INVALID_ARG;
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255) || (heap_offset & 1023)) return GSB_ERR_INVALID_ARG;
     if (path != GSB_PATH_AUTO && path != GSB_PATH_DECODE && path != GSB_PATH_PREFILL) return GSB_ERR_INVALID_ARG;
     EpWs ws = ep_carve(c, n, recv_cap, workspace);
@@ -136,7 +142,7 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
         // (fragment order behind the receive buffer for the split-K path, natural order for the tcgen05 path):
         // the push copies them as they lie, and the shared expert reads the same rows
         st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden, E, ws.logits, ws.scores, s,
-                                  xh_local, decode ? 0 : 1);
+                                  xh_local, decode ? 0 : 1, hidden, norm_w, eps);
         if (st) return st;
         st = launch_router_topk(ws.scores, c.e_bias, n, E, c.topk, c.norm_topk, c.routed_scale, ws.ids, ws.w, s, true);
         if (st) return st;
@@ -215,12 +221,31 @@ int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x
     if (st) return st;
     if (decode)
         st = launch_combine_f32(reinterpret_cast<const float*>(ybuf), ws.slot_pos, ws.w, n, c.topk, c.hidden, P,
-                                c.shared_inter > 0 ? 1 : 0, nullptr, out, s);
+                                c.shared_inter > 0 ? 1 : 0, residual, out, s);
     else
         st = launch_combine_h(reinterpret_cast<const __half*>(ybuf), ws.slot_pos, ws.w, n, c.topk, c.hidden, P,
-                              c.shared_inter > 0 ? 1 : 0, nullptr, out, s);
+                              c.shared_inter > 0 ? 1 : 0, residual, out, s);
     mark(5);
     return st;
+}
+}  // namespace
+
+extern "C" {
+
+int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, int n, float* out,
+                             void* workspace, size_t workspace_bytes, size_t heap_offset, int recv_cap,
+                             int path, int* ids_out, void* stream) {
+    if (n > 0 && !x_bf16) return GSB_ERR_INVALID_ARG;
+    return forward_ep_impl(layer, comm, x_bf16, nullptr, nullptr, 0.f, n, out, nullptr, workspace, workspace_bytes,
+                           heap_offset, recv_cap, path, ids_out, stream);
+}
+
+int gsb_moe_block_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, float* hidden, const float* norm_w, float eps,
+                                   int n, void* workspace, size_t workspace_bytes, size_t heap_offset, int recv_cap,
+                                   int path, int* ids_out, void* stream) {
+    if (n > 0 && (!hidden || !norm_w)) return GSB_ERR_INVALID_ARG;
+    return forward_ep_impl(layer, comm, nullptr, hidden, norm_w, eps, n, hidden, hidden, workspace, workspace_bytes,
+                           heap_offset, recv_cap, path, ids_out, stream);
 }
 
 }  // extern "C"

@@ -327,6 +327,26 @@ class MoELayer:
                                              path, _p(ids_out), _stream()), "moe_layer_forward_ep")
         return out
 
+    def block_forward_ep(self, comm, hidden_f32, norm_w, eps=1e-5, recv_cap=None, heap_offset=None, ids_out=None,
+                         path=PATH_AUTO):
+        """hidden <- hidden + moe(rmsnorm(hidden)) in place over the communicator's ranks (f32 [n,H] = this
+        GPU's tokens): ``forward_ep`` with the pre-norm inside the router-logits launch and the residual add
+        inside the combine."""
+        _need(hidden_f32, torch.float32, "hidden"); _need(norm_w, torch.float32, "norm_w")
+        n = hidden_f32.shape[0]
+        if recv_cap is None:
+            recv_cap = comm.max_over_ranks(n) * self.topk * self.ep_size
+        if heap_offset is None:
+            heap_offset = (comm.reserved + 1023) // 1024 * 1024
+        need = int(lib().gsb_moe_ep_workspace_bytes(self._h, n, recv_cap))
+        if getattr(self, "_ep_ws", None) is None or self._ep_ws.numel() < need + 256:
+            self._ep_ws = torch.zeros(need + 256, dtype=torch.uint8, device=self.device)
+        check(lib().gsb_moe_block_layer_forward_ep(self._h, comm._h, _p(hidden_f32), _p(norm_w), C.c_float(eps), n,
+                                                   _p(self._ep_ws), C.c_size_t(self._ep_ws.numel()),
+                                                   C.c_size_t(heap_offset), recv_cap, path, _p(ids_out), _stream()),
+              "moe_block_layer_forward_ep")
+        return hidden_f32
+
     def ep_heap_bytes(self, n: int, recv_cap: int) -> int:
         return int(lib().gsb_moe_ep_heap_bytes(self._h, n, recv_cap))
 

@@ -407,6 +407,14 @@ GSB_API size_t gsb_moe_ep_workspace_bytes(const gsb_moe_layer* layer, int n_toke
 GSB_API int gsb_moe_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, int n,
                                      float* out, void* workspace, size_t workspace_bytes,
                                      size_t heap_offset, int recv_cap, int path, int* ids_out, void* stream);
+/* The same with the layer's pre-norm and residual add (gsb_moe_block_layer_forward over the box):
+ * hidden f32 [n,H] <- hidden + moe(rmsnorm(hidden) as bf16); the norm rides the router-logits launch, the
+ * residual the combine pass.  The result equals gsb_moe_block_layer_forward of the all-expert layer on one
+ * GPU bit for bit (same kernel family). */
+GSB_API int gsb_moe_block_layer_forward_ep(gsb_moe_layer* layer, gsb_comm* comm, float* hidden,
+                                           const float* norm_w, float eps, int n, void* workspace,
+                                           size_t workspace_bytes, size_t heap_offset, int recv_cap, int path,
+                                           int* ids_out, void* stream);
 
 /* Reads (and clears) the device status word of the last forward on this layer after the
  * caller synchronised the stream: GSB_OK, or the recorded code (GSB_ERR_TIMEOUT when a bounded

@@ -92,6 +92,15 @@ def check_mid(comm, rank, world, dev):
             assert comm.status() == 0, "expert-parallel exchange reported an error"
             assert torch.equal(got, want), f"expert-parallel output differs from single GPU (path {path}, rep {rep})"
         assert_layer_close(got.cpu().numpy(), ref["out"], f"expert-parallel layer vs oracle (path {path})")
+    # the block entry (pre-norm inside the logits launch, residual inside the combine) against the single-GPU block
+    nw = (1.0 + 0.02 * torch.randn(L["H"], generator=torch.Generator(device=dev).manual_seed(5), device=dev)).contiguous()
+    for path in (ops.PATH_PREFILL, ops.PATH_DECODE):
+        h_want = torch.from_numpy(x_loc_np).to(dev)
+        h_got = h_want.clone()
+        full.block_forward(h_want, nw, 1e-5, path=path)
+        layer_ep.block_forward_ep(comm, h_got, nw, 1e-5, path=path)
+        assert comm.status() == 0
+        assert torch.equal(h_got, h_want), f"expert-parallel block differs from the single-GPU block (path {path})"
     # ragged: one rank with no tokens at all, and every rank sizing its buffers from its own n
     n2 = 0 if rank == 0 else 77 + rank
     x2 = bf16_tensor(make_x_np(max(n2, 1), L["H"], seed=70 + rank)[:n2], dev)
