@@ -58,6 +58,15 @@ __global__ void wait_kernel(CommPeers pr, int rank, int world, int ch, int seq, 
         wait_flag(ctrl + kFlagBase + ch * kMaxWorld + threadIdx.x, seq, ctrl + kStatusWord, limit);
 }
 
+__global__ void signal_wait_kernel(CommPeers pr, int rank, int world, int ch, int seq, long long limit) {
+    __threadfence_system();
+    int* ctrl = ctrl_of(pr, rank);
+    if (threadIdx.x < world && threadIdx.x != rank) {
+        st_release_sys(ctrl_of(pr, threadIdx.x) + kFlagBase + ch * kMaxWorld + rank, seq);
+        wait_flag(ctrl + kFlagBase + ch * kMaxWorld + threadIdx.x, seq, ctrl + kStatusWord, limit);
+    }
+}
+
 // ---- all-reduce ---------------------------------------------------------------------------
 // Staging of one parity: two areas of `area` floats.
 //   one-shot  slot[src] = area 0 + src * count floats (both areas together; needs world * count <= 2 * area).
@@ -235,11 +244,15 @@ __global__ void ep_post_counts_kernel(CommPeers pr, int rank, int world, const i
         st_release_sys(ctrl_of(pr, threadIdx.x) + kFlagBase + kChCounts * kMaxWorld + rank, seq);
 }
 
+constexpr int kDestShift = 27;   // row_dest = owner << 27 | row (receive capacities stay below 2^27 rows)
+
 // After every rank's counts arrived: the layout of the rows this rank RECEIVES (local expert
 // major, then source rank, then the source's order) and where the rows it SENDS land.
 //   recv_offsets[El + 1]      first received row of each local expert (El = E / world), clamped to recv_cap
 //   send_base[E]              row index on the owner's receive buffer of this rank's first row for expert e
 //   ydst[row]                 for each received row: where its output row goes (the source's row buffer)
+//   row_dest[P]               for each sorted row this rank sends: owner rank and row of the owner's receive
+//                             buffer packed into one int (-1: the owner has no room for it)
 //   plan[0] = 1 when every peer's counts arrived (0: nothing is pushed and nothing is computed),
 //   plan[1] = rows received, plan[4 + 4r ..] = rank r's posted {receive offset KiB, capacity, row buffer KiB}
 // More rows than recv_cap: GSB_ERR_TOO_LARGE is recorded, the offsets are clamped so that no tile, row of
@@ -248,7 +261,8 @@ __global__ void ep_post_counts_kernel(CommPeers pr, int rank, int world, const i
 __global__ void __launch_bounds__(1024)
 ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restrict__ recv_offsets,
                int* __restrict__ send_base, void** __restrict__ ydst, int H, int y_elem_bytes,
-               int recv_cap, int own_ybuf_kib, int* __restrict__ plan, long long wait_cycles) {
+               int recv_cap, int own_ybuf_kib, int* __restrict__ plan, long long wait_cycles,
+               const int* __restrict__ expert_offsets, int* __restrict__ row_dest) {
     int* ctrl = ctrl_of(pr, rank);
     __shared__ int tot_s[kMaxExperts];             // rows of expert e over all sources
     __shared__ int base_s[kMaxExperts];            // first receive row of expert e on its owner
@@ -295,10 +309,21 @@ ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restric
         int before = 0;
         for (int s = 0; s < rank; ++s) before += cnt[s * kMaxExperts + e];
         send_base[e] = base_s[e] + before;
+        tot_s[e] = base_s[e] + before;             // (the totals are used up) kept for the row loop below
         if (e / El == rank) recv_offsets[e - rank * El] = min(base_s[e], recv_cap);
     }
-    // output destinations of the rows this rank will compute: one warp per (local expert, source)
+    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+    // where every sorted row this rank sends goes: one warp per expert
+    for (int e = warp; e < E; e += nwarp) {
+        const int owner = e / El, base = tot_s[e], beg = expert_offsets[e], end = expert_offsets[e + 1];
+        const int cap = owner == rank ? recv_cap : meta[owner * 8 + 1];
+        for (int r = beg + lane; r < end; r += 32) {
+            const int dst_row = base + (r - beg);
+            row_dest[r] = dst_row < cap ? ((owner << kDestShift) | dst_row) : -1;
+        }
+    }
+    // output destinations of the rows this rank will compute: one warp per (local expert, source)
     for (int job = warp; job < El * world; job += nwarp) {
         const int el = job / world, sidx = job - el * world;
         const int e = rank * El + el;
@@ -329,7 +354,6 @@ ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restric
 // (1.14 ms); on 16 SMs of its own it took 0.6 ms by itself, however the bytes were moved: an SM copies
 // ~47 GB/s, and half (2 GPUs) or a quarter (4) of the rows stay on the GPU and take SM time all the same.
 constexpr int kPushWarps = 32, kPushThreads = kPushWarps * 32;
-constexpr int kDestShift = 27;                                   // row_dest = owner << 27 | row (receive capacities stay below 2^27 rows)
 constexpr int kPushChunk = 3072;                                  // bytes per staged piece
 constexpr int kPushSmem = kPushWarps * 2 * kPushChunk + kPushWarps * 2 * 8;
 __device__ __forceinline__ void bulk_s2g(void* dst, const void* src, uint32_t bytes) {
@@ -405,21 +429,13 @@ ep_dispatch_push_kernel(CommPeers pr, int rank, int world, const __half* __restr
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // every piece this lane sent has been written
 }
 
-// Where every sorted row goes, for the push kernel: owner rank and row of the owner's receive buffer packed
-// into one int (-1: the owner has no room for it), from the plan's send bases and the owners' posted capacities.
-__global__ void ep_rows_dest_kernel(const int* __restrict__ expert_offsets, int E, int world,
-                                    const int* __restrict__ send_base, const int* __restrict__ plan,
-                                    int* __restrict__ row_dest) {
-    const int e = blockIdx.x, owner = e / (E / world);
-    const int base = send_base[e], cap = plan[4 + 4 * owner + 1], beg = expert_offsets[e];
-    for (int r = beg + threadIdx.x; r < expert_offsets[e + 1]; r += blockDim.x) {
-        const int dst_row = base + (r - beg);
-        row_dest[r] = dst_row < cap ? ((owner << kDestShift) | dst_row) : -1;
-    }
-}
-
 int comm_launch_signal(gsb_comm* c, int ch, cudaStream_t s) {
     signal_kernel<<<1, 32, 0, s>>>(c->peers, c->rank, c->world, ch, (int)c->seq[ch]);
+    return launch_status();
+}
+// signal and wait in one launch (the return exchange: nothing lies between the two)
+int comm_launch_signal_wait(gsb_comm* c, int ch, cudaStream_t s) {
+    signal_wait_kernel<<<1, 32, 0, s>>>(c->peers, c->rank, c->world, ch, (int)c->seq[ch], c->wait_cycles);
     return launch_status();
 }
 int comm_launch_wait(gsb_comm* c, int ch, cudaStream_t s) {
@@ -436,8 +452,8 @@ int comm_ep_plan(gsb_comm* c, const EpExchange& e, cudaStream_t s) {
     ep_post_counts_kernel<<<1, 256, 0, s>>>(c->peers, c->rank, c->world, e.expert_offsets, e.E, seq_c,
                                             (int)(e.recv_off >> 10), e.recv_cap, (int)(e.ybuf_off >> 10));
     ep_plan_kernel<<<1, 1024, 0, s>>>(c->peers, c->rank, c->world, e.E, seq_c, e.recv_offsets, e.send_base, e.ydst,
-                                      e.H, e.y_elem_bytes, e.recv_cap, (int)(e.ybuf_off >> 10), e.plan, c->wait_cycles);
-    ep_rows_dest_kernel<<<e.E, 128, 0, s>>>(e.expert_offsets, e.E, c->world, e.send_base, e.plan, e.sorted_expert);
+                                      e.H, e.y_elem_bytes, e.recv_cap, (int)(e.ybuf_off >> 10), e.plan, c->wait_cycles,
+                                      e.expert_offsets, e.sorted_expert);
     return launch_status();
 }
 
@@ -548,9 +564,7 @@ int gsb_comm_barrier(gsb_comm* c, void* stream) {
     if (c->world == 1) return GSB_OK;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     ++c->seq[kChBarrier];
-    int st = comm_launch_signal(c, kChBarrier, s);
-    if (st) return st;
-    return comm_launch_wait(c, kChBarrier, s);
+    return comm_launch_signal_wait(c, kChBarrier, s);
 }
 
 // The first bytes of the heap are the all-reduce staging: two parities of two areas of

@@ -1122,15 +1122,19 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
 // [recv_cap, recv_cap + n)) through the shared expert, as ONE pair of launches.  With P = 0 the gate/up
 // kernel takes slot s from xbuf row s; the down kernel's epilogue stores every output row through ydst
 // (received rows: a row of the token's home GPU over NVLink; shared rows: this GPU's own row buffer).
-int launch_decode_ep(const DecodeEpArgs& d, cudaStream_t s) {
+// `what`: 1 = the work lists only (they need the plan's receive offsets, not the rows: the caller builds them while
+// the rows are still in flight), 2 = the two GEMM kernels only, 3 = both.
+int launch_decode_ep(const DecodeEpArgs& d, cudaStream_t s, int what) {
     const bool shared = d.Is > 0;
     const int imax = d.I > d.Is ? d.I : d.Is;
     if (d.El > 1024 || d.sm_count > 1024) return GSB_ERR_UNSUPPORTED;
     const int ups = (!shared || d.Is == d.I) ? down_reg_ups(d.I) : 0;
     const int units_dn = ups ? (d.H / 32) / ups : d.H / 32;
     int* xsegs = d.segs + xsegs_offset_raw((size_t)d.recv_cap, (size_t)d.n, d.El);
-    seg_build_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, d.n, d.recv_cap, shared ? 1 : 0, d.segs, xsegs, d.I / 16,
-                                        shared ? d.Is / 16 : 1, units_dn, d.sm_count);
+    if (what & 1)
+        seg_build_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, d.n, d.recv_cap, shared ? 1 : 0, d.segs, xsegs, d.I / 16,
+                                            shared ? d.Is / 16 : 1, units_dn, d.sm_count);
+    if (!(what & 2)) return launch_status();
     DecodeKArgs g{};
     g.packed = reinterpret_cast<const uint8_t*>(d.gate_up_packed);
     g.shared_packed = reinterpret_cast<const uint8_t*>(d.shared_gate_up_packed);
@@ -1140,6 +1144,10 @@ int launch_decode_ep(const DecodeEpArgs& d, cudaStream_t s) {
     g.hbuf = d.hbuf; g.ldh = imax; g.ybuf = nullptr; g.ydst = nullptr; g.H = d.H; g.status = d.status;
     g.xsegs = xsegs; g.x_which = 0;
     const bool gu_reg = d.H % 2048 == 0 && d.H / 2048 <= 3;
+    // both register-resident: the down kernel is scheduled as gate/up's CTAs leave and streams its weights
+    // under gate/up's tail (its consumers wait for gate/up's completion before they read h)
+    const bool pdl = gu_reg && ups != 0;
+    g.pdl_trigger = pdl ? 1 : 0;
     if (gu_reg) {
         const int st = launch_reg<true>(g, d.H / 2048, d.sm_count, s);
         if (st) return st;
@@ -1157,6 +1165,7 @@ int launch_decode_ep(const DecodeEpArgs& d, cudaStream_t s) {
     w.bsrc = d.hbuf; w.ldb = imax; w.K = d.I; w.Ks = shared ? d.Is : d.I;
     w.units = units_dn; w.units_s = units_dn;
     w.hbuf = nullptr; w.ybuf = nullptr; w.ydst = d.ydst; w.x_which = 1;
+    w.pdl_trigger = 0; w.pdl_wait = pdl ? 1 : 0; w.pdl_wait_all = 0;
     if (ups) {
         const int st = launch_reg<false>(w, ups == 1 ? d.I / 2048 : 0, d.sm_count, s, ups);
         if (st) return st;

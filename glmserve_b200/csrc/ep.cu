@@ -173,10 +173,6 @@ int forward_ep_impl(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, co
         if (n > 0 && c.shared_inter > 0) {
             ep_shared_dst_kernel<<<(n + 255) / 256, 256, 0, s>>>(ws.ydst + recv_cap, reinterpret_cast<float*>(ybuf) + (size_t)P * c.hidden, n, c.hidden);
         }
-        mark(2);
-        st = comm_launch_wait(comm, kChDispatch, s);
-        if (st) return st;
-        mark(3);
         DecodeEpArgs d{};
         d.H = c.hidden; d.I = c.moe_inter; d.Is = c.shared_inter; d.El = El;
         d.gate_up_packed = c.gate_up_packed; d.down_packed = c.down_packed;
@@ -184,7 +180,13 @@ int forward_ep_impl(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, co
         d.recv_offsets = ws.recv_offsets; d.xbuf = xbuf; d.recv_cap = recv_cap; d.n = c.shared_inter > 0 ? n : 0;
         d.hbuf = ws.hbuf; d.ydst = reinterpret_cast<float* const*>(ws.ydst); d.segs = ws.segs; d.status = ws.status;
         d.sm_count = layer->sm_count;
-        st = launch_decode_ep(d, s);
+        st = launch_decode_ep(d, s, 1);      // the work lists need only the plan: built while the rows travel
+        if (st) return st;
+        mark(2);
+        st = comm_launch_wait(comm, kChDispatch, s);
+        if (st) return st;
+        mark(3);
+        st = launch_decode_ep(d, s, 2);
         if (st) return st;
     } else {
         PrefillEpArgs a{};
@@ -200,6 +202,8 @@ int forward_ep_impl(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, co
         // CTAs without an SM would start their tiles only when the push is over
         a.sm_count = layer->sm_count - comm_ep_push_sms(P, comm->world);
         if (n > 0) { st = launch_prefill_ep_shared(a, s); if (st) return st; }
+        st = launch_prefill_ep_routed(a, s, 1);   // the tile list needs only the plan
+        if (st) return st;
         mark(2);
         st = comm_launch_wait(comm, kChDispatch, s);
         if (st) return st;
@@ -208,16 +212,14 @@ int forward_ep_impl(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, co
         if (cudaStreamWaitEvent(s, layer->ep_join, 0) != cudaSuccess) return GSB_ERR_CUDA;
         mark(3);
         a.sm_count = layer->sm_count;
-        st = launch_prefill_ep_routed(a, s);
+        st = launch_prefill_ep_routed(a, s, 2);
         if (st) return st;
     }
     mark(4);
     // this rank's pushes are part of the call: the caller's stream does not run past them
     if (cudaStreamWaitEvent(s, layer->ep_join, 0) != cudaSuccess) return GSB_ERR_CUDA;
     ++comm->seq[kChCombine];
-    st = comm_launch_signal(comm, kChCombine, s);
-    if (st) return st;
-    st = comm_launch_wait(comm, kChCombine, s);
+    st = comm_launch_signal_wait(comm, kChCombine, s);
     if (st) return st;
     if (decode)
         st = launch_combine_f32(reinterpret_cast<const float*>(ybuf), ws.slot_pos, ws.w, n, c.topk, c.hidden, P,

@@ -62,6 +62,7 @@ struct gsb_moe_layer {
 namespace gsb {
 int comm_launch_signal(gsb_comm* c, int ch, cudaStream_t s);
 int comm_launch_wait(gsb_comm* c, int ch, cudaStream_t s);
+int comm_launch_signal_wait(gsb_comm* c, int ch, cudaStream_t s);
 struct EpExchange {
     const __half* xh;              // this rank's tokens [n, H] as fp16, in the feature order the receiving kernels
                                    // read (natural for the tcgen05 path, fragment order for the split-K path)

@@ -120,7 +120,7 @@ struct DecodeEpArgs {
     int* status;
     int sm_count;
 };
-int launch_decode_ep(const DecodeEpArgs& a, cudaStream_t s);
+int launch_decode_ep(const DecodeEpArgs& a, cudaStream_t s, int what = 3);   // what: 1 lists, 2 kernels, 3 both
 int launch_combine_f32(const float* ybuf, const int* slot_pos, const float* topk_w, int n, int topk, int H, int P,
                        int has_shared, const float* residual, float* out, cudaStream_t s);
 // bf16 rows -> fp16 rows in fragment order (natural = 0) or natural feature order (1)
@@ -182,7 +182,7 @@ struct PrefillEpArgs {
     int sm_count;
 };
 int launch_prefill_ep_shared(const PrefillEpArgs& a, cudaStream_t s);
-int launch_prefill_ep_routed(const PrefillEpArgs& a, cudaStream_t s);
+int launch_prefill_ep_routed(const PrefillEpArgs& a, cudaStream_t s, int what = 3);   // what: 1 tile list, 2 kernels, 3 both
 int launch_combine_h(const __half* ybuf, const int* slot_pos, const float* topk_w, int n, int topk, int H,
                      int P, int has_shared, const float* residual, float* out, cudaStream_t s);
 

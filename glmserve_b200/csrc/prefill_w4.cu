@@ -696,8 +696,9 @@ int launch_prefill_ep_shared(const PrefillEpArgs& d, cudaStream_t s) {
 // Expert parallel, routed experts: the rows this GPU received (grouped by local expert in
 // recv_x) through its resident experts; the down kernel's epilogue stores every output row
 // straight to the GPU that owns the token (ydst) - compute and the return all-to-all in one kernel.
-int launch_prefill_ep_routed(const PrefillEpArgs& d, cudaStream_t s) {
-    tile_list_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, d.El, 0, 0, d.tiles);
+int launch_prefill_ep_routed(const PrefillEpArgs& d, cudaStream_t s, int what) {
+    if (what & 1) tile_list_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, d.El, 0, 0, d.tiles);
+    if (!(what & 2)) return launch_status();
     PrefillKArgs g{};
     g.packed = reinterpret_cast<const uint8_t*>(d.gate_up_packed); g.shared_packed = nullptr;
     g.tiles = d.tiles; g.RB = d.I / 64; g.RBs = 1;
