@@ -19,6 +19,7 @@
 #include <new>
 
 #include "internal.cuh"
+#include "route_device.cuh"
 
 namespace gsb {
 
@@ -228,8 +229,9 @@ allreduce_kernel(const ArArgs a) {
 // Counts: rank posts its per-expert row counts (from its local dispatch offsets) and the layout of its
 // own buffers {receive buffer offset, receive capacity, per-slot row buffer offset} to every peer, so a
 // peer never derives an address on this rank from its own arguments.
-__global__ void ep_post_counts_kernel(CommPeers pr, int rank, int world, const int* __restrict__ expert_offsets,
-                                      int E, int seq, int recv_off_kib, int recv_cap, int ybuf_off_kib) {
+__device__ __forceinline__ void ep_post_counts_block(const CommPeers& pr, int rank, int world,
+                                                     const int* __restrict__ expert_offsets, int E, int seq,
+                                                     int recv_off_kib, int recv_cap, int ybuf_off_kib) {
     for (int p = 0; p < world; ++p) {
         int* dst = ctrl_of(pr, p) + kCntBase + rank * kMaxExperts;
         for (int e = threadIdx.x; e < E; e += blockDim.x) dst[e] = expert_offsets[e + 1] - expert_offsets[e];
@@ -242,6 +244,36 @@ __global__ void ep_post_counts_kernel(CommPeers pr, int rank, int world, const i
     __syncthreads();
     if (threadIdx.x < world && threadIdx.x != rank)
         st_release_sys(ctrl_of(pr, threadIdx.x) + kFlagBase + kChCounts * kMaxWorld + rank, seq);
+}
+__global__ void ep_post_counts_kernel(CommPeers pr, int rank, int world, const int* __restrict__ expert_offsets,
+                                      int E, int seq, int recv_off_kib, int recv_cap, int ybuf_off_kib) {
+    ep_post_counts_block(pr, rank, world, expert_offsets, E, seq, recv_off_kib, recv_cap, ybuf_off_kib);
+}
+
+// Small decode batches (at most kRouteTokens tokens): top-k selection, dispatch and the posting of the counts
+// in ONE launch of one block - three launches and a memset less ahead of the exchange.  Each step is the
+// stand-alone kernel's body, so ids, weights and permutation are the same bits.
+constexpr int kRouteTokens = 32;    // one token per warp: a single block is slower than the separate launches beyond that
+                                    // (128 tokens per GPU: route + plan 98 us fused, 80 us as three launches)
+__global__ void __launch_bounds__(kDispWarps * 32)
+ep_route_post_kernel(CommPeers pr, int rank, int world, const float* __restrict__ scores,
+                     const float* __restrict__ e_bias, int n, int E, int topk, int norm_topk, float routed_scale,
+                     int* __restrict__ ids, float* __restrict__ w, int* __restrict__ expert_offsets,
+                     int* __restrict__ sorted_tok, int* __restrict__ sorted_row, int* __restrict__ slot_pos,
+                     int* __restrict__ status, int seq, int recv_off_kib, int recv_cap, int ybuf_off_kib) {
+    extern __shared__ int route_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x < 4) status[threadIdx.x] = 0;
+    for (int t = warp; t < n; t += kDispWarps) {
+        if (E <= 256) topk_token<8, true>(scores + (size_t)t * E, e_bias, E, topk, norm_topk, routed_scale, lane,
+                                          ids + (size_t)t * topk, w + (size_t)t * topk);
+        else topk_token<32, true>(scores + (size_t)t * E, e_bias, E, topk, norm_topk, routed_scale, lane,
+                                  ids + (size_t)t * topk, w + (size_t)t * topk);
+    }
+    __syncthreads();   // the block's own global writes (ids) are visible to it from here
+    dispatch_block(ids, n * topk, topk, E, expert_offsets, sorted_tok, sorted_row, slot_pos, route_smem);
+    __syncthreads();
+    ep_post_counts_block(pr, rank, world, expert_offsets, E, seq, recv_off_kib, recv_cap, ybuf_off_kib);
 }
 
 constexpr int kDestShift = 27;   // row_dest = owner << 27 | row (receive capacities stay below 2^27 rows)
@@ -444,21 +476,32 @@ int comm_launch_wait(gsb_comm* c, int ch, cudaStream_t s) {
 }
 
 // Count exchange and plan: everything that decides where rows go.
-int comm_ep_plan(gsb_comm* c, const EpExchange& e, cudaStream_t s) {
+int comm_ep_plan(gsb_comm* c, const EpExchange& e, cudaStream_t s, const EpRouting* r) {
     if (e.E > kMaxExperts || e.E % c->world) return GSB_ERR_UNSUPPORTED;
     if ((e.recv_off & 1023) || (e.ybuf_off & 1023) || (e.recv_off >> 10) > 0x7fffffff || (e.ybuf_off >> 10) > 0x7fffffff)
         return GSB_ERR_INVALID_ARG;
     const int seq_c = (int)++c->seq[kChCounts];
-    ep_post_counts_kernel<<<1, 256, 0, s>>>(c->peers, c->rank, c->world, e.expert_offsets, e.E, seq_c,
-                                            (int)(e.recv_off >> 10), e.recv_cap, (int)(e.ybuf_off >> 10));
+    if (r) {   // routing not done yet: top-k + dispatch + counts in one launch (comm_ep_route_fusable)
+        const size_t smem = (size_t)(kDispWarps * e.E + 1024) * sizeof(int);
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(ep_route_post_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return GSB_ERR_CUDA;
+        ep_route_post_kernel<<<1, kDispWarps * 32, smem, s>>>(c->peers, c->rank, c->world, r->scores, r->e_bias, r->n, e.E,
+                                                              r->topk, r->norm_topk, r->routed_scale, r->ids, r->w,
+                                                              r->expert_offsets, r->sorted_tok, r->sorted_row, r->slot_pos,
+                                                              r->status, seq_c, (int)(e.recv_off >> 10), e.recv_cap,
+                                                              (int)(e.ybuf_off >> 10));
+    } else {
+        ep_post_counts_kernel<<<1, 256, 0, s>>>(c->peers, c->rank, c->world, e.expert_offsets, e.E, seq_c,
+                                                (int)(e.recv_off >> 10), e.recv_cap, (int)(e.ybuf_off >> 10));
+    }
     ep_plan_kernel<<<1, 1024, 0, s>>>(c->peers, c->rank, c->world, e.E, seq_c, e.recv_offsets, e.send_base, e.ydst,
                                       e.H, e.y_elem_bytes, e.recv_cap, (int)(e.ybuf_off >> 10), e.plan, c->wait_cycles,
                                       e.expert_offsets, e.sorted_expert);
     return launch_status();
 }
+bool comm_ep_route_fusable(int n, int E) { return n > 0 && n <= kRouteTokens && E <= 1024; }
 
-// Dispatch push of this rank's rows and its signal (any stream ordered after comm_ep_plan's).  The caller
-// waits on kChDispatch before it reads its receive buffer.
 // SMs the push of P rows keeps to itself while it runs (a warp per row in flight).  An SM copies ~47 GB/s
 // (measured, plain stores and bulk copies alike, local or remote), NVLink takes ~670 GB/s per sender, and
 // (world - 1) / world of the rows are remote: with more ranks the link bounds the push and fewer SMs keep up

@@ -136,7 +136,9 @@ int forward_ep_impl(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, co
         ev = layer->prof_ev + (size_t)(layer->prof_used++) * (GSB_N_STAGES + 1);
     auto mark = [&](int i) { if (ev) cudaEventRecord(ev[i], s); };
     mark(0);
-    if (cudaMemsetAsync(ws.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
+    // decode-sized batches: top-k, dispatch and the posting of the counts ride one launch (inside comm_ep_plan)
+    const bool fused_route = comm_ep_route_fusable(n, E);
+    if (!fused_route && cudaMemsetAsync(ws.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
     if (n > 0) {
         // the logits launch leaves this rank's tokens behind as fp16 rows in the order the receiving kernels read
         // (fragment order behind the receive buffer for the split-K path, natural order for the tcgen05 path):
@@ -144,14 +146,16 @@ int forward_ep_impl(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, co
         st = launch_router_logits(x, reinterpret_cast<const __nv_bfloat16*>(c.router_w), n, c.hidden, E, ws.logits, ws.scores, s,
                                   xh_local, decode ? 0 : 1, hidden, norm_w, eps);
         if (st) return st;
-        st = launch_router_topk(ws.scores, c.e_bias, n, E, c.topk, c.norm_topk, c.routed_scale, ws.ids, ws.w, s, true);
-        if (st) return st;
-        if (ids_out && cudaMemcpyAsync(ids_out, ws.ids, (size_t)P * sizeof(int), cudaMemcpyDeviceToDevice, s) != cudaSuccess)
-            return GSB_ERR_CUDA;
+        if (!fused_route) {
+            st = launch_router_topk(ws.scores, c.e_bias, n, E, c.topk, c.norm_topk, c.routed_scale, ws.ids, ws.w, s, true);
+            if (st) return st;
+        }
     }
-    st = launch_dispatch(ws.ids, n, c.topk, E, ws.expert_offsets, ws.sorted_tok, ws.sorted_row, ws.slot_pos, s,
-                         ws.disp_scratch);
-    if (st) return st;
+    if (!fused_route) {
+        st = launch_dispatch(ws.ids, n, c.topk, E, ws.expert_offsets, ws.sorted_tok, ws.sorted_row, ws.slot_pos, s,
+                             ws.disp_scratch);
+        if (st) return st;
+    }
     // counts -> plan on the caller's stream; the push of this rank's rows and its signal on the side stream,
     // so that the shared expert (local tokens only) runs while rows travel in BOTH directions
     EpExchange ex{};
@@ -159,8 +163,14 @@ int forward_ep_impl(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, co
     ex.sorted_expert = ws.sorted_expert; ex.recv_offsets = ws.recv_offsets; ex.send_base = ws.send_base; ex.ydst = ws.ydst;
     ex.plan = ws.plan; ex.recv_off = heap_offset + hp.xbuf; ex.ybuf_off = heap_offset + hp.ybuf;
     ex.y_elem_bytes = decode ? (int)sizeof(float) : (int)sizeof(__half); ex.recv_cap = recv_cap;
-    st = comm_ep_plan(comm, ex, s);
+    EpRouting rt{};
+    rt.scores = ws.scores; rt.e_bias = c.e_bias; rt.n = n; rt.topk = c.topk; rt.norm_topk = c.norm_topk;
+    rt.routed_scale = c.routed_scale; rt.ids = ws.ids; rt.w = ws.w; rt.expert_offsets = ws.expert_offsets;
+    rt.sorted_tok = ws.sorted_tok; rt.sorted_row = ws.sorted_row; rt.slot_pos = ws.slot_pos; rt.status = ws.status;
+    st = comm_ep_plan(comm, ex, s, fused_route ? &rt : nullptr);
     if (st) return st;
+    if (n > 0 && ids_out && cudaMemcpyAsync(ids_out, ws.ids, (size_t)P * sizeof(int), cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+        return GSB_ERR_CUDA;
     if (cudaEventRecord(layer->ep_fork, s) != cudaSuccess || cudaStreamWaitEvent(layer->ep_side, layer->ep_fork, 0) != cudaSuccess)
         return GSB_ERR_CUDA;
     st = comm_ep_push(comm, ex, layer->ep_side);

@@ -79,7 +79,15 @@ struct EpExchange {
     int y_elem_bytes;              // element size of the per-slot output rows (2 = fp16, 4 = fp32)
     int recv_cap;
 };
-int comm_ep_plan(gsb_comm* c, const EpExchange& e, cudaStream_t s);
+// Routing inputs and outputs for the fused form of comm_ep_plan (decode-sized batches): sigmoid scores in,
+// ids / weights / dispatch permutation out, status words zeroed.
+struct EpRouting {
+    const float* scores; const float* e_bias;
+    int n, topk, norm_topk; float routed_scale;
+    int* ids; float* w; int* expert_offsets; int* sorted_tok; int* sorted_row; int* slot_pos; int* status;
+};
+int comm_ep_plan(gsb_comm* c, const EpExchange& e, cudaStream_t s, const EpRouting* routing = nullptr);
+bool comm_ep_route_fusable(int n, int E);
 int comm_ep_push(gsb_comm* c, const EpExchange& e, cudaStream_t s);
 int comm_ep_push_sms(int P, int world);   // SMs that push occupies by itself while it runs
 }  // namespace gsb

@@ -109,6 +109,16 @@ def check_mid(comm, rank, world, dev):
         assert comm.status() == 0
         if n2:
             assert torch.equal(got2, full.forward(x2, path=path))
+    # a handful of tokens per rank: routing, dispatch and the posting of the counts ride one launch there
+    for n3 in (1 + rank % 3, 32):
+        x3 = bf16_tensor(make_x_np(n3, L["H"], seed=80 + rank), dev)
+        for path in (ops.PATH_PREFILL, ops.PATH_DECODE):
+            ids3 = torch.empty((n3, L["topk"]), dtype=torch.int32, device=dev)
+            got5 = layer_ep.forward_ep(comm, x3, recv_cap=1024, path=path, ids_out=ids3)
+            assert comm.status() == 0
+            want5, _, ids_w, _ = full.forward(x3, path=path, return_routing=True)
+            assert torch.equal(ids3, ids_w), f"small-batch expert-parallel routing differs (n={n3}, path {path})"
+            assert torch.equal(got5, want5), f"small-batch expert-parallel output differs (n={n3}, path {path})"
     # a receive capacity that is too small is reported, and nothing is written out of bounds
     got3 = layer_ep.forward_ep(comm, x_loc, recv_cap=64, path=ops.PATH_PREFILL)
     torch.cuda.synchronize()
