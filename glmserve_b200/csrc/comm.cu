@@ -276,7 +276,8 @@ ep_route_post_kernel(CommPeers pr, int rank, int world, const float* __restrict_
     ep_post_counts_block(pr, rank, world, expert_offsets, E, seq, recv_off_kib, recv_cap, ybuf_off_kib);
 }
 
-constexpr int kDestShift = 27;   // row_dest = owner << 27 | row (receive capacities stay below 2^27 rows)
+constexpr int kDestShift = 27;   // row_dest = wave << 30 | owner << 27 | row (receive capacities stay below 2^27 rows)
+constexpr int kDestWaveBit = 30; // wave 1 = the second half of the owner's resident experts
 
 // After every rank's counts arrived: the layout of the rows this rank RECEIVES (local expert
 // major, then source rank, then the source's order) and where the rows it SENDS land.
@@ -352,7 +353,7 @@ ep_plan_kernel(CommPeers pr, int rank, int world, int E, int seq, int* __restric
         const int cap = owner == rank ? recv_cap : meta[owner * 8 + 1];
         for (int r = beg + lane; r < end; r += 32) {
             const int dst_row = base + (r - beg);
-            row_dest[r] = dst_row < cap ? ((owner << kDestShift) | dst_row) : -1;
+            row_dest[r] = dst_row < cap ? ((((e - owner * El) >= (El + 1) / 2 ? 1 : 0) << kDestWaveBit) | (owner << kDestShift) | dst_row) : -1;
         }
     }
     // output destinations of the rows this rank will compute: one warp per (local expert, source)
@@ -395,7 +396,7 @@ __device__ __forceinline__ void bulk_s2g(void* dst, const void* src, uint32_t by
 __global__ void __launch_bounds__(kPushThreads, 1)
 ep_dispatch_push_kernel(CommPeers pr, int rank, int world, const __half* __restrict__ xh,
                         const int* __restrict__ sorted_tok, const int* __restrict__ row_dest, int H, int P,
-                        const int* __restrict__ plan, size_t own_recv_off, long long wait_cycles) {
+                        const int* __restrict__ plan, size_t own_recv_off, long long wait_cycles, int wave) {
     extern __shared__ __align__(128) uint8_t push_smem[];
     if (!plan[0] || (threadIdx.x & 31)) return;                  // one lane per warp drives the copy unit
     const int warp = threadIdx.x >> 5;
@@ -420,7 +421,8 @@ ep_dispatch_push_kernel(CommPeers pr, int rank, int world, const __half* __restr
             const int r = k < dealt ? (k % world) * run + k / world : k;
             const int dest = row_dest[r];
             if (dest < 0) continue;                               // beyond what the owner can receive
-            const int owner = dest >> kDestShift;
+            if (wave >= 0 && ((dest >> kDestWaveBit) & 1) != wave) continue;   // the other wave's launch sends it
+            const int owner = (dest >> kDestShift) & 7;
             const size_t recv_off = owner == rank ? own_recv_off : ((size_t)plan[4 + 4 * owner + 0] << 10);
             src_row = reinterpret_cast<const uint8_t*>(xh) + (size_t)sorted_tok[r] * row_bytes;
             dst_row = pr.base[owner] + kCtrlBytes + recv_off + (size_t)(dest & ((1 << kDestShift) - 1)) * row_bytes;
@@ -470,8 +472,9 @@ int comm_launch_signal_wait(gsb_comm* c, int ch, cudaStream_t s) {
     signal_wait_kernel<<<1, 32, 0, s>>>(c->peers, c->rank, c->world, ch, (int)c->seq[ch], c->wait_cycles);
     return launch_status();
 }
-int comm_launch_wait(gsb_comm* c, int ch, cudaStream_t s) {
-    wait_kernel<<<1, 32, 0, s>>>(c->peers, c->rank, c->world, ch, (int)c->seq[ch], c->wait_cycles);
+// back = 0: the channel's newest sequence number; 1: the one before it (the first of two waves)
+int comm_launch_wait(gsb_comm* c, int ch, cudaStream_t s, int back) {
+    wait_kernel<<<1, 32, 0, s>>>(c->peers, c->rank, c->world, ch, (int)c->seq[ch] - back, c->wait_cycles);
     return launch_status();
 }
 
@@ -512,16 +515,20 @@ int comm_ep_push_sms(int P, int world) {
     return want < blocks ? want : blocks;
 }
 
-int comm_ep_push(gsb_comm* c, const EpExchange& e, cudaStream_t s) {
-    if (e.P > 0)
-    {
-        if (cudaFuncSetAttribute(ep_dispatch_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPushSmem) != cudaSuccess)
-            return GSB_ERR_CUDA;
-        ep_dispatch_push_kernel<<<comm_ep_push_sms(e.P, c->world), kPushThreads, kPushSmem, s>>>(
-            c->peers, c->rank, c->world, e.xh, e.sorted_tok, e.sorted_expert, e.H, e.P, e.plan, e.recv_off, c->wait_cycles);
+int comm_ep_push(gsb_comm* c, const EpExchange& e, cudaStream_t s, int waves) {
+    if (e.P > 0 &&
+        cudaFuncSetAttribute(ep_dispatch_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPushSmem) != cudaSuccess)
+        return GSB_ERR_CUDA;
+    for (int wv = 0; wv < (waves == 2 ? 2 : 1); ++wv) {
+        if (e.P > 0)
+            ep_dispatch_push_kernel<<<comm_ep_push_sms(e.P, c->world), kPushThreads, kPushSmem, s>>>(
+                c->peers, c->rank, c->world, e.xh, e.sorted_tok, e.sorted_expert, e.H, e.P, e.plan, e.recv_off, c->wait_cycles,
+                waves == 2 ? wv : -1);
+        ++c->seq[kChDispatch];
+        const int st = comm_launch_signal(c, kChDispatch, s);
+        if (st) return st;
     }
-    ++c->seq[kChDispatch];
-    return comm_launch_signal(c, kChDispatch, s);
+    return GSB_OK;
 }
 
 }  // namespace gsb

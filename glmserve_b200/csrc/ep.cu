@@ -26,7 +26,7 @@ EpHeap ep_heap(const gsb_moe_config& c, int n, int recv_cap) {
 struct EpWs {
     int* status; float* logits; float* scores; int* ids; float* w; int* expert_offsets; int* sorted_tok;
     int* sorted_row; int* slot_pos; int* sorted_expert; int* disp_scratch; int* recv_offsets; int* send_base; void** ydst;
-    int* plan; int* tiles; int* tiles_sh; int* segs;
+    int* plan; int* tiles; int* tiles2; int* tiles_sh; int* segs;
     __half* hbuf; __half* xs_local; __half* hbuf_sh;
     size_t total;
 };
@@ -57,6 +57,7 @@ EpWs ep_carve(const gsb_moe_config& c, int n, int recv_cap, void* base) {
     ws.ydst = reinterpret_cast<void**>(take(((size_t)recv_cap + n) * sizeof(void*)));
     ws.plan = reinterpret_cast<int*>(take((4 + 4 * kMaxWorld) * sizeof(int)));
     ws.tiles = reinterpret_cast<int*>(take(prefill_tile_bytes(recv_cap / (c.topk > 0 ? c.topk : 1) + 1, c.topk, El)));
+    ws.tiles2 = reinterpret_cast<int*>(take(prefill_tile_bytes(recv_cap / (c.topk > 0 ? c.topk : 1) + 1, c.topk, El)));
     ws.tiles_sh = reinterpret_cast<int*>(take(prefill_tile_bytes(n, 1, 1)));
     ws.segs = reinterpret_cast<int*>(take(decode_seg_bytes_raw((size_t)recv_cap, (size_t)n, El)));
     ws.hbuf = reinterpret_cast<__half*>(take(((size_t)recv_cap + n) * imax * sizeof(__half)));
@@ -173,7 +174,11 @@ int forward_ep_impl(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, co
         return GSB_ERR_CUDA;
     if (cudaEventRecord(layer->ep_fork, s) != cudaSuccess || cudaStreamWaitEvent(layer->ep_side, layer->ep_fork, 0) != cudaSuccess)
         return GSB_ERR_CUDA;
-    st = comm_ep_push(comm, ex, layer->ep_side);
+    // tcgen05 path on four or more GPUs: the rows travel in two waves (first and second half of every owner's
+    // experts) and the routed GEMMs of the first half run while the second half is still on the link - with more
+    // ranks more of the rows are remote and the push outlasts the shared expert (8 GPUs: by 0.36 ms)
+    const int waves = (!decode && comm->world >= 4 && El >= 2) ? 2 : 1;
+    st = comm_ep_push(comm, ex, layer->ep_side, waves);
     if (st) return st;
     if (cudaEventRecord(layer->ep_join, layer->ep_side) != cudaSuccess) return GSB_ERR_CUDA;
     mark(1);
@@ -212,17 +217,27 @@ int forward_ep_impl(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, co
         // CTAs without an SM would start their tiles only when the push is over
         a.sm_count = layer->sm_count - comm_ep_push_sms(P, comm->world);
         if (n > 0) { st = launch_prefill_ep_shared(a, s); if (st) return st; }
-        st = launch_prefill_ep_routed(a, s, 1);   // the tile list needs only the plan
+        PrefillEpArgs a0 = a, a1 = a;
+        if (waves == 2) { a0.e_begin = 0; a0.e_end = (El + 1) / 2; a1.e_begin = (El + 1) / 2; a1.e_end = El; a1.tiles = ws.tiles2; }
+        st = launch_prefill_ep_routed(a0, s, 1);   // the tile lists need only the plan
         if (st) return st;
+        if (waves == 2) { st = launch_prefill_ep_routed(a1, s, 1); if (st) return st; }
         mark(2);
-        st = comm_launch_wait(comm, kChDispatch, s);
+        st = comm_launch_wait(comm, kChDispatch, s, waves - 1);   // the first (or only) wave of every peer has landed
         if (st) return st;
-        // the routed experts take every SM: this rank's own push has to be off them first (it normally is by
-        // the time every peer's rows have arrived)
-        if (cudaStreamWaitEvent(s, layer->ep_join, 0) != cudaSuccess) return GSB_ERR_CUDA;
         mark(3);
-        a.sm_count = layer->sm_count;
-        st = launch_prefill_ep_routed(a, s, 2);
+        if (waves == 2) {
+            st = launch_prefill_ep_routed(a0, s, 2);               // beside this rank's own second wave: not on its SMs
+            if (st) return st;
+            st = comm_launch_wait(comm, kChDispatch, s);
+            if (st) return st;
+        }
+        // the rest takes every SM: this rank's own push has to be off them first (it normally is by the time
+        // every peer's rows have arrived)
+        if (cudaStreamWaitEvent(s, layer->ep_join, 0) != cudaSuccess) return GSB_ERR_CUDA;
+        PrefillEpArgs& al = waves == 2 ? a1 : a0;
+        al.sm_count = layer->sm_count;
+        st = launch_prefill_ep_routed(al, s, 2);
         if (st) return st;
     }
     mark(4);

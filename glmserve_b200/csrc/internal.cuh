@@ -61,7 +61,7 @@ struct gsb_moe_layer {
 
 namespace gsb {
 int comm_launch_signal(gsb_comm* c, int ch, cudaStream_t s);
-int comm_launch_wait(gsb_comm* c, int ch, cudaStream_t s);
+int comm_launch_wait(gsb_comm* c, int ch, cudaStream_t s, int back = 0);
 int comm_launch_signal_wait(gsb_comm* c, int ch, cudaStream_t s);
 struct EpExchange {
     const __half* xh;              // this rank's tokens [n, H] as fp16, in the feature order the receiving kernels
@@ -88,6 +88,7 @@ struct EpRouting {
 };
 int comm_ep_plan(gsb_comm* c, const EpExchange& e, cudaStream_t s, const EpRouting* routing = nullptr);
 bool comm_ep_route_fusable(int n, int E);
-int comm_ep_push(gsb_comm* c, const EpExchange& e, cudaStream_t s);
+// waves = 2: the rows for the first half of every owner's experts, a signal, then the rest and a second signal
+int comm_ep_push(gsb_comm* c, const EpExchange& e, cudaStream_t s, int waves = 1);
 int comm_ep_push_sms(int P, int world);   // SMs that push occupies by itself while it runs
 }  // namespace gsb

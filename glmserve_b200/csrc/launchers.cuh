@@ -173,6 +173,8 @@ struct PrefillEpArgs {
     __half* hbuf;                       // [recv_cap, I]
     __half* const* ydst;                // [recv_cap] where each received row's output goes
     int* tiles;                         // token-tile list over the received rows
+    int e_begin, e_end;                 // resident experts this call covers (0, 0 = all El): the exchange can hand
+                                        // the rows over in two waves, each with a tile list of its own
     const __nv_bfloat16* x; int n;      // this GPU's own tokens (shared expert)
     __half* xs_local;                   // [n, H] this GPU's tokens as fp16 in natural order, filled by the caller
     __half* hbuf_sh;                    // [n, Is]

@@ -697,15 +697,19 @@ int launch_prefill_ep_shared(const PrefillEpArgs& d, cudaStream_t s) {
 // recv_x) through its resident experts; the down kernel's epilogue stores every output row
 // straight to the GPU that owns the token (ydst) - compute and the return all-to-all in one kernel.
 int launch_prefill_ep_routed(const PrefillEpArgs& d, cudaStream_t s, int what) {
-    if (what & 1) tile_list_kernel<<<1, 1024, 0, s>>>(d.recv_offsets, d.El, d.El, 0, 0, d.tiles);
+    const int e0 = d.e_end > d.e_begin ? d.e_begin : 0, e1 = d.e_end > d.e_begin ? d.e_end : d.El;
+    // tile experts count from e0: the offsets and the weight streams are handed over from there
+    if (what & 1) tile_list_kernel<<<1, 1024, 0, s>>>(d.recv_offsets + e0, e1 - e0, d.El, 0, 0, d.tiles);
     if (!(what & 2)) return launch_status();
+    const size_t gu_expert = (size_t)(d.I / 16) * (d.H / kChunkCols) * kChunkBytes;
+    const size_t dn_expert = (size_t)(d.H / 32) * (d.I / kChunkCols) * kChunkBytes;
     PrefillKArgs g{};
-    g.packed = reinterpret_cast<const uint8_t*>(d.gate_up_packed); g.shared_packed = nullptr;
+    g.packed = reinterpret_cast<const uint8_t*>(d.gate_up_packed) + (size_t)e0 * gu_expert; g.shared_packed = nullptr;
     g.tiles = d.tiles; g.RB = d.I / 64; g.RBs = 1;
     g.K = d.H; g.Ks = d.H; g.units = d.I / 16; g.units_s = 1; g.E = d.El;
     g.hbuf = d.hbuf; g.ldh = d.I; g.ybuf = nullptr; g.H = d.H; g.ydst = nullptr; g.status = d.status;
     PrefillKArgs w = g;
-    w.packed = reinterpret_cast<const uint8_t*>(d.down_packed);
+    w.packed = reinterpret_cast<const uint8_t*>(d.down_packed) + (size_t)e0 * dn_expert;
     w.RB = d.H / 128; w.K = d.I; w.Ks = d.I; w.units = d.H / 32; w.units_s = 1;
     w.hbuf = nullptr; w.ybuf = nullptr; w.ydst = d.ydst;
     return run_gemm_pair(g, w, d.recv_x, d.recv_cap, d.H, d.hbuf, d.recv_cap, d.I, d.sm_count, s, nullptr);
