@@ -476,13 +476,50 @@ def run_ours(args) -> None:
         # the all-reduce alone, both algorithms, against NCCL as the baseline; the faster one is then
         # set for the tensor-parallel layer (the choice changes no bit of the result)
         us_alg_all = {}
+        # Device time of the collective: n calls from ONE host call (gsb_comm_allreduce_sum_n) for ours, one
+        # CUDA-graph replay of n calls for NCCL - launched call by call from Python both are bound by the host
+        # (~10-20 us per call) below about 20 us.
+        nrep = 50
+
+        def ours_n(buf):
+            comm.allreduce_sum_n(buf, 5)
+            barrier(); ea.record()
+            comm.allreduce_sum_n(buf, nrep)
+            eb.record(); barrier()
+            return ea.elapsed_time(eb) / nrep * 1e3
+
+        def nccl_n(buf):
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    for _ in range(3):
+                        dist.all_reduce(buf)
+                torch.cuda.current_stream().wait_stream(side)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for _ in range(nrep):
+                        dist.all_reduce(buf)
+                g.replay()
+                barrier(); ea.record()
+                g.replay()
+                eb.record(); barrier()
+                return ea.elapsed_time(eb) / nrep * 1e3, "cuda graph replay"
+            except Exception:          # capture of the collective refused: per-call launches from the host
+                torch.cuda.synchronize()
+                return timed(lambda: dist.all_reduce(buf), nrep, warm=5) * 1e3, "host-launched calls"
+        nccl_how = ""
         for nfl in (GLM["H"], T * GLM["H"]):
             buf = torch.zeros(nfl, device=dev)
             us_alg = {}
+            comm.allreduce_ll_limit(1)                      # the flag-in-data form off: time the two flag forms
             for name, limit in (("one_shot", 1 << 40), ("two_shot", 1)):
                 comm.allreduce_one_shot_limit(limit)
-                us_alg[name] = timed(lambda: comm.allreduce_sum(buf), 50, warm=5) * 1e3
-            us_alg["nccl"] = timed(lambda: dist.all_reduce(buf), 50, warm=5) * 1e3
+                us_alg[name] = ours_n(buf)
+            comm.allreduce_ll_limit(0)
+            if nfl <= 65536:                                # decode-sized: the form the library picks by default
+                us_alg["flag_in_data"] = ours_n(buf)
+            us_alg["nccl"], nccl_how = nccl_n(buf)
             keys = list(us_alg)
             us_alg_all[nfl] = dict(zip(keys, max_over_ranks([us_alg[k] for k in keys])))
         us_alg = us_alg_all[T * GLM["H"]]
@@ -530,7 +567,9 @@ def run_ours(args) -> None:
                                           "stage_us_reference_names": {"ar.mlp": us_ar, "layer_without_ar": ms_tp * 1e3 - us_ar},
                                           "allreduce_us_by_algorithm": {k: v for k, v in us_alg.items() if k != "nccl"},
                                           "nccl_allreduce_us": us_nccl, "allreduce_floats": T * GLM["H"],
-                                          "allreduce_one_row_us": us_alg_all[GLM["H"]], "status": int(st_tp)}
+                                          "allreduce_one_row_us": us_alg_all[GLM["H"]],
+                                          "allreduce_timing": "device time per call: 50 calls from one host call (ours), " + nccl_how + " (NCCL)",
+                                          "status": int(st_tp)}
         extra[f"spec_verify_block_8_layers_T256_tp{world}"] = {
             "us_per_block": us_blk, "us_per_layer": us_blk / nl,
             "note": "RMSNorm -> tensor-parallel layer (split-K kernels) -> NVLink all-reduce -> residual, "

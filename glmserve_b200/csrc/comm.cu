@@ -225,6 +225,64 @@ allreduce_kernel(const ArArgs a) {
     }
 }
 
+// Flag-in-data form for decode-sized messages: a 16-byte word carries two floats and the call's sequence number
+// twice, {x, seq, y, seq} - each 8-byte half validates itself, so the word may cross the link as one store or as
+// two.  A rank stores its words into its slot on every peer and then polls the peers' slots in its own memory
+// until both sequence numbers match: no fence, no separate flag, one NVLink traversal (the exchange of flags
+// costs the other forms ~4.7 us a round).  Slots alternate between two parities: a rank can be one call ahead of
+// a peer, never two, because a call needs every peer's words of the same call.  Sum order: rank 0..world-1 per
+// element with the own contribution from `data`, as in the other forms - the same bits.
+__global__ void __launch_bounds__(256)
+allreduce_ll_kernel(const ArArgs a) {
+    const int64_t nw = a.count4 * 2;
+    const uint32_t seq = (uint32_t)a.seq;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const float2* in = reinterpret_cast<const float2*>(a.data);
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < nw; w += stride) {
+        const float2 v = in[w];
+        const uint32_t x = __float_as_uint(v.x), y = __float_as_uint(v.y);
+        for (int p = 0; p < a.world; ++p) {
+            if (p == a.rank) continue;
+            uint8_t* dst = a.pr.base[p] + a.stage_off + (size_t)a.rank * a.area_bytes + (size_t)w * 16;
+            asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(x), "r"(seq), "r"(y), "r"(seq) : "memory");
+        }
+    }
+    const uint8_t* mine = a.pr.base[a.rank] + a.stage_off;
+    const long long start = clock64();
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < nw; w += stride) {
+        uint4 got[kMaxWorld];
+        uint32_t pending = 0;
+#pragma unroll
+        for (int r = 0; r < kMaxWorld; ++r)
+            if (r < a.world && r != a.rank) pending |= 1u << r;
+        while (pending) {
+#pragma unroll
+            for (int r = 0; r < kMaxWorld; ++r) {
+                if (!(pending >> r & 1u)) continue;
+                const uint8_t* src = mine + (size_t)r * a.area_bytes + (size_t)w * 16;
+                asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(got[r].x), "=r"(got[r].y), "=r"(got[r].z), "=r"(got[r].w) : "l"(src) : "memory");
+            }
+#pragma unroll
+            for (int r = 0; r < kMaxWorld; ++r)
+                if ((pending >> r & 1u) && got[r].y == seq && got[r].w == seq) pending &= ~(1u << r);
+            if (pending && clock64() - start > a.wait_cycles) {
+                atomicCAS(ctrl_of(a.pr, a.rank) + kStatusWord, 0, GSB_ERR_TIMEOUT);
+                return;
+            }
+        }
+        const float2 own = in[w];
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int r = 0; r < kMaxWorld; ++r) {
+            if (r >= a.world) continue;
+            acc.x += r == a.rank ? own.x : __uint_as_float(got[r].x);
+            acc.y += r == a.rank ? own.y : __uint_as_float(got[r].z);
+        }
+        reinterpret_cast<float2*>(a.data)[w] = acc;
+    }
+}
+
 // ---- expert-parallel exchange ---------------------------------------------------------------
 // Counts: rank posts its per-expert row counts (from its local dispatch offsets) and the layout of its
 // own buffers {receive buffer offset, receive capacity, per-slot row buffer offset} to every peer, so a
@@ -550,7 +608,9 @@ int gsb_comm_create(int rank, int world, size_t heap_bytes, void* out_handle, gs
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     c->sm_count = sms > 0 ? sms : 148;
     if (cudaMalloc(reinterpret_cast<void**>(&c->local), kCtrlBytes + c->heap_bytes) != cudaSuccess) { delete c; return GSB_ERR_CUDA; }
-    if (cudaMemset(c->local, 0, kCtrlBytes) != cudaSuccess) { cudaFree(c->local); delete c; return GSB_ERR_CUDA; }
+    // all of it zero before any peer can reach it: the flag-in-data all-reduce takes a word for valid when its
+    // sequence numbers match, and those start at 1
+    if (cudaMemset(c->local, 0, kCtrlBytes + c->heap_bytes) != cudaSuccess) { cudaFree(c->local); delete c; return GSB_ERR_CUDA; }
     cudaIpcMemHandle_t h;
     if (cudaIpcGetMemHandle(&h, c->local) != cudaSuccess) { cudaFree(c->local); delete c; return GSB_ERR_CUDA; }
     memcpy(out_handle, &h, sizeof(h));
@@ -624,7 +684,15 @@ size_t gsb_comm_allreduce_reserve(gsb_comm* c, int64_t max_count) {
     if (!c || max_count < 0) return 0;
     const size_t fl = ((size_t)max_count + 3) / 4 * 4;
     c->ar_stage_floats = fl;
-    return 4 * (fl + kArPad) * sizeof(float);
+    // behind the staging: the flag-in-data area, two parities of world slots of 16-byte words (two floats each)
+    c->ar_ll_words = (fl < (size_t)kArLLFloats ? fl : (size_t)kArLLFloats) / 2;
+    return 4 * (fl + kArPad) * sizeof(float) + 2 * (size_t)c->world * c->ar_ll_words * 16;
+}
+
+int gsb_comm_allreduce_ll_limit(gsb_comm* c, int64_t floats) {
+    if (!c || floats < 0) return GSB_ERR_INVALID_ARG;
+    c->ar_ll_limit = floats ? floats : (int64_t)kArLLFloats;
+    return GSB_OK;
 }
 
 int gsb_comm_allreduce_one_shot_limit(gsb_comm* c, int64_t total_floats) {
@@ -639,10 +707,21 @@ int gsb_comm_allreduce_sum(gsb_comm* c, float* data, int64_t count, void* stream
     if (count % 4 || (reinterpret_cast<uintptr_t>(data) & 15)) return GSB_ERR_INVALID_ARG;
     if ((size_t)count > c->ar_stage_floats) return GSB_ERR_TOO_LARGE;
     const size_t area = c->ar_stage_floats + kArPad;
-    if (4 * area * sizeof(float) > c->heap_bytes) return GSB_ERR_WORKSPACE;
-    const unsigned seq = ++c->seq[kChAllReduce];
+    const size_t ll_bytes = 2 * (size_t)c->world * c->ar_ll_words * 16;
+    if (4 * area * sizeof(float) + ll_bytes > c->heap_bytes) return GSB_ERR_WORKSPACE;
     ArArgs a{};
     a.pr = c->peers; a.rank = c->rank; a.world = c->world; a.data = data; a.count4 = count / 4;
+    if (count <= c->ar_ll_limit && (size_t)count / 2 <= c->ar_ll_words) {
+        const unsigned lseq = ++c->ar_ll_seq;
+        a.area_bytes = c->ar_ll_words * 16;                                   // one source's slot
+        a.stage_off = kCtrlBytes + 4 * area * sizeof(float) + (size_t)(lseq & 1u) * c->world * a.area_bytes;
+        a.seq = (int)lseq; a.wait_cycles = c->wait_cycles;
+        int64_t lb = (a.count4 * 2 + 255) / 256;
+        if (lb > c->sm_count) lb = c->sm_count;
+        allreduce_ll_kernel<<<(unsigned)lb, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+        return launch_status();
+    }
+    const unsigned seq = ++c->seq[kChAllReduce];
     a.area_bytes = area * sizeof(float);
     a.stage_off = kCtrlBytes + (size_t)(seq & 1u) * 2 * a.area_bytes;
     a.seq = (int)seq; a.wait_cycles = c->wait_cycles;
@@ -656,6 +735,14 @@ int gsb_comm_allreduce_sum(gsb_comm* c, float* data, int64_t count, void* stream
     if (blocks < 1) blocks = 1;
     allreduce_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
     return launch_status();
+}
+
+int gsb_comm_allreduce_sum_n(gsb_comm* c, float* data, int64_t count, int n, void* stream) {
+    for (int i = 0; i < n; ++i) {
+        const int st = gsb_comm_allreduce_sum(c, data, count, stream);
+        if (st) return st;
+    }
+    return GSB_OK;
 }
 
 }  // extern "C"

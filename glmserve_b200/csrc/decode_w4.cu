@@ -798,26 +798,43 @@ struct RouteFusedArgs {
 
 constexpr int kRouteCluster = 8;   // CTAs that share the top-k phase
 
-__global__ void __cluster_dims__(kRouteCluster, 1, 1) __launch_bounds__(1024)
-route_fused_kernel(const RouteFusedArgs a) {
+// CL = 1: up to 32 tokens a single block has a warp per token and needs no cluster (and no cluster barrier).
+template <int CL>
+__device__ __forceinline__ void route_fused_body(const RouteFusedArgs& a, int rank) {
     extern __shared__ int route_smem[];
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
-    const int rank = (int)cluster.block_rank();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     asm volatile("griddepcontrol.wait;" ::: "memory");                // launched under the logits kernel's tail
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // gate/up may be scheduled; it waits for this grid
     if (rank == 0 && threadIdx.x < 4) a.status[threadIdx.x] = 0;
     // top-k: a warp per token over the whole cluster (one block alone spends 15 us on 64 tokens)
-    for (int t = rank + kRouteCluster * warp; t < a.n; t += kRouteCluster * 32)   // tokens dealt round-robin to the CTAs
+    for (int t = rank + CL * warp; t < a.n; t += CL * 32)   // tokens dealt round-robin to the CTAs
         topk_token<8, true>(a.scores + (size_t)t * a.E, a.e_bias, a.E, a.topk, a.norm_topk, a.routed_scale, lane,
                             a.ids + (size_t)t * a.topk, a.w + (size_t)t * a.topk);
-    cluster.sync();    // hardware barrier with release/acquire: every CTA's ids are visible to CTA 0
-    if (rank != 0) return;
+}
+__device__ __forceinline__ void route_fused_tail(const RouteFusedArgs& a) {
+    extern __shared__ int route_smem[];
     dispatch_block(a.ids, a.n * a.topk, a.topk, a.E, a.expert_offsets, a.sorted_tok, a.sorted_row, a.slot_pos, route_smem);
     __syncthreads();   // the block's own global writes (expert_offsets) are visible to it from here
     seg_build_block(a.expert_offsets, a.E, a.n, a.n * a.topk, a.has_shared, a.segs, a.xsegs, a.units_gu,
                     a.units_gu_s, a.units_dn, a.grid);
+}
+
+__global__ void __cluster_dims__(kRouteCluster, 1, 1) __launch_bounds__(1024)
+route_fused_kernel(const RouteFusedArgs a) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    route_fused_body<kRouteCluster>(a, rank);
+    cluster.sync();    // hardware barrier with release/acquire: every CTA's ids are visible to CTA 0
+    if (rank != 0) return;
+    route_fused_tail(a);
+}
+
+__global__ void __launch_bounds__(1024)
+route_fused_small_kernel(const RouteFusedArgs a) {
+    route_fused_body<1>(a, 0);
+    __syncthreads();   // the block's own global writes (ids) are visible to it from here
+    route_fused_tail(a);
 }
 
 // bf16 activations -> fp16 in fragment order or natural order (exact for |x| in the fp16 normal
@@ -1035,12 +1052,14 @@ int launch_decode_layer(const DecodeArgs& d, cudaStream_t s) {
         r.status = d.status;
         const size_t smem = (size_t)(kDispWarps * d.E + 1024) * sizeof(int);   // 36 KiB at 256 experts
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(kRouteCluster); cfg.blockDim = dim3(1024); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+        const bool small = d.n <= 32;
+        cfg.gridDim = dim3(small ? 1 : kRouteCluster); cfg.blockDim = dim3(1024); cfg.dynamicSmemBytes = smem; cfg.stream = s;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the logits kernel triggers at its start
         at[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, route_fused_kernel, r) != cudaSuccess) return GSB_ERR_LAUNCH;
+        if ((small ? cudaLaunchKernelEx(&cfg, route_fused_small_kernel, r) : cudaLaunchKernelEx(&cfg, route_fused_kernel, r)) != cudaSuccess)
+            return GSB_ERR_LAUNCH;
     } else {
         if (cudaMemsetAsync(d.status, 0, 16, s) != cudaSuccess) return GSB_ERR_CUDA;
         seg_build_kernel<<<1, 1024, 0, s>>>(d.expert_offsets, d.E, d.n, P, shared ? 1 : 0, d.segs, xsegs, d.I / 16,

@@ -6,6 +6,7 @@
 namespace gsb {
 
 constexpr int kMaxWorld = 8;
+constexpr int kArLLFloats = 65536;   // largest all-reduce message of the flag-in-data form (256 KiB)
 constexpr size_t kCtrlBytes = 1 << 20;          // control area at the start of the heap
 constexpr long long kCommWaitCycles = 4000000000LL;
 
@@ -40,6 +41,9 @@ struct gsb_comm {
     unsigned seq[gsb::kNumCh] = {};
     size_t ar_stage_floats = 0;                 // largest message the all-reduce staging was reserved for
     int64_t ar_one_shot_limit = 1 << 18;        // count * world up to which the one-shot form is used
+    size_t ar_ll_words = 0;                     // 16-byte words per source and parity of the flag-in-data area (0: none)
+    int64_t ar_ll_limit = gsb::kArLLFloats;     // messages up to this many floats take the flag-in-data form
+    unsigned ar_ll_seq = 0;
     long long wait_cycles = gsb::kCommWaitCycles;  // budget of every device-side wait (SM clocks)
     bool loopback = false;                      // every peer slot maps this rank's own heap (single-process tests)
     int sm_count = 148;

@@ -72,12 +72,24 @@ class Comm:
         """count * world up to which the all-reduce is a one-shot pull (0 = default 2**21)."""
         check(lib().gsb_comm_allreduce_one_shot_limit(self._h, C.c_int64(total_floats)), "allreduce_one_shot_limit")
 
+    def allreduce_ll_limit(self, floats: int) -> None:
+        """Messages up to ``floats`` floats take the flag-in-data form (0 = default 65536, 1 = off)."""
+        check(lib().gsb_comm_allreduce_ll_limit(self._h, C.c_int64(floats)), "allreduce_ll_limit")
+
     def allreduce_sum(self, t):
         """In-place sum of a contiguous float32 CUDA tensor over all ranks (rank order)."""
         import torch
         assert t.dtype == torch.float32 and t.is_contiguous() and t.is_cuda
         check(lib().gsb_comm_allreduce_sum(self._h, C.c_void_p(t.data_ptr()), C.c_int64(t.numel()),
                                            C.c_void_p(torch.cuda.current_stream().cuda_stream)), "allreduce_sum")
+        return t
+
+    def allreduce_sum_n(self, t, n: int):
+        """``n`` in-place sums launched from one host call (timing aid: no per-call host cost in between)."""
+        import torch
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.is_cuda
+        check(lib().gsb_comm_allreduce_sum_n(self._h, C.c_void_p(t.data_ptr()), C.c_int64(t.numel()), int(n),
+                                             C.c_void_p(torch.cuda.current_stream().cuda_stream)), "comm_allreduce_sum_n")
         return t
 
     def allreduce_sum_rows(self, t):

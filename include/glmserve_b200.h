@@ -386,6 +386,14 @@ GSB_API int gsb_comm_allreduce_sum(gsb_comm* comm, float* data, int64_t count, v
  * default (2^18).  Same value on every rank; both orders of summation are rank 0..world-1 per element, so
  * the result does not depend on the choice. */
 GSB_API int gsb_comm_allreduce_one_shot_limit(gsb_comm* comm, int64_t total_floats);
+/* Decode-sized messages (count <= floats, at most 65536 = the default; 0 restores it, 1 switches the form off)
+ * take a third form: every 16-byte word carries two floats and the call's sequence number twice, so the
+ * receiver needs no flag round - one NVLink traversal.  Same rank-order sums, same bits.  Same value on every
+ * rank. */
+GSB_API int gsb_comm_allreduce_ll_limit(gsb_comm* comm, int64_t floats);
+/* n back-to-back in-place sums from one host call (data ends as the n-fold sum): what a benchmark uses to see
+ * the collective's device time instead of the host's per-call cost. */
+GSB_API int gsb_comm_allreduce_sum_n(gsb_comm* comm, float* data, int64_t count, int n, void* stream);
 
 /* Expert-parallel forward of one layer (cfg.ep_size = world): router and dispatch on this GPU's
  * n tokens, per-expert counts and buffer layouts exchanged, rows pushed over NVLink into the owners'

@@ -47,6 +47,20 @@ def check_allreduce(comm, rank, world, dev):
         assert comm.status() == 0
         got.append(y)
     assert torch.equal(got[0], got[1]) and torch.equal(got[0], got[2]), "one-shot vs two-shot"
+    # decode-sized messages: the flag-in-data form (default) against the flag forms, bit for bit
+    for count in (4, 6144, 4 * 6144, 65536):
+        gen = torch.Generator(device=dev); gen.manual_seed(500 + rank)
+        x = torch.randn(count, generator=gen, device=dev)
+        got = []
+        for ll in (0, 1, 0):                                 # on, off, on again
+            comm.allreduce_ll_limit(ll)
+            for rep in range(3):                             # both parities of the slots, and a reuse
+                y = x.clone()
+                comm.allreduce_sum(y)
+                assert comm.status() == 0
+                got.append(y)
+        assert all(torch.equal(g, got[0]) for g in got), f"flag-in-data all-reduce differs (count={count})"
+    comm.allreduce_ll_limit(0)
     rows = torch.randn((5, 6144), generator=torch.Generator(device=dev).manual_seed(7 + rank), device=dev)
     a, b = rows.clone(), rows.clone()
     comm.allreduce_sum(a.view(-1))
