@@ -426,7 +426,7 @@ def run_ours(args) -> None:
         recv_cap = 2 * Te * GLM["topk"]
         layer_ep = ops.MoELayer(shard_layer_ep(Lt, rank, world), keep_raw=False)
         ar_max = 256 * GLM["H"]
-        heap = layer_ep.ep_heap_bytes(Te, recv_cap) + 4 * (ar_max + 64) * 4 + (4 << 20)
+        heap = layer_ep.ep_heap_bytes(Te, recv_cap) + Comm.reserve_bytes(world, ar_max) + (1 << 20)
         comm = Comm(heap_bytes=heap, allreduce_max_count=ar_max)
         xe = make_x_torch(Te, GLM["H"], seed=300 + rank, device=dev)
         oe = torch.empty((Te, GLM["H"]), dtype=torch.float32, device=dev)

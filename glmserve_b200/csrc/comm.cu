@@ -680,13 +680,20 @@ int gsb_comm_barrier(gsb_comm* c, void* stream) {
 // The first bytes of the heap are the all-reduce staging: two parities of two areas of
 // (max_count + kArPad) floats; callers that also use the heap for expert parallelism place their
 // buffers after gsb_comm_allreduce_reserve() bytes.
+// staging of the two flag forms, then the flag-in-data area: two parities of world slots of 16-byte words
+size_t gsb_comm_allreduce_reserve_bytes(int world, int64_t max_count) {
+    if (world < 1 || max_count < 0) return 0;
+    const size_t fl = ((size_t)max_count + 3) / 4 * 4;
+    const size_t ll_words = (fl < (size_t)kArLLFloats ? fl : (size_t)kArLLFloats) / 2;
+    return 4 * (fl + kArPad) * sizeof(float) + 2 * (size_t)world * ll_words * 16;
+}
+
 size_t gsb_comm_allreduce_reserve(gsb_comm* c, int64_t max_count) {
     if (!c || max_count < 0) return 0;
     const size_t fl = ((size_t)max_count + 3) / 4 * 4;
     c->ar_stage_floats = fl;
-    // behind the staging: the flag-in-data area, two parities of world slots of 16-byte words (two floats each)
     c->ar_ll_words = (fl < (size_t)kArLLFloats ? fl : (size_t)kArLLFloats) / 2;
-    return 4 * (fl + kArPad) * sizeof(float) + 2 * (size_t)c->world * c->ar_ll_words * 16;
+    return gsb_comm_allreduce_reserve_bytes(c->world, max_count);
 }
 
 int gsb_comm_allreduce_ll_limit(gsb_comm* c, int64_t floats) {

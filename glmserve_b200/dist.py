@@ -52,6 +52,12 @@ class Comm:
         if not loopback_world:
             self._dist.barrier()
 
+    @staticmethod
+    def reserve_bytes(world: int, allreduce_max_count: int) -> int:
+        """Bytes at the start of the heap the all-reduce takes: add them when sizing ``heap_bytes``."""
+        lib().gsb_comm_allreduce_reserve_bytes.restype = C.c_size_t
+        return int(lib().gsb_comm_allreduce_reserve_bytes(int(world), C.c_int64(allreduce_max_count)))
+
     def set_wait_cycles(self, cycles: int) -> None:
         """Budget of every device-side wait in SM clock cycles (0 = default, about two seconds)."""
         check(lib().gsb_comm_set_wait_cycles(self._h, C.c_longlong(cycles)), "comm_set_wait_cycles")

@@ -380,6 +380,8 @@ GSB_API int gsb_comm_barrier(gsb_comm* comm, void* stream);
  * gsb_comm_allreduce_reserve(max_count) must be called once (same value on every rank): it
  * returns the bytes at the START of the heap that the all-reduce staging occupies. */
 GSB_API size_t gsb_comm_allreduce_reserve(gsb_comm* comm, int64_t max_count);
+/* The same byte count without a communicator, for sizing the heap before gsb_comm_create. */
+GSB_API size_t gsb_comm_allreduce_reserve_bytes(int world, int64_t max_count);
 GSB_API int gsb_comm_allreduce_sum(gsb_comm* comm, float* data, int64_t count, void* stream);
 /* Algorithm switch: messages with count * world <= total_floats (and world * count <= 2 * max_count, the
  * room the staging has) take the one-shot form, larger ones reduce-scatter + all-gather.  0 restores the
