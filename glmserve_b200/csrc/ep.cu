@@ -210,7 +210,7 @@ int forward_ep_impl(gsb_moe_layer* layer, gsb_comm* comm, const void* x_bf16, co
         a.H = c.hidden; a.I = c.moe_inter; a.Is = c.shared_inter; a.El = El;
         a.recv_offsets = ws.recv_offsets; a.recv_x = xbuf; a.recv_cap = recv_cap; a.hbuf = ws.hbuf;
         a.ydst = reinterpret_cast<__half* const*>(ws.ydst); a.tiles = ws.tiles;
-        a.x = x; a.n = n; a.xs_local = ws.xs_local; a.hbuf_sh = ws.hbuf_sh;
+        a.n = n; a.xs_local = ws.xs_local; a.hbuf_sh = ws.hbuf_sh;
         a.y_shared = reinterpret_cast<__half*>(ybuf) + (size_t)P * c.hidden;
         a.tiles_sh = ws.tiles_sh; a.status = ws.status;
         // the push keeps a few SMs to itself: the shared expert's persistent CTAs take the others, or the

@@ -175,7 +175,7 @@ struct PrefillEpArgs {
     int* tiles;                         // token-tile list over the received rows
     int e_begin, e_end;                 // resident experts this call covers (0, 0 = all El): the exchange can hand
                                         // the rows over in two waves, each with a tile list of its own
-    const __nv_bfloat16* x; int n;      // this GPU's own tokens (shared expert)
+    int n;                              // this GPU's own tokens (shared expert)
     __half* xs_local;                   // [n, H] this GPU's tokens as fp16 in natural order, filled by the caller
     __half* hbuf_sh;                    // [n, Is]
     __half* y_shared;                   // [n, H]
