@@ -40,6 +40,14 @@ def test_pure_host_entry_points_validate_arguments():
     assert L.gsb_prepack_bytes(1, 64, 1000) == 0
     assert L.gsb_moe_layer_create(None, None) == 1
     assert L.gsb_moe_route_static_max_floats() == 65536
+    # heap bytes the all-reduce reserves: staging of four areas plus two parities of world slots of the
+    # flag-in-data words (8 bytes per float, at most 65536 floats) - it grows with the world size
+    L.gsb_comm_allreduce_reserve_bytes.restype = ctypes.c_size_t
+    rb = lambda w, n: L.gsb_comm_allreduce_reserve_bytes(w, ctypes.c_int64(n))
+    assert rb(2, 6144) == 4 * (6144 + 64) * 4 + 2 * 2 * (6144 // 2) * 16
+    assert rb(8, 256 * 6144) == 4 * (256 * 6144 + 64) * 4 + 2 * 8 * 32768 * 16
+    assert rb(8, 1 << 20) > rb(4, 1 << 20) > rb(2, 1 << 20)
+    assert rb(0, 16) == 0 and rb(2, -1) == 0
 
 
 def test_shim_header_names_match_reference_surface():
