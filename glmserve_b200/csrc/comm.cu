@@ -595,6 +595,12 @@ using namespace gsb;
 
 extern "C" {
 
+// One-shot while a rank sends at most ~4 MB ((world - 1) copies of the message): measured for 64 x 6144 floats,
+// device time one-shot / two-shot: 2 ranks 14.0 / 18.7 us, 4 ranks 21.1 / 21.1, 8 ranks 38.6 / 23.3.
+static int64_t default_one_shot_limit(int world) {
+    return ((int64_t)1 << 20) * world / (world > 1 ? world - 1 : 1);
+}
+
 int gsb_comm_handle_bytes(void) { return (int)sizeof(cudaIpcMemHandle_t); }
 
 int gsb_comm_create(int rank, int world, size_t heap_bytes, void* out_handle, gsb_comm** out) {
@@ -603,6 +609,7 @@ int gsb_comm_create(int rank, int world, size_t heap_bytes, void* out_handle, gs
     gsb_comm* c = new (std::nothrow) gsb_comm();
     if (!c) return GSB_ERR_CUDA;
     c->rank = rank; c->world = world;
+    c->ar_one_shot_limit = default_one_shot_limit(world);
     c->heap_bytes = (heap_bytes + 255) / 256 * 256;
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -704,7 +711,7 @@ int gsb_comm_allreduce_ll_limit(gsb_comm* c, int64_t floats) {
 
 int gsb_comm_allreduce_one_shot_limit(gsb_comm* c, int64_t total_floats) {
     if (!c || total_floats < 0) return GSB_ERR_INVALID_ARG;
-    c->ar_one_shot_limit = total_floats ? total_floats : (int64_t)(1 << 18);
+    c->ar_one_shot_limit = total_floats ? total_floats : default_one_shot_limit(c->world);
     return GSB_OK;
 }
 

@@ -385,7 +385,7 @@ GSB_API size_t gsb_comm_allreduce_reserve_bytes(int world, int64_t max_count);
 GSB_API int gsb_comm_allreduce_sum(gsb_comm* comm, float* data, int64_t count, void* stream);
 /* Algorithm switch: messages with count * world <= total_floats (and world * count <= 2 * max_count, the
  * room the staging has) take the one-shot form, larger ones reduce-scatter + all-gather.  0 restores the
- * default (2^18).  Same value on every rank; both orders of summation are rank 0..world-1 per element, so
+ * default (2^20 * world / (world - 1): one-shot while a rank sends at most about 4 MB).  Same value on every rank; both orders of summation are rank 0..world-1 per element, so
  * the result does not depend on the choice. */
 GSB_API int gsb_comm_allreduce_one_shot_limit(gsb_comm* comm, int64_t total_floats);
 /* Decode-sized messages (count <= floats, at most 65536 = the default; 0 restores it, 1 switches the form off)
